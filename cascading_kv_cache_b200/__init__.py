@@ -1,0 +1,12 @@
+"""B200-native cascading KV cache hot path: the cache update and the attention over the cache.
+
+The package is a host-side mirror of the reference's ``cascade/models`` interface for this path;
+all device work is done by hand-written sm_100a kernels in ``libckv_b200.so`` (C ABI in
+``include/cascade_kv_b200.h``).  There is no CPU or PyTorch fallback.
+"""
+from .cascading_cache import CascadingKVCache, cascade_every_n  # noqa: F401
+from .cascade_attention import (  # noqa: F401
+    CascadeAttention, LlamaCascadeAttention, Qwen2CascadeAttention, cascade_attention)
+
+__all__ = ["CascadingKVCache", "cascade_every_n", "CascadeAttention", "LlamaCascadeAttention",
+           "Qwen2CascadeAttention", "cascade_attention"]

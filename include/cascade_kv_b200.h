@@ -1,0 +1,163 @@
+/*
+ * cascade_kv_b200 -- C ABI of the B200 (sm_100a) cascading KV cache hot path.
+ *
+ * Plain pointers and sizes only; no torch types.  Every pointer is a DEVICE
+ * pointer unless its comment says "host".  All entry points return 0 on
+ * success and a negative CKV_E_* code on failure; ckv_last_error() gives the
+ * message of the calling thread's last failure.  Nothing here synchronises the
+ * stream or allocates device memory: callers own every buffer, kernels mutate
+ * the cache state in place on the stream they are given.
+ *
+ * One "lane" is one (batch, kv_head) pair.  Cache state of one layer
+ * (reference: CascadingKVCache.init_cache, cascade/models/cascading_cache.py:1187-1276):
+ *
+ *   key_cache, value_cache  [B, KVH, S, D]   cache dtype, contiguous, S = cascades * window
+ *   score_cache             [B, KVH, S]      cache dtype
+ *   sink_keys, sink_values  [B, KVH, NS, D]  cache dtype
+ *   og_pos                  [B, KVH, S]      int64, 1-based stream index of the token in each slot
+ *
+ * The reference also stores, per lane, quantities that are identical for every
+ * lane because they depend only on how many tokens were seen (the slot
+ * counters and everything derived from them).  Here they are stored ONCE:
+ *
+ *   mask       [S]   uint8, 1 = slot empty          (reference: bool [B,KVH,S])
+ *   sink_mask  [NS]  uint8, 1 = slot empty          (reference: bool [B,KVH,NS])
+ *   pos        [S]   int64 rank of the slot's token (reference: int64 [B,KVH,S])
+ *   sink_pos   [NS]  int64
+ *   stored_tokens, start_indices [C] int64          (reference: [B,KVH,C])
+ *   stored_sinks [1] int64                          (reference: [B,KVH])
+ *   seen_tokens  [1] int64                          (reference: seen_tokens_by_layer[l])
+ *   every_n      [C] int64  admission stride per cascade (reference: do_cache_every_n)
+ *
+ * The host-side mirror exposes them as stride-0 expanded views with the
+ * reference's shapes.
+ */
+#ifndef CASCADE_KV_B200_H
+#define CASCADE_KV_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CKV_ABI_VERSION 1
+
+enum { CKV_F32 = 0, CKV_F16 = 1, CKV_BF16 = 2 };
+enum { CKV_REDUCE_MEAN = 0, CKV_REDUCE_MAX = 1, CKV_REDUCE_MEDIAN = 2 };
+/* CKV_ADMIT_STRIDE: every incoming score is zero and the score cache is never
+ * touched by attention (reference: update(..., score_states=None),
+ * cascading_cache.py:1306-1311).  CKV_ADMIT_EMA: attention feeds EMA scores. */
+enum { CKV_ADMIT_STRIDE = 0, CKV_ADMIT_EMA = 1 };
+
+enum {
+    CKV_OK = 0,
+    CKV_E_ARG = -1,        /* bad shape / dtype / null pointer / alignment */
+    CKV_E_UNSUPPORTED = -2,/* configuration outside what the kernels implement */
+    CKV_E_WORKSPACE = -3,  /* workspace too small */
+    CKV_E_CUDA = -4        /* a CUDA runtime call failed */
+};
+
+/* flags of ckv_attention */
+enum {
+    CKV_ATTN_UPDATE = 1,        /* also run the score EMA (EMA rule) and the cache update */
+    CKV_ATTN_FORCE_GENERIC = 2  /* use the plain CUDA-core kernels even where a tuned path exists */
+};
+
+typedef struct ckv_config {
+    int32_t batch;             /* B */
+    int32_t kv_heads;          /* KVH */
+    int32_t q_heads;           /* H, a multiple of KVH */
+    int32_t head_dim;          /* D */
+    int32_t num_sinks;         /* NS */
+    int32_t window;            /* W, slots per cascade */
+    int32_t cascades;          /* C */
+    int32_t dtype;             /* CKV_F32 / CKV_F16 / CKV_BF16 (cache and activations) */
+    int32_t eager_fill;        /* reference: CascadingKVCache(eager_fill=...) */
+    int32_t head_reduction;    /* CKV_REDUCE_*   (reference: config._head_reduction) */
+    int32_t homogeneous_heads; /* reference: config._homogeneous_heads */
+    int32_t admission;         /* CKV_ADMIT_* */
+    double beta;               /* EMA coefficient (reference: cache.beta) */
+} ckv_config;
+
+typedef struct ckv_layer_state {
+    void *key_cache;
+    void *value_cache;
+    void *score_cache;
+    void *sink_keys;
+    void *sink_values;
+    uint8_t *mask;
+    uint8_t *sink_mask;
+    int64_t *pos;
+    int64_t *og_pos;
+    int64_t *sink_pos;
+    int64_t *stored_tokens;
+    int64_t *start_indices;
+    int64_t *stored_sinks;
+    int64_t *seen_tokens;
+    const int64_t *every_n;
+} ckv_layer_state;
+
+int ckv_abi_version(void);
+const char *ckv_last_error(void);
+
+/*
+ * Insert n_tokens new tokens per lane into the cache, in stream order.
+ * Replaces: sink_cache(...) / SinkCacheFunc.forward / the Triton kernel
+ * _update_kv_cache (cascade/models/cascading_cache.py:962-1028, :777-901,
+ * :145-774) and the counter bump in CascadingKVCache.update (:1346).
+ *
+ *   key, value  [B, KVH, n_tokens, D] cache dtype; element strides for b/h/t are given,
+ *               the last dimension is contiguous and every row 16-byte aligned.
+ *   scores      [B, >=KVH, n_tokens] cache dtype with element strides, or NULL = all zero
+ *               (only heads < KVH are read, as in the reference).
+ * seen_tokens is advanced by n_tokens on the device.
+ */
+int ckv_cascade_update(const ckv_config *cfg, const ckv_layer_state *st,
+                       const void *key, const void *value,
+                       int64_t kv_stride_b, int64_t kv_stride_h, int64_t kv_stride_t,
+                       const void *scores, int64_t s_stride_b, int64_t s_stride_h, int64_t s_stride_t,
+                       int32_t n_tokens, void *cuda_stream);
+
+/* Bytes of scratch ckv_attention needs for calls of up to n_tokens query tokens. */
+size_t ckv_attention_workspace_bytes(const ckv_config *cfg, int32_t n_tokens);
+
+/*
+ * Attention of n_tokens new tokens over [sinks | cascade cache | the new tokens
+ * themselves (causal)], with RoPE applied at cache positions, followed (flag
+ * CKV_ATTN_UPDATE) by the EMA score update and the cache update.
+ * Replaces: CascadeAttention.forward_cascade position/RoPE logic
+ * (cascade/models/cascade_attention.py:114-181), cascade_attn_eager (:250-340),
+ * calc_scores (:231-248), and stands in for cascade_attn_flash + the Triton
+ * attention(q,k,v,causal,sm_scale,mask,beta) (:202-229,
+ * cascade/models/flash_attention.py:540-652) with the eager path's exact score
+ * definition.
+ *
+ *   q           [B, H, n_tokens, D]    un-rotated, element strides for b/h/t
+ *   key, value  [B, KVH, n_tokens, D]  un-rotated, element strides for b/h/t
+ *   rope        [rope_rows, D] cache dtype: row p = (cos(p*f_0..f_{D/2-1}) | sin(...)),
+ *               rope_rows > NS + S + n_tokens
+ *   ema_w_cache [n_tokens] float32: weight of query row q for cached slots,
+ *               (1-beta)*beta^(n_tokens-1-q)            (cascade_attention.py:315-317)
+ *   ema_w_new   [n_tokens] cache dtype: weight at distance j = q - i for new tokens,
+ *               (1-beta)*beta^j                         (cascade_attention.py:269-282)
+ *               (both may be NULL under CKV_ADMIT_STRIDE)
+ *   out         [B, H, n_tokens, D]    element strides for b/h/t
+ *   workspace   at least ckv_attention_workspace_bytes(cfg, n_tokens) bytes, 256-byte aligned
+ */
+int ckv_attention(const ckv_config *cfg, const ckv_layer_state *st,
+                  const void *q, int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_t,
+                  const void *key, const void *value,
+                  int64_t kv_stride_b, int64_t kv_stride_h, int64_t kv_stride_t,
+                  int32_t n_tokens,
+                  const void *rope, int64_t rope_rows,
+                  const float *ema_w_cache, const void *ema_w_new,
+                  void *out, int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_t,
+                  void *workspace, size_t workspace_bytes,
+                  int32_t flags, void *cuda_stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CASCADE_KV_B200_H */

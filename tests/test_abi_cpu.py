@@ -1,0 +1,56 @@
+"""CPU-side checks of the shipped package: the C-ABI library loads and exports every declared
+symbol, and the host mirror validates its arguments.  No compute calls."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    from cascading_kv_cache_b200 import _lib
+    from cascading_kv_cache_b200.build import build
+    build()
+    header = open(os.path.join(ROOT, "include", "cascade_kv_b200.h")).read()
+    declared = set(re.findall(r"\b(ckv_[a-z_0-9]+)\s*\(", header))
+    assert declared == set(_lib.EXPORTS)
+    lib = ctypes.CDLL(_lib.LIB_PATH)
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert _lib.load().ckv_abi_version() == 1
+
+
+def test_struct_layout_matches_header():
+    from cascading_kv_cache_b200 import _lib
+    assert ctypes.sizeof(_lib.CkvConfig) == 12 * 4 + 8
+    assert ctypes.sizeof(_lib.CkvLayerState) == 15 * 8
+
+
+def test_argument_errors_do_not_need_a_gpu():
+    from cascading_kv_cache_b200 import _lib
+    lib = _lib.load()
+    cfg = _lib.CkvConfig(batch=1, kv_heads=3, q_heads=4, head_dim=8, num_sinks=1, window=4, cascades=2, dtype=0)
+    assert lib.ckv_attention_workspace_bytes(ctypes.byref(cfg), 4) == 0  # q_heads not a multiple of kv_heads
+    st = _lib.CkvLayerState()
+    rc = lib.ckv_cascade_update(ctypes.byref(cfg), ctypes.byref(st), None, None, 0, 0, 0, None, 0, 0, 0, 1, None)
+    assert rc == -1 and b"multiple" in lib.ckv_last_error()
+    cfg.q_heads = 6
+    assert lib.ckv_attention_workspace_bytes(ctypes.byref(cfg), 4) > 0
+    rc = lib.ckv_cascade_update(ctypes.byref(cfg), ctypes.byref(st), None, None, 0, 0, 0, None, 0, 0, 0, 1, None)
+    assert rc == -1 and b"null" in lib.ckv_last_error()
+
+
+def test_cache_refuses_cpu_device_and_bad_configs():
+    from cascading_kv_cache_b200 import CascadingKVCache, cascade_every_n
+    with pytest.raises(RuntimeError):
+        CascadingKVCache(8, 4, 1, 2, 16, 32, device="cpu", dtype=torch.float32, layers=1)
+    with pytest.raises(ValueError):
+        CascadingKVCache(7, 4, 1, 2, 16, 32, device="cuda", dtype=torch.float32, layers=1)
+    with pytest.raises(ValueError):
+        CascadingKVCache(8, 4, 1, 2, 16, [32], device="cuda", dtype=torch.float32, layers=1)
+    with pytest.raises(ValueError):
+        CascadingKVCache(8, 4, 1, 2, 16, 32, device="cuda", dtype=torch.float32, layers=1, cascade_func="nope")
+    assert cascade_every_n("pow2", 4) == [1, 2, 4, 8]

@@ -1,0 +1,138 @@
+"""Cache update through the C ABI on the GPU against the CPU oracle: bit-exact."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle.cascade_oracle import OracleCascadingKVCache
+from tests.test_oracle import UPDATE
+
+pytestmark = pytest.mark.gpu
+
+
+def assert_same_state(cache, ref, layer=0):
+    l = layer
+    valid = ~ref.mask[l]
+    assert torch.equal(cache.mask[l].cpu(), ref.mask[l])
+    assert torch.equal(cache.sink_mask[l].cpu(), ref.sink_mask[l])
+    assert torch.equal(cache.stored_tokens[l].cpu(), ref.stored_tokens[l])
+    assert torch.equal(cache.start_indices[l].cpu(), ref.start_indices[l])
+    assert torch.equal(cache.stored_sinks[l].cpu(), ref.stored_sinks[l])
+    assert torch.equal(cache.pos[l].cpu()[valid], ref.pos[l][valid])
+    assert torch.equal(cache.og_pos[l].cpu()[valid], ref.og_pos[l][valid])
+    svalid = ~ref.sink_mask[l]
+    assert torch.equal(cache.sink_pos[l].cpu()[svalid], ref.sink_pos[l][svalid])
+    # raw bits, so that -0.0 / NaN payloads would also be caught
+    bits = lambda t: t.cpu().contiguous().view(torch.int16 if t.element_size() == 2 else torch.int32)
+    assert torch.equal(bits(cache.key_cache[l])[valid], bits(ref.key_cache[l])[valid])
+    assert torch.equal(bits(cache.value_cache[l])[valid], bits(ref.value_cache[l])[valid])
+    assert torch.equal(bits(cache.score_cache[l])[valid], bits(ref.score_cache[l])[valid])
+    assert torch.equal(bits(cache.sink_keys[l])[svalid], bits(ref.sink_keys[l])[svalid])
+    assert torch.equal(bits(cache.sink_values[l])[svalid], bits(ref.sink_values[l])[svalid])
+    assert cache.seen_tokens_by_layer[l].item() == ref.seen_tokens_by_layer[l] == cache.seen_tokens_host(l)
+
+
+def make_pair(W, C, NS, B, H, D, dtype, eager_fill, cascade_func="pow2"):
+    from cascading_kv_cache_b200 import CascadingKVCache
+    cache = CascadingKVCache(W, NS, B, H, D, W * C, device="cuda:0", dtype=dtype, cascade_func=cascade_func,
+                             layers=1, eager_fill=eager_fill)
+    ref = OracleCascadingKVCache(W, NS, B, H, D, W * C, dtype=dtype, cascade_func=cascade_func, layers=1,
+                                 eager_fill=eager_fill)
+    return cache, ref
+
+
+@pytest.mark.parametrize("name", sorted(UPDATE))
+def test_golden_stride_streams(name):
+    """The reference CascadingKVCacheSlow vectors, fed in ragged chunks."""
+    st = UPDATE[name]
+    W, C, NS, N, B, H, D = (int(x) for x in st["cfg"])
+    D4 = 4  # rows must be multiples of 16 bytes: widen D=1 fixtures by repetition
+    k = torch.from_numpy(st["k"]).float()
+    v = torch.from_numpy(st["v"]).float()
+    if D < D4:
+        k, v = k.repeat(1, 1, 1, D4), v.repeat(1, 1, 1, D4)
+        D = D4
+    cache, ref = make_pair(W, C, NS, B, H, D, torch.float32, False)
+    rng = np.random.default_rng(N)
+    cuts = sorted({0, N, *rng.integers(0, N + 1, size=5).tolist()})
+    for a, b in zip(cuts[:-1], cuts[1:]):
+        cache.update(k[:, :, a:b].cuda(), v[:, :, a:b].cuda(), 0)
+        ref.update(k[:, :, a:b], v[:, :, a:b], 0)
+        assert_same_state(cache, ref)
+    # and against the reference's own dump
+    valid = st["valid"]
+    got_k = cache.key_cache[0].cpu().numpy()
+    assert np.array_equal(got_k[:, :, valid, :st["key_cache"].shape[-1]], st["key_cache"][:, :, valid])
+    shift = NS if N > NS else 0
+    assert np.array_equal((cache.pos[0][0, 0].cpu().numpy() + shift)[valid], st["pos"][valid])
+
+
+CASES = [
+    # W, C, NS, B, H, D, dtype, eager_fill, func, n_tokens, chunk
+    (4, 4, 2, 1, 2, 8, torch.float32, False, "pow2", 300, 1),
+    (4, 4, 2, 2, 2, 8, torch.float32, True, "pow2", 300, 7),
+    (8, 4, 4, 2, 3, 16, torch.bfloat16, True, "pow2", 700, 64),
+    (8, 4, 4, 2, 3, 16, torch.float16, False, "iplus1", 500, 33),
+    (16, 3, 1, 1, 2, 128, torch.bfloat16, True, "pow3", 900, 100),
+    (16, 4, 64, 1, 4, 128, torch.float16, False, "pow2", 1000, 1000),
+    (32, 4, 4, 2, 2, 64, torch.bfloat16, False, "1-then-2", 1200, 31),
+    (8, 8, 3, 1, 2, 32, torch.bfloat16, True, "pow2-1-4", 1500, 50),
+    (8, 4, 0, 1, 2, 32, torch.float32, True, "pow4", 400, 9),
+    (512, 4, 4, 1, 8, 128, torch.float32, False, "pow2", 5000, 512),
+]
+
+
+@pytest.mark.parametrize("case", CASES, ids=lambda c: f"W{c[0]}C{c[1]}NS{c[2]}-{str(c[6])[6:]}-{c[8]}-k{c[10]}")
+@pytest.mark.parametrize("rule", ["stride", "ema"])
+def test_update_matches_oracle(case, rule):
+    """Random streams; under 'ema' every token arrives with a random score and the score cache is
+    perturbed between calls as the attention would, so the score-driven branch is exercised."""
+    W, C, NS, B, H, D, dtype, eager_fill, func, N, chunk = case
+    g = torch.Generator().manual_seed(W * 1000 + C * 100 + NS + N)
+    cache, ref = make_pair(W, C, NS, B, H, D, dtype, eager_fill, func)
+    done = 0
+    while done < N:
+        n = min(chunk, N - done)
+        k = torch.randn(B, H, n, D, generator=g).to(dtype)
+        v = torch.randn(B, H, n, D, generator=g).to(dtype)
+        s = None
+        if rule == "ema":
+            # few distinct values so that ties (>=) are frequent
+            s = (torch.randint(0, 6, (B, H + 1, n), generator=g).float() / 8).to(dtype)
+            bump = (torch.randint(0, 3, (B, H, W * C), generator=g).float() / 8).to(dtype)
+            ref.score_cache[0] = (ref.score_cache[0] + bump).to(dtype)
+            cache.score_cache[0] = (cache.score_cache[0] + bump.cuda()).to(dtype)
+        # strided input views, as the projections produce them
+        kk = k.transpose(1, 2).contiguous().cuda().transpose(1, 2)
+        vv = v.transpose(1, 2).contiguous().cuda().transpose(1, 2)
+        cache.update(kk, vv, 0, score_states=None if s is None else s.cuda())
+        ref.update(k, v, 0, score_states=s)
+        done += n
+        if done % (chunk * 4) == 0 or done == N:
+            assert_same_state(cache, ref)
+    assert_same_state(cache, ref)
+
+
+def test_reset_and_reuse():
+    cache, ref = make_pair(8, 2, 2, 1, 2, 8, torch.float32, True)
+    k = torch.randn(1, 2, 50, 8)
+    cache.update(k.cuda(), k.cuda(), 0)
+    cache.reset()
+    assert cache.mask[0].all() and cache.get_seq_length(0) == 0 and cache.seen_tokens_host(0) == 0
+    cache.update(k.cuda(), k.cuda(), 0)
+    ref.update(k, k, 0)
+    assert_same_state(cache, ref)
+    assert cache.get_seq_length(0) == 2 + 16
+
+
+def test_update_rejects_bad_shapes():
+    cache, _ = make_pair(8, 2, 2, 1, 2, 8, torch.float32, True)
+    with pytest.raises(ValueError):
+        cache.update(torch.zeros(1, 3, 4, 8).cuda(), torch.zeros(1, 3, 4, 8).cuda(), 0)
+    with pytest.raises(ValueError):
+        cache.update(torch.zeros(1, 2, 4, 8).cuda(), torch.zeros(1, 2, 4, 8).cuda(), 0,
+                     score_states=torch.zeros(1, 1, 4).cuda())
+    # empty chunk is a no-op
+    cache.update(torch.zeros(1, 2, 0, 8).cuda(), torch.zeros(1, 2, 0, 8).cuda(), 0)
+    assert cache.seen_tokens_host(0) == 0
