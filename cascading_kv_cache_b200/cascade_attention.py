@@ -72,8 +72,8 @@ def cascade_attention(
     cfg = cache.ckv_config(layer_idx, q_heads=H, homogeneous_heads=homogeneous_heads, head_reduction=head_reduction)
     st = cache.ckv_state(layer_idx)
     nbytes = lib.ckv_attention_workspace_bytes(ctypes.byref(cfg), K)
-    ws = cache.workspace(nbytes)
-    ws_ptr = (ws.data_ptr() + 255) & ~255
+    cache.workspace(nbytes)
+    ws_ptr = cache.workspace_ptr()
     rope = cache.rope_table(rope_theta, cache.num_sink_tokens + cache.max_seq_len[layer_idx] + K + 1)
     if cache.admission == "ema" and update:
         w_cache, w_new = cache.ema_weights(K)

@@ -242,6 +242,18 @@ class CascadingKVCache(Cache):
             self._workspace = torch.empty(nbytes + 256, device=self.device, dtype=torch.uint8)
         return self._workspace
 
+    def workspace_ptr(self) -> int:
+        return (self._workspace.data_ptr() + 255) & ~255
+
+    def kernel_status(self) -> int:
+        """Status word of the last attention call (synchronises): 0 unless a bounded wait inside a
+        kernel ran out, in which case that call's results are invalid."""
+        if self._workspace is None:
+            return 0
+        status = ctypes.c_int32(0)
+        _lib.check(self._lib.ckv_read_status(self.workspace_ptr(), ctypes.byref(status)), "ckv_read_status")
+        return int(status.value)
+
     def rope_table(self, theta: float, rows: int) -> torch.Tensor:
         """[rows, D] table in the cache dtype: cos | sin of position * inv_freq, computed like
         LlamaRotaryEmbedding.forward (fp32 angles, fp32 cos/sin, cast)."""

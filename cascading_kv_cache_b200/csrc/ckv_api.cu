@@ -2,6 +2,9 @@
 #include <stdarg.h>
 #include <stdio.h>
 
+#include <utility>
+#include <vector>
+
 #include "ckv_common.cuh"
 
 namespace ckv {
@@ -15,6 +18,35 @@ int fail(int code, const char *fmt, ...) {
     va_end(ap);
     return code;
 }
+
+// ---- profiling hook: library-owned CUDA events around the dominant kernel of each call ----------
+static bool g_profile_on = false;
+static std::vector<std::pair<cudaEvent_t, cudaEvent_t>> g_events;
+static size_t g_events_used = 0;
+static const char *g_kernel_name = "";
+static ProfileHook g_hook;
+static thread_local int g_launches = 0;
+
+void ProfileHook::before(cudaStream_t stream, const char *kernel_name) {
+    g_kernel_name = kernel_name;
+    if (g_events_used == g_events.size()) {
+        cudaEvent_t a, b;
+        if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) return;
+        g_events.emplace_back(a, b);
+    }
+    cudaEventRecord(g_events[g_events_used].first, stream);
+}
+
+void ProfileHook::after(cudaStream_t stream) {
+    if (g_events_used < g_events.size()) {
+        cudaEventRecord(g_events[g_events_used].second, stream);
+        g_events_used += 1;
+    }
+}
+
+ProfileHook *active_profile_hook() { return g_profile_on ? &g_hook : nullptr; }
+
+void note_launches(int n) { g_launches += n; }
 
 static int check_state(const ckv_layer_state *st) {
     if (!st) return fail(CKV_E_ARG, "layer state is null");
@@ -45,6 +77,7 @@ extern "C" int ckv_cascade_update(const ckv_config *cfg, const ckv_layer_state *
     if (n_tokens < 1) return fail(CKV_E_ARG, "n_tokens must be at least 1, got %d", n_tokens);
     if (d.NS > 0 && (!st->sink_keys || !st->sink_values || !st->sink_mask || !st->sink_pos))
         return fail(CKV_E_ARG, "sink buffers are null");
+    g_launches = 0;
     return launch_update_serial(d, st, key, value, kv_stride_b, kv_stride_h, kv_stride_t, scores, s_stride_b,
                                 s_stride_h, s_stride_t, n_tokens, (cudaStream_t)cuda_stream);
 }
@@ -52,7 +85,48 @@ extern "C" int ckv_cascade_update(const ckv_config *cfg, const ckv_layer_state *
 extern "C" size_t ckv_attention_workspace_bytes(const ckv_config *cfg, int32_t n_tokens) {
     Dims d;
     if (make_dims(cfg, &d) != CKV_OK || n_tokens < 1) return 0;
-    return generic_workspace_bytes(d, n_tokens);
+    size_t n = generic_workspace_bytes(d, n_tokens);
+    if (decode_tuned_supported(d, n_tokens)) {
+        const size_t t = decode_workspace_bytes(d);
+        n = t > n ? t : n;
+    }
+    return n;
+}
+
+extern "C" int ckv_last_launch_count(void) { return g_launches; }
+
+extern "C" int ckv_profile_enable(int enable) {
+    g_profile_on = enable != 0;
+    g_events_used = 0;
+    if (!g_profile_on) {
+        for (auto &e : g_events) {
+            cudaEventDestroy(e.first);
+            cudaEventDestroy(e.second);
+        }
+        g_events.clear();
+    }
+    return CKV_OK;
+}
+
+extern "C" int ckv_profile_read(double *total_ms, int32_t *launches, const char **kernel_name) {
+    double total = 0.0;
+    for (size_t i = 0; i < g_events_used; ++i) {
+        CKV_CUDA_CHECK(cudaEventSynchronize(g_events[i].second));
+        float ms = 0.f;
+        CKV_CUDA_CHECK(cudaEventElapsedTime(&ms, g_events[i].first, g_events[i].second));
+        total += ms;
+    }
+    if (total_ms) *total_ms = total;
+    if (launches) *launches = (int32_t)g_events_used;
+    if (kernel_name) *kernel_name = g_kernel_name;
+    g_events_used = 0;
+    return CKV_OK;
+}
+
+extern "C" int ckv_read_status(const void *workspace, int32_t *status) {
+    if (!workspace || !status) return fail(CKV_E_ARG, "workspace/status is null");
+    CKV_CUDA_CHECK(cudaMemcpy(status, workspace, 4, cudaMemcpyDeviceToHost));
+    return CKV_OK;
 }
 
 extern "C" int ckv_attention(const ckv_config *cfg, const ckv_layer_state *st, const void *q, int64_t q_stride_b,
@@ -69,6 +143,11 @@ extern "C" int ckv_attention(const ckv_config *cfg, const ckv_layer_state *st, c
     if (!q || !key || !value || !out || !rope) return fail(CKV_E_ARG, "q/key/value/out/rope is null");
     if (n_tokens < 1) return fail(CKV_E_ARG, "n_tokens must be at least 1, got %d", n_tokens);
     if (d.NS < 1) return fail(CKV_E_UNSUPPORTED, "attention needs at least one sink token");
+    g_launches = 0;
+    if (!(flags & CKV_ATTN_FORCE_GENERIC) && decode_tuned_supported(d, n_tokens))
+        return launch_decode_tuned(d, st, q, q_stride_b, q_stride_h, key, value, kv_stride_b, kv_stride_h, rope,
+                                   rope_rows, ema_w_cache, ema_w_new, out, o_stride_b, o_stride_h, workspace,
+                                   workspace_bytes, flags, (cudaStream_t)cuda_stream, active_profile_hook());
     return launch_attention_generic(d, st, q, q_stride_b, q_stride_h, q_stride_t, key, value, kv_stride_b,
                                     kv_stride_h, kv_stride_t, n_tokens, rope, rope_rows, ema_w_cache, ema_w_new, out,
                                     o_stride_b, o_stride_h, o_stride_t, workspace, workspace_bytes, flags,

@@ -319,7 +319,10 @@ int run_generic(const Dims &d, GenericParams &p, bool ema, cudaStream_t stream) 
     rope_gather_kernel<T><<<blocks, 256, 0, stream>>>(p);
     CKV_CUDA_CHECK(cudaGetLastError());
     const long long n_rows = (long long)d.B * d.H * p.K;
+    ProfileHook *hook = active_profile_hook();
+    if (hook) hook->before(stream, "attn_rows_kernel");
     attn_rows_kernel<T><<<(unsigned)((n_rows + 3) / 4), 128, 0, stream>>>(p);
+    if (hook) hook->after(stream);
     CKV_CUDA_CHECK(cudaGetLastError());
     if (ema) {
         const long long n_cols = (long long)d.B * d.H * (d.S + p.K);
@@ -329,6 +332,7 @@ int run_generic(const Dims &d, GenericParams &p, bool ema, cudaStream_t stream) 
         reduce_ema_kernel<T><<<(unsigned)((n_red + 127) / 128), 128, 0, stream>>>(p);
         CKV_CUDA_CHECK(cudaGetLastError());
     }
+    note_launches(ema ? 4 : 2);
     return CKV_OK;
 }
 

@@ -98,4 +98,20 @@ int launch_attention_generic(const Dims &d, const ckv_layer_state *st, const voi
                              const void *ema_w_new, void *out, int64_t osb, int64_t osh, int64_t ost, void *workspace,
                              size_t workspace_bytes, int flags, cudaStream_t stream);
 
+// Optional CUDA-event timing of the dominant kernel of a call (see ckv_profile_enable).
+struct ProfileHook {
+    void before(cudaStream_t stream, const char *kernel_name);
+    void after(cudaStream_t stream);
+};
+ProfileHook *active_profile_hook();  // null when profiling is off
+void note_launches(int n);           // kernels launched by the current call
+
+bool decode_tuned_supported(const Dims &d, int n_tokens);
+size_t decode_workspace_bytes(const Dims &d);
+int launch_decode_tuned(const Dims &d, const ckv_layer_state *st, const void *q, int64_t qsb, int64_t qsh,
+                        const void *key, const void *value, int64_t ksb, int64_t ksh, const void *rope,
+                        int64_t rope_rows, const float *ema_w_cache, const void *ema_w_new, void *out, int64_t osb,
+                        int64_t osh, void *workspace, size_t workspace_bytes, int flags, cudaStream_t stream,
+                        ProfileHook *hook);
+
 }  // namespace ckv

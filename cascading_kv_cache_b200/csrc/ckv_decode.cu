@@ -1,0 +1,827 @@
+// Single-token decode over the cascading cache for 16-bit caches with head_dim 128.
+//
+// Kernel 1, decode_stream_kernel (HBM-bound, persistent, one CTA per SM):
+//   The valid keys of all lanes form one flat stream of 64-key tiles; every CTA takes a
+//   contiguous range of that stream (a split of the key dimension that ignores lane borders, so
+//   all SMs stream the same number of bytes).  A producer warp moves each tile into a 4-stage
+//   shared-memory ring: K and V through TMA (cp.async.bulk.tensor, 128-byte swizzle) and the
+//   cos/sin rows of the tile's cache positions through 16-byte cp.async gathers, all completing
+//   on one mbarrier per stage.  Four consumer warps each own 16 keys of a tile: ldmatrix K and
+//   cos/sin fragments, RoPE in packed 16-bit arithmetic on the fragments (the same rounding
+//   points as the reference: cascade_attention.py:31-35, :284-291), QK^T and PV on mma.sync
+//   m16n8k16 with the GQA group as the M dimension, online softmax per warp.  It writes one
+//   (max, sum, out[G][128]) partial per (CTA, lane, warp) and, under the EMA rule, the logits of
+//   every cached slot in the cache dtype (the rounding point of the reference's einsum output).
+//
+// Kernel 2, decode_finish_kernel: merges the partials with the new token's own logit, writes the
+//   output, turns logits into probabilities, reduces them over the GQA group, applies
+//   score_cache = beta*score_cache + ema (cascade_attention.py:315-330), then the last block of
+//   each lane inserts the new token (the cascade update state machine) and the last block of all
+//   advances the lane-invariant counters.  No host synchronisation anywhere.
+#include <cuda.h>
+
+#include "ckv_common.cuh"
+#include "ckv_update_device.cuh"
+
+namespace ckv {
+
+namespace {
+
+constexpr int kTile = 64;                       // keys per stage
+constexpr int kStages = 4;
+constexpr int kComputeWarps = 4;
+constexpr int kStreamThreads = (kComputeWarps + 1) * 32;
+constexpr int kSubBytes = kTile * 128;          // one swizzled 64-row x 128-byte sub-tile
+constexpr int kStageBytes = 6 * kSubBytes;      // K lo | K hi | V lo | V hi | cos | sin
+constexpr int kOffK = 0, kOffV = 2 * kSubBytes, kOffCos = 4 * kSubBytes, kOffSin = 5 * kSubBytes;
+constexpr int kStreamSmem = kStages * kStageBytes + 1024 + 256;
+constexpr int kPartialStride = 130;             // m, l, out[128] per head row
+constexpr int kMaxG = 16;
+constexpr unsigned kSpinLimit = 1u << 24;       // bounded mbarrier waits (each probe also sleeps)
+constexpr int kFinishThreads = 256;
+
+struct DecodeParams {
+    const void *q;
+    long long qsb, qsh;                          // elements
+    const void *knew, *vnew;
+    long long ksb, ksh;                          // elements
+    void *out;
+    long long osb, osh;
+    const void *rope;
+    long long rope_rows;
+    const float *ema_w_cache;                    // [1]
+    const void *ema_w_new;                       // [1]
+    // state
+    void *score_cache;
+    long long *pos, *sink_pos, *stored_tokens, *start_indices, *stored_sinks, *seen;
+    const long long *every_n;
+    uint8_t *mask, *sink_mask;
+    // scratch
+    int *status;                                 // [0] error flag
+    unsigned int *sync;                          // [0] lanes done, [1 + lane] blocks done
+    void *logits;                                // [B*H][S]
+    float *partials;                             // [(grid + lanes)][warps][G][130]
+    void *new_scores;                            // [B*KVH]
+    int B, KVH, H, G, NS, W, C, S;
+    int ema, update, head_reduction, eager_fill, dtype;
+    int stream_grid, finish_chunks;
+    float rs, beta_pow;
+    UpdateParams upd;                            // the one-token cache update of the finish kernel
+};
+
+// ---------------------------------------------------------------------------------- PTX helpers
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after kSpinLimit probes, raises the status flag and reports failure so
+// that the caller leaves its loop instead of hanging the GPU.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, unsigned parity, int *status) {
+    for (unsigned n = 0; n < kSpinLimit; ++n) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (n > 64) __nanosleep(64);
+        if ((n & 1023) == 1023 && *((volatile int *)status) != 0) return false;
+    }
+    atomicExch(status, 1);
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *tm, int x, int y, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(tm), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void cp_async_16(void *dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_arrive_noinc(uint64_t *bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+
+template <typename T> struct Mma;
+template <> struct Mma<__nv_bfloat16> {
+    static __device__ __forceinline__ void run(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    }
+};
+template <> struct Mma<__half> {
+    static __device__ __forceinline__ void run(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    }
+};
+
+// ---- packed 16-bit arithmetic with one rounding per operation ---------------------------------
+template <typename T> struct Pack;
+template <> struct Pack<__nv_bfloat16> {
+    using T2 = __nv_bfloat162;
+    static __device__ __forceinline__ T2 from_u(uint32_t u) { return *reinterpret_cast<T2 *>(&u); }
+    static __device__ __forceinline__ uint32_t to_u(T2 v) { return *reinterpret_cast<uint32_t *>(&v); }
+    static __device__ __forceinline__ float2 to_f2(T2 v) { return __bfloat1622float2(v); }
+    static __device__ __forceinline__ T2 from_f2(float2 f) { return __float22bfloat162_rn(f); }
+};
+template <> struct Pack<__half> {
+    using T2 = __half2;
+    static __device__ __forceinline__ T2 from_u(uint32_t u) { return *reinterpret_cast<T2 *>(&u); }
+    static __device__ __forceinline__ uint32_t to_u(T2 v) { return *reinterpret_cast<uint32_t *>(&v); }
+    static __device__ __forceinline__ float2 to_f2(T2 v) { return __half22float2(v); }
+    static __device__ __forceinline__ T2 from_f2(float2 f) { return __float22half2_rn(f); }
+};
+
+// (lo, hi) are the element pairs at dims d and d+64.  out = x*cos + rotate_half(x)*sin with each
+// product and the sum rounded to T, then times sqrt(scale) in fp32 rounded to T.
+template <typename T>
+__device__ __forceinline__ void rope_pair(uint32_t &lo, uint32_t &hi, uint32_t c, uint32_t s, float rs) {
+    using P = Pack<T>;
+    const typename P::T2 l = P::from_u(lo), h = P::from_u(hi), cc = P::from_u(c), ss = P::from_u(s);
+    const typename P::T2 nl = __hsub2(__hmul2(l, cc), __hmul2(h, ss));
+    const typename P::T2 nh = __hadd2(__hmul2(h, cc), __hmul2(l, ss));
+    float2 fl = P::to_f2(nl), fh = P::to_f2(nh);
+    fl.x *= rs; fl.y *= rs; fh.x *= rs; fh.y *= rs;
+    lo = P::to_u(P::from_f2(fl));
+    hi = P::to_u(P::from_f2(fh));
+}
+
+struct Schedule {
+    long long seen, sinks, total, shift, max_pos;
+    int n_sink_tiles, n_cache_tiles, tiles_per_lane;
+    long long n_tiles;
+};
+
+__device__ __forceinline__ Schedule make_schedule(const DecodeParams &p) {
+    Schedule s;
+    s.seen = *p.seen;
+    s.sinks = *p.stored_sinks;
+    s.total = 0;
+    for (int i = 0; i < p.C; ++i) s.total += p.stored_tokens[i];
+    s.shift = s.seen > p.NS ? p.NS : 0;
+    s.max_pos = s.seen == 0 ? 0 : (s.seen <= p.NS ? s.seen : p.NS + s.total);
+    s.n_sink_tiles = (int)((s.sinks + kTile - 1) / kTile);
+    s.n_cache_tiles = (int)((s.total + kTile - 1) / kTile);
+    s.tiles_per_lane = s.n_sink_tiles + s.n_cache_tiles;
+    s.n_tiles = (long long)s.tiles_per_lane * p.B * p.KVH;
+    return s;
+}
+
+__device__ __forceinline__ long long cta_first_tile(long long cta, long long n_tiles, int grid) {
+    return (cta * n_tiles) / grid;
+}
+
+// ------------------------------------------------------------------------------ stream kernel
+template <typename T>
+__global__ void __launch_bounds__(kStreamThreads, 1)
+decode_stream_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                     const __grid_constant__ CUtensorMap tmSK, const __grid_constant__ CUtensorMap tmSV,
+                     DecodeParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + kStages * kStageBytes);
+    uint64_t *empty = full + kStages;
+    const int warp = threadIdx.x >> 5, lane_id = threadIdx.x & 31;
+    const Schedule sc = make_schedule(p);
+    const long long t_begin = cta_first_tile(blockIdx.x, sc.n_tiles, gridDim.x);
+    const long long t_end = cta_first_tile(blockIdx.x + 1, sc.n_tiles, gridDim.x);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&full[s], 33);   // 32 cp.async arrivals + the expect_tx arrival
+            mbar_init(&empty[s], kComputeWarps);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (blockIdx.x == 0) {
+        const int n = 1 + p.B * p.KVH;
+        for (int i = threadIdx.x; i < n; i += blockDim.x) p.sync[i] = 0;
+    }
+    __syncthreads();
+
+    if (warp == kComputeWarps) {
+        // ------------------------------------------------------------------ producer warp
+        const uint8_t *rope = reinterpret_cast<const uint8_t *>(p.rope);
+        int it = 0;
+        for (long long t = t_begin; t < t_end; ++t, ++it) {
+            const int s = it % kStages;
+            if (it >= kStages) {
+                if (!mbar_wait(&empty[s], ((it / kStages) & 1) ^ 1, p.status)) break;
+            }
+            const int lane = (int)(t / sc.tiles_per_lane);
+            const int ti = (int)(t % sc.tiles_per_lane);
+            uint8_t *stage = smem + s * kStageBytes;
+            const bool sink_tile = ti < sc.n_sink_tiles;
+            const int row0 = sink_tile ? ti * kTile : (ti - sc.n_sink_tiles) * kTile;
+            if (lane_id == 0) {
+                mbar_expect_tx(&full[s], 4 * kSubBytes);
+                const int y = sink_tile ? lane * p.NS + row0 : lane * p.S + row0;
+                const CUtensorMap *mk = sink_tile ? &tmSK : &tmK;
+                const CUtensorMap *mv = sink_tile ? &tmSV : &tmV;
+                tma_load_2d(stage + kOffK, mk, 0, y, &full[s]);
+                tma_load_2d(stage + kOffK + kSubBytes, mk, 64, y, &full[s]);
+                tma_load_2d(stage + kOffV, mv, 0, y, &full[s]);
+                tma_load_2d(stage + kOffV + kSubBytes, mv, 64, y, &full[s]);
+            }
+            // cos|sin rows of the tile's positions: 64 rows x 16 chunks of 16 bytes
+#pragma unroll 4
+            for (int i = 0; i < 32; ++i) {
+                const int qd = i * 32 + lane_id;
+                const int r = qd >> 4, c = qd & 15;
+                const int idx = row0 + r;
+                long long pos;
+                if (sink_tile) pos = idx < sc.sinks ? p.sink_pos[idx] : 0;
+                else pos = idx < sc.total ? p.pos[idx] + sc.shift : 0;
+                pos = pos < 0 ? 0 : (pos >= p.rope_rows ? p.rope_rows - 1 : pos);
+                const uint8_t *src = rope + pos * 256 + c * 16;
+                uint8_t *dst = stage + (c < 8 ? kOffCos : kOffSin) + r * 128 + (((c & 7) ^ (r & 7)) << 4);
+                cp_async_16(dst, src);
+            }
+            cp_async_arrive_noinc(&full[s]);
+        }
+        asm volatile("cp.async.wait_all;" ::: "memory");
+    } else {
+        // ----------------------------------------------------------------- consumer warps
+        const int g = lane_id >> 2, tq = lane_id & 3;
+        const T *rope = reinterpret_cast<const T *>(p.rope);
+        uint32_t qa[8][4];
+        float o[16][4];
+        float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+        int cur_lane = -1;
+        T *logits = reinterpret_cast<T *>(p.logits);
+
+        auto flush = [&](int lane) {
+            // quad-reduce the row sums, then write this warp's partial of (CTA, lane)
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+                l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+            }
+            float *base = p.partials + ((long long)(blockIdx.x + lane) * kComputeWarps + warp) * p.G * kPartialStride;
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const int row = g + 8 * r;
+                if (row < p.G) {
+                    float *pr = base + row * kPartialStride;
+                    if (tq == 0) {
+                        pr[0] = m_run[r];
+                        pr[1] = l_run[r];
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        *reinterpret_cast<float2 *>(pr + 2 + 8 * j + 2 * tq) = make_float2(o[j][2 * r], o[j][2 * r + 1]);
+                }
+            }
+        };
+
+        int it = 0;
+        for (long long t = t_begin; t < t_end; ++t, ++it) {
+            const int s = it % kStages;
+            const int lane = (int)(t / sc.tiles_per_lane);
+            const int ti = (int)(t % sc.tiles_per_lane);
+            if (lane != cur_lane) {
+                if (cur_lane >= 0) flush(cur_lane);
+                cur_lane = lane;
+                m_run[0] = m_run[1] = -INFINITY;
+                l_run[0] = l_run[1] = 0.f;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+                // A fragments of q (rows = heads of the group), rotated at max_pos and scaled
+                const int b = lane / p.KVH, kvh = lane % p.KVH;
+                const T *crow = rope + (sc.max_pos < p.rope_rows ? sc.max_pos : p.rope_rows - 1) * 128;
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    const int row = g + 8 * r;
+                    if (row < p.G) {
+                        const T *qrow = reinterpret_cast<const T *>(p.q) + b * p.qsb + (long long)(kvh * p.G + row) * p.qsh;
+#pragma unroll
+                        for (int ks = 0; ks < 4; ++ks) {
+#pragma unroll
+                            for (int hf = 0; hf < 2; ++hf) {
+                                const int d = 16 * ks + 8 * hf + 2 * tq;
+                                uint32_t lo = *reinterpret_cast<const uint32_t *>(qrow + d);
+                                uint32_t hi = *reinterpret_cast<const uint32_t *>(qrow + d + 64);
+                                const uint32_t c = *reinterpret_cast<const uint32_t *>(crow + d);
+                                const uint32_t sn = *reinterpret_cast<const uint32_t *>(crow + 64 + d);
+                                rope_pair<T>(lo, hi, c, sn, p.rs);
+                                qa[ks][r + 2 * hf] = lo;
+                                qa[ks + 4][r + 2 * hf] = hi;
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int ks = 0; ks < 8; ++ks) qa[ks][r] = qa[ks][r + 2] = 0u;
+                    }
+                }
+            }
+            if (!mbar_wait(&full[s], (it / kStages) & 1, p.status)) break;
+
+            const bool sink_tile = ti < sc.n_sink_tiles;
+            const int row0 = sink_tile ? ti * kTile : (ti - sc.n_sink_tiles) * kTile;
+            const long long limit = sink_tile ? sc.sinks : sc.total;
+            const int nvalid = (int)(limit - row0 < kTile ? limit - row0 : kTile);
+            const int key0 = 16 * warp;
+            if (key0 < nvalid) {
+                const uint32_t stage = smem_u32(smem + s * kStageBytes);
+                float sacc[2][4];
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) {
+                    sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f;
+                    const int krow = key0 + 8 * nt + (lane_id & 7);
+                    const uint32_t rowoff = krow * 128;
+                    const int sw = krow & 7;
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        // k-steps 2u, 2u+1 (dims < 64) with their partners 2u+4, 2u+5 (dims + 64)
+                        const uint32_t choff = (uint32_t)(((4 * u + (lane_id >> 3)) ^ sw) << 4);
+                        uint32_t kl[4], kh[4], cs[4], sn[4];
+                        ldsm_x4(stage + kOffK + rowoff + choff, kl[0], kl[1], kl[2], kl[3]);
+                        ldsm_x4(stage + kOffK + kSubBytes + rowoff + choff, kh[0], kh[1], kh[2], kh[3]);
+                        ldsm_x4(stage + kOffCos + rowoff + choff, cs[0], cs[1], cs[2], cs[3]);
+                        ldsm_x4(stage + kOffSin + rowoff + choff, sn[0], sn[1], sn[2], sn[3]);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) rope_pair<T>(kl[e], kh[e], cs[e], sn[e], p.rs);
+                        Mma<T>::run(sacc[nt], qa[2 * u], kl[0], kl[1]);
+                        Mma<T>::run(sacc[nt], qa[2 * u + 1], kl[2], kl[3]);
+                        Mma<T>::run(sacc[nt], qa[2 * u + 4], kh[0], kh[1]);
+                        Mma<T>::run(sacc[nt], qa[2 * u + 5], kh[2], kh[3]);
+                    }
+                }
+                // logits rounded to T (the reference's einsum output), masked past the valid keys
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int key = key0 + 8 * nt + 2 * tq + (e & 1);
+                        sacc[nt][e] = key < nvalid ? rnd<T>(sacc[nt][e]) : -INFINITY;
+                    }
+                }
+                if (p.ema && !sink_tile) {
+                    const int b = lane / p.KVH, kvh = lane % p.KVH;
+#pragma unroll
+                    for (int r = 0; r < 2; ++r) {
+                        const int row = g + 8 * r;
+                        if (row < p.G) {
+                            T *lrow = logits + ((long long)b * p.H + kvh * p.G + row) * p.S;
+#pragma unroll
+                            for (int nt = 0; nt < 2; ++nt) {
+                                const int slot = row0 + key0 + 8 * nt + 2 * tq;
+                                if (slot + 1 < p.S) {
+                                    typename Pack<T>::T2 v = Pack<T>::from_f2(make_float2(sacc[nt][2 * r], sacc[nt][2 * r + 1]));
+                                    *reinterpret_cast<typename Pack<T>::T2 *>(lrow + slot) = v;
+                                } else if (slot < p.S) {
+                                    lrow[slot] = Elem<T>::from_f(sacc[nt][2 * r]);
+                                }
+                            }
+                        }
+                    }
+                }
+                // online softmax for rows g and g+8 over this warp's 16 keys
+                uint32_t pa[4];
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    float mx = fmaxf(fmaxf(sacc[0][2 * r], sacc[0][2 * r + 1]), fmaxf(sacc[1][2 * r], sacc[1][2 * r + 1]));
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                    const float m_new = fmaxf(m_run[r], mx);
+                    float corr = 1.f, p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
+                    if (m_new != -INFINITY) {
+                        corr = __expf(m_run[r] - m_new);
+                        p0 = __expf(sacc[0][2 * r] - m_new);
+                        p1 = __expf(sacc[0][2 * r + 1] - m_new);
+                        p2 = __expf(sacc[1][2 * r] - m_new);
+                        p3 = __expf(sacc[1][2 * r + 1] - m_new);
+                    }
+                    m_run[r] = m_new;
+                    l_run[r] = l_run[r] * corr + (p0 + p1 + p2 + p3);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        o[j][2 * r] *= corr;
+                        o[j][2 * r + 1] *= corr;
+                    }
+                    pa[r] = Pack<T>::to_u(Pack<T>::from_f2(make_float2(p0, p1)));
+                    pa[r + 2] = Pack<T>::to_u(Pack<T>::from_f2(make_float2(p2, p3)));
+                }
+                // out += P (16 x 16 keys) * V (16 keys x 128)
+                {
+                    const int vrow = key0 + (lane_id & 7) + 8 * ((lane_id >> 3) & 1);
+                    const uint32_t rowoff = vrow * 128;
+                    const int sw = vrow & 7;
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+#pragma unroll
+                        for (int cp = 0; cp < 4; ++cp) {
+                            const uint32_t choff = (uint32_t)(((2 * cp + (lane_id >> 4)) ^ sw) << 4);
+                            uint32_t v0, v1, v2, v3;
+                            ldsm_x4_t(stage + kOffV + half * kSubBytes + rowoff + choff, v0, v1, v2, v3);
+                            Mma<T>::run(o[8 * half + 2 * cp], pa, v0, v1);
+                            Mma<T>::run(o[8 * half + 2 * cp + 1], pa, v2, v3);
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane_id == 0) mbar_arrive(&empty[s]);
+        }
+        if (cur_lane >= 0) flush(cur_lane);
+    }
+}
+
+// ------------------------------------------------------------------------------ finish kernel
+__device__ __forceinline__ float reduce_group(const float *v, int n, int how) {
+    if (how == CKV_REDUCE_MAX) {
+        float m = v[0];
+        for (int i = 1; i < n; ++i) m = fmaxf(m, v[i]);
+        return m;
+    }
+    if (how == CKV_REDUCE_MEAN) {
+        float s = 0.f;
+        for (int i = 0; i < n; ++i) s += v[i];
+        return s / (float)n;
+    }
+    const int want = (n - 1) / 2;  // lower median
+    for (int i = 0; i < n; ++i) {
+        int less = 0, eq = 0;
+        for (int j = 0; j < n; ++j) {
+            less += v[j] < v[i];
+            eq += v[j] == v[i];
+        }
+        if (less <= want && want < less + eq) return v[i];
+    }
+    return v[0];
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kFinishThreads) decode_finish_kernel(DecodeParams p) {
+    __shared__ float s_m[kMaxG], s_linv[kMaxG], s_snew[kMaxG], s_pnew[kMaxG];
+    __shared__ long long s_stored[CKV_MAX_CASCADES], s_start[CKV_MAX_CASCADES], s_every[CKV_MAX_CASCADES];
+    __shared__ long long s_new_stored[CKV_MAX_CASCADES], s_new_start[CKV_MAX_CASCADES];
+    __shared__ long long s_new_sinks, s_new_total;
+    __shared__ int s_is_last;
+    const int lane = blockIdx.y;
+    const int b = lane / p.KVH, kvh = lane % p.KVH;
+    const int tid = threadIdx.x, warp = tid >> 5, lane_id = tid & 31;
+    const Schedule sc = make_schedule(p);
+    const T *rope = reinterpret_cast<const T *>(p.rope);
+    const T *crow = rope + (sc.max_pos < p.rope_rows ? sc.max_pos : p.rope_rows - 1) * 128;
+    const T *krow = reinterpret_cast<const T *>(p.knew) + b * p.ksb + kvh * p.ksh;
+    const T *vrow = reinterpret_cast<const T *>(p.vnew) + b * p.ksb + kvh * p.ksh;
+
+    // 1. the new token's own logit per head: both operands rotated at max_pos and scaled
+    for (int gh = warp; gh < p.G; gh += kFinishThreads / 32) {
+        const T *qrow = reinterpret_cast<const T *>(p.q) + b * p.qsb + (long long)(kvh * p.G + gh) * p.qsh;
+        float part = 0.f;
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int i = lane_id + 32 * e;
+            const float c = Elem<T>::to_f(crow[i]), sn = Elem<T>::to_f(crow[64 + i]);
+            const float ql = Elem<T>::to_f(qrow[i]), qh = Elem<T>::to_f(qrow[i + 64]);
+            const float kl = Elem<T>::to_f(krow[i]), kh = Elem<T>::to_f(krow[i + 64]);
+            const float qrl = rnd<T>(__fmul_rn(rnd<T>(__fadd_rn(rnd<T>(__fmul_rn(ql, c)), rnd<T>(__fmul_rn(-qh, sn)))), p.rs));
+            const float qrh = rnd<T>(__fmul_rn(rnd<T>(__fadd_rn(rnd<T>(__fmul_rn(qh, c)), rnd<T>(__fmul_rn(ql, sn)))), p.rs));
+            const float krl = rnd<T>(__fmul_rn(rnd<T>(__fadd_rn(rnd<T>(__fmul_rn(kl, c)), rnd<T>(__fmul_rn(-kh, sn)))), p.rs));
+            const float krh = rnd<T>(__fmul_rn(rnd<T>(__fadd_rn(rnd<T>(__fmul_rn(kh, c)), rnd<T>(__fmul_rn(kl, sn)))), p.rs));
+            part = fmaf(qrl, krl, part);
+            part = fmaf(qrh, krh, part);
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
+        if (lane_id == 0) s_snew[gh] = rnd<T>(part);
+    }
+    __syncthreads();
+
+    // 2. merge the stream kernel's partials of this lane: CTAs whose tile range meets the lane's
+    const long long a_tile = (long long)lane * sc.tiles_per_lane, b_tile = a_tile + sc.tiles_per_lane;
+    int cta_lo = 0, cta_hi = -1;
+    if (sc.tiles_per_lane > 0) {
+        cta_lo = (int)((a_tile * p.stream_grid) / sc.n_tiles);
+        while (cta_lo > 0 && cta_first_tile(cta_lo, sc.n_tiles, p.stream_grid) > a_tile) --cta_lo;
+        while (cta_lo + 1 < p.stream_grid && cta_first_tile(cta_lo + 1, sc.n_tiles, p.stream_grid) <= a_tile) ++cta_lo;
+        cta_hi = cta_lo;
+        while (cta_hi + 1 < p.stream_grid && cta_first_tile(cta_hi + 1, sc.n_tiles, p.stream_grid) < b_tile) ++cta_hi;
+    }
+    // partial i of the lane: CTA cta_lo + i/warps, warp i%warps; CTAs with an empty range wrote nothing
+    const int n_parts = (cta_hi - cta_lo + 1) * kComputeWarps;
+    auto part = [&](int i, int row) -> const float * {
+        const int c = cta_lo + i / kComputeWarps;
+        if (cta_first_tile(c, sc.n_tiles, p.stream_grid) >= cta_first_tile(c + 1, sc.n_tiles, p.stream_grid))
+            return nullptr;
+        return p.partials + ((long long)(cta_lo + lane) * kComputeWarps + i) * p.G * kPartialStride +
+               row * kPartialStride;
+    };
+    if (tid < p.G) {
+        float m = s_snew[tid];
+        for (int i = 0; i < n_parts; ++i) {
+            const float *pr = part(i, tid);
+            if (pr) m = fmaxf(m, pr[0]);
+        }
+        float l = __expf(s_snew[tid] - m);
+        for (int i = 0; i < n_parts; ++i) {
+            const float *pr = part(i, tid);
+            if (pr && pr[0] != -INFINITY) l += pr[1] * __expf(pr[0] - m);
+        }
+        s_m[tid] = m;
+        s_linv[tid] = 1.f / l;
+        s_pnew[tid] = __expf(s_snew[tid] - m) / l;
+    }
+    __syncthreads();
+
+    // 3. output rows (first block of the lane)
+    if (blockIdx.x == 0) {
+        for (int idx = tid; idx < p.G * 128; idx += kFinishThreads) {
+            const int gh = idx >> 7, d = idx & 127;
+            float acc = __expf(s_snew[gh] - s_m[gh]) * Elem<T>::to_f(vrow[d]);
+            for (int i = 0; i < n_parts; ++i) {
+                const float *pr = part(i, gh);
+                if (pr && pr[0] != -INFINITY) acc = fmaf(pr[2 + d], __expf(pr[0] - s_m[gh]), acc);
+            }
+            T *orow = reinterpret_cast<T *>(p.out) + b * p.osb + (long long)(kvh * p.G + gh) * p.osh;
+            orow[d] = Elem<T>::from_f(acc * s_linv[gh]);
+        }
+    }
+    if (!p.update) return;
+
+    // 4. EMA scores of this block's slots:  score = T(T(beta*score) + reduce_g T(T(p_g) * (1-beta)))
+    if (p.ema) {
+        const float w0 = p.ema_w_cache[0];
+        const int per_block = (((p.S + p.finish_chunks - 1) / p.finish_chunks) + 1) & ~1;
+        const int s_begin = blockIdx.x * per_block;
+        const int s_end = min(p.S, s_begin + per_block);
+        const T *lg = reinterpret_cast<const T *>(p.logits) + ((long long)b * p.H + kvh * p.G) * p.S;
+        T *scr = reinterpret_cast<T *>(p.score_cache) + (long long)lane * p.S;
+        for (int slot = s_begin + tid; slot < s_end; slot += kFinishThreads) {
+            float red = 0.f;
+            if (slot < sc.total) {
+                float e[kMaxG];
+                for (int gh = 0; gh < p.G; ++gh) {
+                    const float pr = rnd<T>(__expf(Elem<T>::to_f(lg[(long long)gh * p.S + slot]) - s_m[gh]) * s_linv[gh]);
+                    e[gh] = rnd<T>(__fmul_rn(pr, w0));
+                }
+                red = rnd<T>(reduce_group(e, p.G, p.head_reduction));
+            }
+            const float decayed = rnd<T>(__fmul_rn(Elem<T>::to_f(scr[slot]), p.beta_pow));
+            scr[slot] = Elem<T>::from_f(__fadd_rn(decayed, red));
+        }
+    }
+
+    // 5. lane-invariant state after this token: lane 0's blocks rewrite positions / masks of their
+    //    slots from the advanced counters (nothing in this kernel reads them)
+    if (tid == 0) {
+        for (int i = 0; i < p.C; ++i) {
+            s_new_stored[i] = p.stored_tokens[i];
+            s_new_start[i] = p.start_indices[i];
+            s_every[i] = p.every_n[i];
+        }
+        long long sinks = sc.sinks;
+        advance_counters(s_new_stored, s_new_start, sinks, sc.seen, s_every, 1, p.NS, p.W, p.C, p.S, p.eager_fill);
+        long long total = 0;
+        for (int i = 0; i < p.C; ++i) total += s_new_stored[i];
+        s_new_sinks = sinks;
+        s_new_total = total;
+    }
+    __syncthreads();
+    if (lane == 0) {
+        const int per_block = (p.S + p.finish_chunks - 1) / p.finish_chunks;
+        const int s_begin = blockIdx.x * per_block, s_end = min(p.S, s_begin + per_block);
+        const bool rewrite = sc.seen + 1 > p.NS;
+        for (int t = s_begin + tid; t < s_end; t += kFinishThreads) {
+            const int i = t / p.W, j = t % p.W;
+            const long long stored_i = s_new_stored[i];
+            if (j < stored_i) p.mask[t] = 0;
+            const long long ub = s_new_total - (long long)i * p.W;
+            const long long seg = stored_i < p.W ? stored_i : p.W;
+            if (rewrite && ub > 0 && seg > 0) p.pos[t] = ((j + seg - s_new_start[i]) % seg) + ub - seg;
+        }
+    }
+
+    // 6. the last block of the lane inserts the token; the last lane advances the counters
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_is_last = (atomicAdd(&p.sync[1 + lane], 1u) == (unsigned)(gridDim.x - 1));
+    __syncthreads();
+    if (!s_is_last) return;
+    __threadfence();
+    if (warp == 0) {
+        if (p.ema && lane_id == 0) {
+            float e[kMaxG];
+            const float w1 = Elem<T>::to_f(reinterpret_cast<const T *>(p.ema_w_new)[0]);
+            for (int gh = 0; gh < p.G; ++gh) e[gh] = rnd<T>(__fmul_rn(rnd<T>(s_pnew[gh]), w1));
+            reinterpret_cast<T *>(p.new_scores)[lane] = Elem<T>::from_f(rnd<T>(reduce_group(e, p.G, p.head_reduction)));
+        }
+        __syncwarp();
+        update_lane_walk(p.upd, lane, s_stored, s_start, s_every);
+        __threadfence();
+        __syncwarp();
+        unsigned last = 0;
+        if (lane_id == 0) last = (atomicAdd(&p.sync[0], 1u) == (unsigned)(gridDim.y - 1));
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (last) {
+            // every lane has read the old counters and finished its insert: publish the new ones
+            for (int i = lane_id; i < p.C; i += 32) {
+                p.stored_tokens[i] = s_new_stored[i];
+                p.start_indices[i] = s_new_start[i];
+            }
+            if (lane_id == 0) {
+                if (s_new_sinks > sc.sinks) {
+                    p.sink_pos[sc.sinks] = sc.sinks;
+                    p.sink_mask[sc.sinks] = 0;
+                }
+                *p.stored_sinks = s_new_sinks;
+                *p.seen = sc.seen + 1;
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+// [rows, 128] 16-bit row-major tensor, boxes of 64 rows x 64 elements (128 bytes), 128-byte swizzle.
+int make_rows_map(CUtensorMap *tm, const void *base, uint64_t rows, int dtype) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return fail(CKV_E_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    const cuuint64_t dims[2] = {128, rows};
+    const cuuint64_t strides[1] = {256};
+    const cuuint32_t box[2] = {64, (cuuint32_t)kTile};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(tm, dtype == CKV_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                          const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(CKV_E_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return CKV_OK;
+}
+
+size_t up256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+struct DecodeScratch {
+    size_t status, sync, logits, partials, new_scores, total;
+};
+
+int sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+            n = 148;
+    }
+    return n;
+}
+
+DecodeScratch decode_scratch(const Dims &d) {
+    DecodeScratch s;
+    const size_t lanes = (size_t)d.B * d.KVH;
+    size_t off = 0;
+    s.status = off; off += 256;
+    s.sync = off; off += up256((1 + lanes) * 4);
+    s.logits = off; off += up256((size_t)d.B * d.H * d.S * 2);
+    s.partials = off; off += up256((size_t)(sm_count() + lanes) * kComputeWarps * d.G * kPartialStride * 4);
+    s.new_scores = off; off += up256(lanes * 2);
+    s.total = off;
+    return s;
+}
+
+}  // namespace
+
+bool decode_tuned_supported(const Dims &d, int n_tokens) {
+    return n_tokens == 1 && (d.dtype == CKV_BF16 || d.dtype == CKV_F16) && d.D == 128 && d.G <= kMaxG &&
+           !d.homogeneous && d.S % 2 == 0 && d.NS >= 1;
+}
+
+size_t decode_workspace_bytes(const Dims &d) { return decode_scratch(d).total; }
+
+int launch_decode_tuned(const Dims &d, const ckv_layer_state *st, const void *q, int64_t qsb, int64_t qsh,
+                        const void *key, const void *value, int64_t ksb, int64_t ksh, const void *rope,
+                        int64_t rope_rows, const float *ema_w_cache, const void *ema_w_new, void *out, int64_t osb,
+                        int64_t osh, void *workspace, size_t workspace_bytes, int flags, cudaStream_t stream,
+                        ProfileHook *hook) {
+    const DecodeScratch s = decode_scratch(d);
+    if (!workspace || workspace_bytes < s.total)
+        return fail(CKV_E_WORKSPACE, "workspace of %zu bytes, need %zu", workspace_bytes, s.total);
+    if (rope_rows <= (int64_t)d.NS + d.S + 1)
+        return fail(CKV_E_ARG, "rope table has %lld rows, need more than %d", (long long)rope_rows, d.NS + d.S + 1);
+    const bool update = (flags & CKV_ATTN_UPDATE) != 0;
+    const bool ema = update && d.admission == CKV_ADMIT_EMA;
+    if (ema && (!ema_w_cache || !ema_w_new)) return fail(CKV_E_ARG, "EMA rule needs ema_w_cache and ema_w_new");
+    if (((uintptr_t)q | (uintptr_t)out) % 4 != 0 || (qsb % 2) || (qsh % 2))
+        return fail(CKV_E_ARG, "q rows must be 4-byte aligned");
+    if (((uintptr_t)key | (uintptr_t)value | (uintptr_t)rope) % 16 != 0 || (ksb * 2) % 16 || (ksh * 2) % 16)
+        return fail(CKV_E_ARG, "key/value/rope rows must be 16-byte aligned");
+    if (((uintptr_t)st->key_cache | (uintptr_t)st->value_cache | (uintptr_t)st->sink_keys |
+         (uintptr_t)st->sink_values) % 16 != 0)
+        return fail(CKV_E_ARG, "cache tensors must be 16-byte aligned");
+
+    static bool attr_set = false;
+    if (!attr_set) {
+        CKV_CUDA_CHECK(cudaFuncSetAttribute(decode_stream_kernel<__nv_bfloat16>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmem));
+        CKV_CUDA_CHECK(cudaFuncSetAttribute(decode_stream_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            kStreamSmem));
+        attr_set = true;
+    }
+    const uint64_t lanes = (uint64_t)d.B * d.KVH;
+    CUtensorMap tmK, tmV, tmSK, tmSV;
+    int rc;
+    if ((rc = make_rows_map(&tmK, st->key_cache, lanes * d.S, d.dtype)) != CKV_OK) return rc;
+    if ((rc = make_rows_map(&tmV, st->value_cache, lanes * d.S, d.dtype)) != CKV_OK) return rc;
+    if ((rc = make_rows_map(&tmSK, st->sink_keys, lanes * d.NS, d.dtype)) != CKV_OK) return rc;
+    if ((rc = make_rows_map(&tmSV, st->sink_values, lanes * d.NS, d.dtype)) != CKV_OK) return rc;
+
+    uint8_t *ws = (uint8_t *)workspace;
+    DecodeParams p;
+    p.q = q; p.qsb = qsb; p.qsh = qsh;
+    p.knew = key; p.vnew = value; p.ksb = ksb; p.ksh = ksh;
+    p.out = out; p.osb = osb; p.osh = osh;
+    p.rope = rope; p.rope_rows = rope_rows;
+    p.ema_w_cache = ema_w_cache; p.ema_w_new = ema_w_new;
+    p.score_cache = st->score_cache;
+    p.pos = (long long *)st->pos; p.sink_pos = (long long *)st->sink_pos;
+    p.stored_tokens = (long long *)st->stored_tokens; p.start_indices = (long long *)st->start_indices;
+    p.stored_sinks = (long long *)st->stored_sinks; p.seen = (long long *)st->seen_tokens;
+    p.every_n = (const long long *)st->every_n;
+    p.mask = st->mask; p.sink_mask = st->sink_mask;
+    p.status = (int *)(ws + s.status);
+    p.sync = (unsigned int *)(ws + s.sync);
+    p.logits = ws + s.logits;
+    p.partials = (float *)(ws + s.partials);
+    p.new_scores = ws + s.new_scores;
+    p.B = d.B; p.KVH = d.KVH; p.H = d.H; p.G = d.G; p.NS = d.NS; p.W = d.W; p.C = d.C; p.S = d.S;
+    p.ema = ema; p.update = update; p.head_reduction = d.head_reduction; p.eager_fill = d.eager_fill;
+    p.dtype = d.dtype;
+    p.stream_grid = sm_count();
+    int chunks = 1;
+    if (ema) {
+        chunks = (int)((4 * (uint64_t)sm_count() + lanes - 1) / lanes);
+        chunks = chunks < 1 ? 1 : (chunks > 64 ? 64 : chunks);
+    }
+    p.finish_chunks = chunks;
+    p.rs = (float)sqrt(1.0 / sqrt((double)d.D));
+    p.beta_pow = (float)d.beta;
+    UpdateParams &u = p.upd;
+    u.key = (const uint8_t *)key; u.val = (const uint8_t *)value;
+    u.ksb = ksb * 2; u.ksh = ksh * 2; u.kst = 0;
+    u.scr = ema ? (const uint8_t *)p.new_scores : nullptr;
+    u.ssb = (long long)d.KVH * 2; u.ssh = 2; u.sst = 0;
+    u.sink_k = (uint8_t *)st->sink_keys; u.sink_v = (uint8_t *)st->sink_values;
+    u.cache_k = (uint8_t *)st->key_cache; u.cache_v = (uint8_t *)st->value_cache;
+    u.cache_s = (uint8_t *)st->score_cache;
+    u.og_pos = (long long *)st->og_pos;
+    u.stored_tokens = (const long long *)st->stored_tokens; u.start_indices = (const long long *)st->start_indices;
+    u.stored_sinks = (const long long *)st->stored_sinks; u.seen = (const long long *)st->seen_tokens;
+    u.every_n = (const long long *)st->every_n;
+    u.KVH = d.KVH; u.K = 1; u.NS = d.NS; u.W = d.W; u.C = d.C; u.S = d.S;
+    u.row_bytes = 256; u.esz = 2; u.dtype = d.dtype; u.eager_fill = d.eager_fill;
+
+    CKV_CUDA_CHECK(cudaMemsetAsync(p.status, 0, 4, stream));
+    if (hook) hook->before(stream, "decode_stream_kernel");
+    if (d.dtype == CKV_BF16)
+        decode_stream_kernel<__nv_bfloat16><<<p.stream_grid, kStreamThreads, kStreamSmem, stream>>>(tmK, tmV, tmSK, tmSV, p);
+    else
+        decode_stream_kernel<__half><<<p.stream_grid, kStreamThreads, kStreamSmem, stream>>>(tmK, tmV, tmSK, tmSV, p);
+    if (hook) hook->after(stream);
+    CKV_CUDA_CHECK(cudaGetLastError());
+    const dim3 grid(chunks, (unsigned)lanes);
+    if (d.dtype == CKV_BF16) decode_finish_kernel<__nv_bfloat16><<<grid, kFinishThreads, 0, stream>>>(p);
+    else decode_finish_kernel<__half><<<grid, kFinishThreads, 0, stream>>>(p);
+    CKV_CUDA_CHECK(cudaGetLastError());
+    note_launches(2);
+    return CKV_OK;
+}
+
+}  // namespace ckv

@@ -1,0 +1,42 @@
+"""CUDA-event timing of the dominant kernel through the library's own profiling hook
+(``ckv_profile_enable`` / ``ckv_profile_read``), the counterpart of the reference's
+``sink_cache(..., BENCHMARK=True)`` event timing (cascading_cache.py:986-1026)."""
+from __future__ import annotations
+
+import ctypes
+import json
+import os
+
+from . import _lib
+
+_TRAFFIC_FILE = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "profiles",
+                             "dram_traffic.json")
+
+
+def time_dominant_kernel(run_step, n_steps: int = 20):
+    """Run ``run_step(i)`` ``n_steps`` times with the hook on; return (ms per launch, launches, kernel name)."""
+    lib = _lib.load()
+    lib.ckv_profile_enable(1)
+    try:
+        for i in range(n_steps):
+            run_step(i)
+        total, n, name = ctypes.c_double(0), ctypes.c_int32(0), ctypes.c_char_p()
+        _lib.check(lib.ckv_profile_read(ctypes.byref(total), ctypes.byref(n), ctypes.byref(name)),
+                   "ckv_profile_read")
+    finally:
+        lib.ckv_profile_enable(0)
+    launches = max(n.value, 1)
+    return total.value / launches, n.value, (name.value or b"").decode()
+
+
+def last_launch_count() -> int:
+    return int(_lib.load().ckv_last_launch_count())
+
+
+def recorded_dram_traffic(workload: str, kernel: str):
+    """DRAM bytes per launch of ``kernel`` on ``workload`` from the committed ncu summary, or None."""
+    try:
+        table = json.load(open(_TRAFFIC_FILE))
+        return table.get(workload, {}).get(kernel)
+    except Exception:
+        return None

@@ -157,6 +157,27 @@ int ckv_attention(const ckv_config *cfg, const ckv_layer_state *st,
                   void *workspace, size_t workspace_bytes,
                   int32_t flags, void *cuda_stream);
 
+/* Number of kernels the calling thread's last ckv_attention / ckv_cascade_update call launched. */
+int ckv_last_launch_count(void);
+
+/*
+ * Optional CUDA-event timing of the dominant (key/value streaming) kernel of every following
+ * ckv_attention call, with events owned by the library.  Replaces the BENCHMARK switch of the
+ * reference's sink_cache(), which brackets its launch with CUDA events and prints the time
+ * (cascade/models/cascading_cache.py:986-1026).  ckv_profile_read synchronises on the recorded
+ * events, returns their summed duration, how many launches were timed and the kernel's name, and
+ * starts a new collection.  Not thread-safe; meant for benchmarks.
+ */
+int ckv_profile_enable(int enable);
+int ckv_profile_read(double *total_ms /* host */, int32_t *launches /* host */, const char **kernel_name /* host */);
+
+/*
+ * Copy the status word of a ckv_attention workspace to the host (synchronises).  0 = no kernel of
+ * the last call gave up on a bounded wait; non-zero = a pipeline wait ran out and the results of
+ * that call are invalid.  (No counterpart in the reference: its kernels have no waits.)
+ */
+int ckv_read_status(const void *workspace, int32_t *status /* host */);
+
 #ifdef __cplusplus
 }
 #endif

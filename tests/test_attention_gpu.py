@@ -99,9 +99,12 @@ def test_streams_against_oracle(spec, force_generic):
                                 head_reduction=red, force_generic=force_generic).float().cpu()
         ok, err = close_enough(got, want.float(), is16)
         assert ok, err
+    assert cache.kernel_status() == 0
     valid = ~ref.mask[0]
     assert torch.equal(cache.mask[0].cpu(), ref.mask[0])
     assert torch.equal(cache.pos[0].cpu()[valid], ref.pos[0][valid])
+    assert torch.equal(cache.stored_tokens[0].cpu(), ref.stored_tokens[0])
+    assert torch.equal(cache.start_indices[0].cpu(), ref.start_indices[0])
     agree = (cache.og_pos[0].cpu()[valid] == ref.og_pos[0][valid]).float().mean().item()
     if rule == "stride":
         assert agree == 1.0
@@ -126,3 +129,67 @@ def test_attention_without_update_leaves_state_untouched():
     assert torch.equal(o1, o2) and cache.seen_tokens_host(0) == seen
     for a, b in zip(before, (cache.key_cache[0], cache.score_cache[0], cache.og_pos[0], cache.pos[0])):
         assert torch.equal(a, b)
+
+
+def copy_state_to_gpu(ref, cache, l=0):
+    """Give the CUDA cache exactly the bits of a CPU oracle cache."""
+    for name in ("key_cache", "value_cache", "score_cache", "sink_keys", "sink_values", "og_pos"):
+        getattr(cache, name)[l].copy_(getattr(ref, name)[l])
+    cache._stored_tokens[l].copy_(ref.stored_tokens[l][0, 0])
+    cache._start_indices[l].copy_(ref.start_indices[l][0, 0])
+    cache._stored_sinks[l].copy_(ref.stored_sinks[l][0, 0].view(1))
+    cache._pos[l].copy_(ref.pos[l][0, 0])
+    cache._sink_pos[l].copy_(ref.sink_pos[l][0, 0])
+    cache._mask[l].copy_(ref.mask[l][0, 0])
+    cache._sink_mask[l].copy_(ref.sink_mask[l][0, 0])
+    cache.seen_tokens_by_layer[l] = ref.seen_tokens_by_layer[l]
+    cache._seen_host[l] = ref.seen_tokens_by_layer[l]
+    cache.beta = ref.beta
+
+
+DECODE = [
+    # B,H,KVH, NS,W,C, dtype, rule, red, steps
+    (2, 8, 2, 64, 512, 4, torch.bfloat16, "ema", "max", 6),
+    (4, 8, 2, 64, 1024, 8, torch.bfloat16, "ema", "max", 5),
+    (3, 14, 2, 4, 256, 8, torch.bfloat16, "stride", "max", 6),
+    (2, 12, 4, 70, 320, 4, torch.float16, "ema", "mean", 5),
+    (1, 32, 2, 4, 192, 2, torch.bfloat16, "ema", "median", 4),
+]
+
+
+@pytest.mark.parametrize("spec", DECODE, ids=lambda s: f"B{s[0]}H{s[1]}kv{s[2]}NS{s[3]}W{s[4]}C{s[5]}-{str(s[6])[6:]}-{s[7]}-{s[8]}")
+def test_decode_on_full_cache(spec):
+    """Decode steps on a fully populated cache (the benchmark's regime): the streaming kernel's
+    split of the key stream crosses lanes and CTAs hold several tiles."""
+    from cascading_kv_cache_b200 import CascadingKVCache, cascade_attention
+    from cascading_kv_cache_b200.synthetic import populate_steady_state
+    B, H, KVH, NS, W, C, dtype, rule, red, steps = spec
+    D, S = 128, W * C
+    ref = OracleCascadingKVCache(W, NS, B, KVH, D, S, dtype=dtype, head_reduction=red, layers=1, eager_fill=True)
+    populate_steady_state(ref, 0, seed=5, beta=0.999)
+    cache = CascadingKVCache(W, NS, B, KVH, D, S, device="cuda:0", dtype=dtype, head_reduction=red, layers=1,
+                             eager_fill=True, admission=rule)
+    copy_state_to_gpu(ref, cache)
+    g = torch.Generator().manual_seed(11)
+    for _ in range(steps):
+        q = torch.randn(B, H, 1, D, generator=g).to(dtype)
+        k = torch.randn(B, KVH, 1, D, generator=g).to(dtype)
+        v = torch.randn(B, KVH, 1, D, generator=g).to(dtype)
+        if rule == "stride":
+            want = cascade_attention_step(q, k, v, ref, 0, 5e5, red, False, do_update=False)
+            ref.update(k, v, 0)
+        else:
+            want = cascade_attention_step(q, k, v, ref, 0, 5e5, red, False)
+        got = cascade_attention(q.cuda(), k.cuda(), v.cuda(), cache, 0, rope_theta=5e5).float().cpu()
+        ok, err = close_enough(got, want.float(), True)
+        assert ok, err
+    assert cache.kernel_status() == 0
+    assert torch.equal(cache.pos[0].cpu(), ref.pos[0])
+    assert torch.equal(cache.start_indices[0].cpu(), ref.start_indices[0])
+    agree = (cache.og_pos[0].cpu() == ref.og_pos[0]).float().mean().item()
+    assert agree >= 0.999, agree
+    if rule == "ema":
+        a, b = cache.score_cache[0].float().cpu(), ref.score_cache[0].float()
+        same = (a == b).float().mean().item()
+        assert same >= 0.99, same   # scores are 16-bit: equal bits almost everywhere
+        assert torch.allclose(a, b, rtol=2e-2, atol=1e-8)
