@@ -161,8 +161,13 @@ def main():
     ap.add_argument("--workload", default="c2_llama8b_decode", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--force-generic", action="store_true")
+    ap.add_argument("--batch", type=int, default=0, help="override the batch (smaller cases for profiler captures)")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiler captures)")
+    ap.add_argument("--no-profile", action="store_true", help="skip the per-kernel event timing")
     args = ap.parse_args()
-    w = WORKLOADS[args.workload]
+    w = dict(WORKLOADS[args.workload])
+    if args.batch > 0:
+        w["B"] = args.batch
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -235,16 +240,18 @@ def main():
         hout.copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()  # the caller reads the result
 
-    for i in range(3):
-        e2e_step(i)
-    barrier()
-    ev2, ev3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev2.record()
-    for i in range(e2e_steps):
-        e2e_step(i)
-    ev3.record()
-    barrier()
-    ms_e2e_total = ev2.elapsed_time(ev3)
+    ms_e2e_total = float("nan")
+    if not args.no_e2e:
+        for i in range(3):
+            e2e_step(i)
+        barrier()
+        ev2, ev3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev2.record()
+        for i in range(e2e_steps):
+            e2e_step(i)
+        ev3.record()
+        barrier()
+        ms_e2e_total = ev2.elapsed_time(ev3)
 
     t = torch.tensor([ms_total, ms_e2e_total], device=dev, dtype=torch.float64)
     if world > 1:
@@ -260,7 +267,11 @@ def main():
 
     if rank == 0:
         from cascading_kv_cache_b200 import profiling
-        k_ms, k_n, k_name = profiling.time_dominant_kernel(step, n_steps=min(steps, 50))
+        if args.no_profile:
+            step(0)
+            k_ms, k_name = ms_step, "whole step"
+        else:
+            k_ms, k_n, k_name = profiling.time_dominant_kernel(step, n_steps=min(steps, 50))
         launches_per_step = profiling.last_launch_count()
         torch.cuda.synchronize()
         prof = {"ms": k_ms, "gbs": nbytes / (k_ms * 1e-3) / 1e9, "kernel": k_name,

@@ -299,7 +299,7 @@ struct Scratch {
 
 Scratch scratch_layout(const Dims &d, int K) {
     Scratch s;
-    size_t off = 0;
+    size_t off = 256;  // the first 256 bytes of every attention workspace hold the status word
     s.q_rs = off; off += align_up((size_t)d.B * d.H * K * d.D * d.esz);
     s.k_rot = off; off += align_up((size_t)d.B * d.KVH * (d.NS + d.S + K) * d.D * d.esz);
     s.row_m = off; off += align_up((size_t)d.B * d.H * K * 4);
@@ -359,6 +359,7 @@ int launch_attention_generic(const Dims &d, const ckv_layer_state *st, const voi
         return fail(CKV_E_ARG, "rope table has %lld rows, need more than %d", (long long)rope_rows,
                     d.NS + d.S + n_tokens);
     uint8_t *ws = (uint8_t *)workspace;
+    CKV_CUDA_CHECK(cudaMemsetAsync(ws, 0, 4, stream));
     GenericParams p;
     p.q = q; p.key = key; p.val = value;
     p.qsb = qsb; p.qsh = qsh; p.qst = qst; p.ksb = ksb; p.ksh = ksh; p.kst = kst;

@@ -29,7 +29,7 @@ namespace {
 
 constexpr int kTile = 64;                       // keys per stage
 constexpr int kStages = 4;
-constexpr int kComputeWarps = 4;
+constexpr int kComputeWarps = 8;                // each owns 8 keys of a tile
 constexpr int kStreamThreads = (kComputeWarps + 1) * 32;
 constexpr int kSubBytes = kTile * 128;          // one swizzled 64-row x 128-byte sub-tile
 constexpr int kStageBytes = 6 * kSubBytes;      // K lo | K hi | V lo | V hi | cos | sin
@@ -101,13 +101,28 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, unsigned parity, int *s
     atomicExch(status, 1);
     return false;
 }
-__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *tm, int x, int y, uint64_t *bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(smem_u32(dst)), "l"(tm), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+// L2 policies: the key/value stream is read once (evict first), the cos/sin table is re-read by
+// every lane (evict last).
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
 }
-__device__ __forceinline__ void cp_async_16(void *dst, const void *src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *tm, int x, int y, uint64_t *bar,
+                                            uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%3, %4}], [%2], %5;"
+        ::"r"(smem_u32(dst)), "l"(tm), "r"(smem_u32(bar)), "r"(x), "r"(y), "l"(policy) : "memory");
+}
+__device__ __forceinline__ void cp_async_16(void *dst, const void *src, uint64_t policy) {
+    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;"
+                 ::"r"(smem_u32(dst)), "l"(src), "l"(policy) : "memory");
 }
 __device__ __forceinline__ void cp_async_arrive_noinc(uint64_t *bar) {
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -137,6 +152,20 @@ template <> struct Mma<__half> {
     }
 };
 
+template <typename T> struct MmaK8;
+template <> struct MmaK8<__nv_bfloat16> {
+    static __device__ __forceinline__ void run(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+        asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(b0));
+    }
+};
+template <> struct MmaK8<__half> {
+    static __device__ __forceinline__ void run(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+        asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(b0));
+    }
+};
+
 // ---- packed 16-bit arithmetic with one rounding per operation ---------------------------------
 template <typename T> struct Pack;
 template <> struct Pack<__nv_bfloat16> {
@@ -160,8 +189,8 @@ template <typename T>
 __device__ __forceinline__ void rope_pair(uint32_t &lo, uint32_t &hi, uint32_t c, uint32_t s, float rs) {
     using P = Pack<T>;
     const typename P::T2 l = P::from_u(lo), h = P::from_u(hi), cc = P::from_u(c), ss = P::from_u(s);
-    const typename P::T2 nl = __hsub2(__hmul2(l, cc), __hmul2(h, ss));
-    const typename P::T2 nh = __hadd2(__hmul2(h, cc), __hmul2(l, ss));
+    const typename P::T2 nl = __hsub2_rn(__hmul2_rn(l, cc), __hmul2_rn(h, ss));  // _rn: never contracted into fma
+    const typename P::T2 nh = __hadd2_rn(__hmul2_rn(h, cc), __hmul2_rn(l, ss));
     float2 fl = P::to_f2(nl), fh = P::to_f2(nh);
     fl.x *= rs; fl.y *= rs; fh.x *= rs; fh.y *= rs;
     lo = P::to_u(P::from_f2(fl));
@@ -194,7 +223,7 @@ __device__ __forceinline__ long long cta_first_tile(long long cta, long long n_t
 }
 
 // ------------------------------------------------------------------------------ stream kernel
-template <typename T>
+template <typename T, int kRowHalves>
 __global__ void __launch_bounds__(kStreamThreads, 1)
 decode_stream_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                      const __grid_constant__ CUtensorMap tmSK, const __grid_constant__ CUtensorMap tmSV,
@@ -224,40 +253,48 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     if (warp == kComputeWarps) {
         // ------------------------------------------------------------------ producer warp
         const uint8_t *rope = reinterpret_cast<const uint8_t *>(p.rope);
+        const uint64_t pol_stream = l2_policy_evict_first(), pol_keep = l2_policy_evict_last();
         int it = 0;
         for (long long t = t_begin; t < t_end; ++t, ++it) {
             const int s = it % kStages;
+            const int lane = (int)(t / sc.tiles_per_lane);
+            const int ti = (int)(t % sc.tiles_per_lane);
+            const bool sink_tile = ti < sc.n_sink_tiles;
+            const int row0 = sink_tile ? ti * kTile : (ti - sc.n_sink_tiles) * kTile;
+            // positions of rows lane_id and lane_id + 32: issued before the wait so that their
+            // latency hides behind it
+            long long pos[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int idx = row0 + lane_id + 32 * h;
+                if (sink_tile) pos[h] = idx < sc.sinks ? p.sink_pos[idx] : 0;
+                else pos[h] = idx < sc.total ? p.pos[idx] + sc.shift : 0;
+            }
             if (it >= kStages) {
                 if (!mbar_wait(&empty[s], ((it / kStages) & 1) ^ 1, p.status)) break;
             }
-            const int lane = (int)(t / sc.tiles_per_lane);
-            const int ti = (int)(t % sc.tiles_per_lane);
             uint8_t *stage = smem + s * kStageBytes;
-            const bool sink_tile = ti < sc.n_sink_tiles;
-            const int row0 = sink_tile ? ti * kTile : (ti - sc.n_sink_tiles) * kTile;
             if (lane_id == 0) {
                 mbar_expect_tx(&full[s], 4 * kSubBytes);
                 const int y = sink_tile ? lane * p.NS + row0 : lane * p.S + row0;
                 const CUtensorMap *mk = sink_tile ? &tmSK : &tmK;
                 const CUtensorMap *mv = sink_tile ? &tmSV : &tmV;
-                tma_load_2d(stage + kOffK, mk, 0, y, &full[s]);
-                tma_load_2d(stage + kOffK + kSubBytes, mk, 64, y, &full[s]);
-                tma_load_2d(stage + kOffV, mv, 0, y, &full[s]);
-                tma_load_2d(stage + kOffV + kSubBytes, mv, 64, y, &full[s]);
+                tma_load_2d(stage + kOffK, mk, 0, y, &full[s], pol_stream);
+                tma_load_2d(stage + kOffK + kSubBytes, mk, 64, y, &full[s], pol_stream);
+                tma_load_2d(stage + kOffV, mv, 0, y, &full[s], pol_stream);
+                tma_load_2d(stage + kOffV + kSubBytes, mv, 64, y, &full[s], pol_stream);
             }
-            // cos|sin rows of the tile's positions: 64 rows x 16 chunks of 16 bytes
-#pragma unroll 4
-            for (int i = 0; i < 32; ++i) {
-                const int qd = i * 32 + lane_id;
-                const int r = qd >> 4, c = qd & 15;
-                const int idx = row0 + r;
-                long long pos;
-                if (sink_tile) pos = idx < sc.sinks ? p.sink_pos[idx] : 0;
-                else pos = idx < sc.total ? p.pos[idx] + sc.shift : 0;
-                pos = pos < 0 ? 0 : (pos >= p.rope_rows ? p.rope_rows - 1 : pos);
-                const uint8_t *src = rope + pos * 256 + c * 16;
-                uint8_t *dst = stage + (c < 8 ? kOffCos : kOffSin) + r * 128 + (((c & 7) ^ (r & 7)) << 4);
-                cp_async_16(dst, src);
+            // cos|sin rows of the tile's positions: 16 chunks of 16 bytes per row, swizzled like K
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int r = lane_id + 32 * h;
+                const long long ps = pos[h] < 0 ? 0 : (pos[h] >= p.rope_rows ? p.rope_rows - 1 : pos[h]);
+                const uint8_t *srow = rope + ps * 256;
+                uint8_t *drow = stage + r * 128;
+#pragma unroll
+                for (int c = 0; c < 16; ++c)
+                    cp_async_16(drow + (c < 8 ? kOffCos : kOffSin) + (((c & 7) ^ (r & 7)) << 4), srow + c * 16,
+                                pol_keep);
             }
             cp_async_arrive_noinc(&full[s]);
         }
@@ -342,103 +379,89 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
             const int row0 = sink_tile ? ti * kTile : (ti - sc.n_sink_tiles) * kTile;
             const long long limit = sink_tile ? sc.sinks : sc.total;
             const int nvalid = (int)(limit - row0 < kTile ? limit - row0 : kTile);
-            const int key0 = 16 * warp;
+            const int key0 = 8 * warp;
             if (key0 < nvalid) {
                 const uint32_t stage = smem_u32(smem + s * kStageBytes);
-                float sacc[2][4];
+                const int krow = key0 + (lane_id & 7);
+                const uint32_t rowoff = krow * 128;
+                const int sw = krow & 7;
+                float sacc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                for (int nt = 0; nt < 2; ++nt) {
-                    sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f;
-                    const int krow = key0 + 8 * nt + (lane_id & 7);
-                    const uint32_t rowoff = krow * 128;
-                    const int sw = krow & 7;
+                for (int u = 0; u < 2; ++u) {
+                    // k-steps 2u, 2u+1 (dims < 64) with their partners 2u+4, 2u+5 (dims + 64)
+                    const uint32_t choff = (uint32_t)(((4 * u + (lane_id >> 3)) ^ sw) << 4);
+                    uint32_t kl[4], kh[4], cs[4], sn[4];
+                    ldsm_x4(stage + kOffK + rowoff + choff, kl[0], kl[1], kl[2], kl[3]);
+                    ldsm_x4(stage + kOffK + kSubBytes + rowoff + choff, kh[0], kh[1], kh[2], kh[3]);
+                    ldsm_x4(stage + kOffCos + rowoff + choff, cs[0], cs[1], cs[2], cs[3]);
+                    ldsm_x4(stage + kOffSin + rowoff + choff, sn[0], sn[1], sn[2], sn[3]);
 #pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        // k-steps 2u, 2u+1 (dims < 64) with their partners 2u+4, 2u+5 (dims + 64)
-                        const uint32_t choff = (uint32_t)(((4 * u + (lane_id >> 3)) ^ sw) << 4);
-                        uint32_t kl[4], kh[4], cs[4], sn[4];
-                        ldsm_x4(stage + kOffK + rowoff + choff, kl[0], kl[1], kl[2], kl[3]);
-                        ldsm_x4(stage + kOffK + kSubBytes + rowoff + choff, kh[0], kh[1], kh[2], kh[3]);
-                        ldsm_x4(stage + kOffCos + rowoff + choff, cs[0], cs[1], cs[2], cs[3]);
-                        ldsm_x4(stage + kOffSin + rowoff + choff, sn[0], sn[1], sn[2], sn[3]);
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) rope_pair<T>(kl[e], kh[e], cs[e], sn[e], p.rs);
-                        Mma<T>::run(sacc[nt], qa[2 * u], kl[0], kl[1]);
-                        Mma<T>::run(sacc[nt], qa[2 * u + 1], kl[2], kl[3]);
-                        Mma<T>::run(sacc[nt], qa[2 * u + 4], kh[0], kh[1]);
-                        Mma<T>::run(sacc[nt], qa[2 * u + 5], kh[2], kh[3]);
-                    }
+                    for (int e = 0; e < 4; ++e) rope_pair<T>(kl[e], kh[e], cs[e], sn[e], p.rs);
+                    Mma<T>::run(sacc, qa[2 * u], kl[0], kl[1]);
+                    Mma<T>::run(sacc, qa[2 * u + 1], kl[2], kl[3]);
+                    Mma<T>::run(sacc, qa[2 * u + 4], kh[0], kh[1]);
+                    Mma<T>::run(sacc, qa[2 * u + 5], kh[2], kh[3]);
                 }
                 // logits rounded to T (the reference's einsum output), masked past the valid keys
 #pragma unroll
-                for (int nt = 0; nt < 2; ++nt) {
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int key = key0 + 8 * nt + 2 * tq + (e & 1);
-                        sacc[nt][e] = key < nvalid ? rnd<T>(sacc[nt][e]) : -INFINITY;
-                    }
+                for (int e = 0; e < 4; ++e) {
+                    const int key = key0 + 2 * tq + (e & 1);
+                    sacc[e] = key < nvalid ? rnd<T>(sacc[e]) : -INFINITY;
                 }
                 if (p.ema && !sink_tile) {
                     const int b = lane / p.KVH, kvh = lane % p.KVH;
 #pragma unroll
-                    for (int r = 0; r < 2; ++r) {
+                    for (int r = 0; r < kRowHalves; ++r) {
                         const int row = g + 8 * r;
                         if (row < p.G) {
                             T *lrow = logits + ((long long)b * p.H + kvh * p.G + row) * p.S;
-#pragma unroll
-                            for (int nt = 0; nt < 2; ++nt) {
-                                const int slot = row0 + key0 + 8 * nt + 2 * tq;
-                                if (slot + 1 < p.S) {
-                                    typename Pack<T>::T2 v = Pack<T>::from_f2(make_float2(sacc[nt][2 * r], sacc[nt][2 * r + 1]));
-                                    *reinterpret_cast<typename Pack<T>::T2 *>(lrow + slot) = v;
-                                } else if (slot < p.S) {
-                                    lrow[slot] = Elem<T>::from_f(sacc[nt][2 * r]);
-                                }
+                            const int slot = row0 + key0 + 2 * tq;
+                            if (slot + 1 < p.S) {
+                                typename Pack<T>::T2 v = Pack<T>::from_f2(make_float2(sacc[2 * r], sacc[2 * r + 1]));
+                                *reinterpret_cast<typename Pack<T>::T2 *>(lrow + slot) = v;
+                            } else if (slot < p.S) {
+                                lrow[slot] = Elem<T>::from_f(sacc[2 * r]);
                             }
                         }
                     }
                 }
-                // online softmax for rows g and g+8 over this warp's 16 keys
-                uint32_t pa[4];
+                // online softmax over this warp's 8 keys (rows g, and g+8 when the group is larger than 8)
+                uint32_t pa[2] = {0u, 0u};
 #pragma unroll
-                for (int r = 0; r < 2; ++r) {
-                    float mx = fmaxf(fmaxf(sacc[0][2 * r], sacc[0][2 * r + 1]), fmaxf(sacc[1][2 * r], sacc[1][2 * r + 1]));
+                for (int r = 0; r < kRowHalves; ++r) {
+                    float mx = fmaxf(sacc[2 * r], sacc[2 * r + 1]);
                     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
                     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
                     const float m_new = fmaxf(m_run[r], mx);
-                    float corr = 1.f, p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
+                    float corr = 1.f, p0 = 0.f, p1 = 0.f;
                     if (m_new != -INFINITY) {
                         corr = __expf(m_run[r] - m_new);
-                        p0 = __expf(sacc[0][2 * r] - m_new);
-                        p1 = __expf(sacc[0][2 * r + 1] - m_new);
-                        p2 = __expf(sacc[1][2 * r] - m_new);
-                        p3 = __expf(sacc[1][2 * r + 1] - m_new);
+                        p0 = __expf(sacc[2 * r] - m_new);
+                        p1 = __expf(sacc[2 * r + 1] - m_new);
                     }
                     m_run[r] = m_new;
-                    l_run[r] = l_run[r] * corr + (p0 + p1 + p2 + p3);
+                    l_run[r] = l_run[r] * corr + (p0 + p1);
+                    if (__any_sync(0xffffffffu, corr != 1.f)) {  // the running max rarely moves
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        o[j][2 * r] *= corr;
-                        o[j][2 * r + 1] *= corr;
+                        for (int j = 0; j < 16; ++j) {
+                            o[j][2 * r] *= corr;
+                            o[j][2 * r + 1] *= corr;
+                        }
                     }
                     pa[r] = Pack<T>::to_u(Pack<T>::from_f2(make_float2(p0, p1)));
-                    pa[r + 2] = Pack<T>::to_u(Pack<T>::from_f2(make_float2(p2, p3)));
                 }
-                // out += P (16 x 16 keys) * V (16 keys x 128)
-                {
-                    const int vrow = key0 + (lane_id & 7) + 8 * ((lane_id >> 3) & 1);
-                    const uint32_t rowoff = vrow * 128;
-                    const int sw = vrow & 7;
+                // out += P (16 x 8 keys) * V (8 keys x 128)
 #pragma unroll
-                    for (int half = 0; half < 2; ++half) {
+                for (int half = 0; half < 2; ++half) {
 #pragma unroll
-                        for (int cp = 0; cp < 4; ++cp) {
-                            const uint32_t choff = (uint32_t)(((2 * cp + (lane_id >> 4)) ^ sw) << 4);
-                            uint32_t v0, v1, v2, v3;
-                            ldsm_x4_t(stage + kOffV + half * kSubBytes + rowoff + choff, v0, v1, v2, v3);
-                            Mma<T>::run(o[8 * half + 2 * cp], pa, v0, v1);
-                            Mma<T>::run(o[8 * half + 2 * cp + 1], pa, v2, v3);
-                        }
+                    for (int cq = 0; cq < 2; ++cq) {
+                        const uint32_t choff = (uint32_t)(((4 * cq + (lane_id >> 3)) ^ sw) << 4);
+                        uint32_t v0, v1, v2, v3;
+                        ldsm_x4_t(stage + kOffV + half * kSubBytes + rowoff + choff, v0, v1, v2, v3);
+                        MmaK8<T>::run(o[8 * half + 4 * cq], pa[0], pa[1], v0);
+                        MmaK8<T>::run(o[8 * half + 4 * cq + 1], pa[0], pa[1], v1);
+                        MmaK8<T>::run(o[8 * half + 4 * cq + 2], pa[0], pa[1], v2);
+                        MmaK8<T>::run(o[8 * half + 4 * cq + 3], pa[0], pa[1], v3);
                     }
                 }
             }
@@ -566,23 +589,59 @@ __global__ void __launch_bounds__(kFinishThreads) decode_finish_kernel(DecodePar
     // 4. EMA scores of this block's slots:  score = T(T(beta*score) + reduce_g T(T(p_g) * (1-beta)))
     if (p.ema) {
         const float w0 = p.ema_w_cache[0];
-        const int per_block = (((p.S + p.finish_chunks - 1) / p.finish_chunks) + 1) & ~1;
-        const int s_begin = blockIdx.x * per_block;
-        const int s_end = min(p.S, s_begin + per_block);
         const T *lg = reinterpret_cast<const T *>(p.logits) + ((long long)b * p.H + kvh * p.G) * p.S;
         T *scr = reinterpret_cast<T *>(p.score_cache) + (long long)lane * p.S;
-        for (int slot = s_begin + tid; slot < s_end; slot += kFinishThreads) {
-            float red = 0.f;
-            if (slot < sc.total) {
-                float e[kMaxG];
-                for (int gh = 0; gh < p.G; ++gh) {
-                    const float pr = rnd<T>(__expf(Elem<T>::to_f(lg[(long long)gh * p.S + slot]) - s_m[gh]) * s_linv[gh]);
-                    e[gh] = rnd<T>(__fmul_rn(pr, w0));
+        if (p.S % 8 == 0 && p.head_reduction != CKV_REDUCE_MEDIAN) {
+            // eight slots per thread: one 16-byte load per head row and one for the scores
+            const int nvec = p.S / 8;
+            const int per_block = (nvec + p.finish_chunks - 1) / p.finish_chunks;
+            const int v_end = min(nvec, (int)(blockIdx.x + 1) * per_block);
+            const bool is_max = p.head_reduction == CKV_REDUCE_MAX;
+            for (int v = blockIdx.x * per_block + tid; v < v_end; v += kFinishThreads) {
+                const int slot0 = v * 8;
+                uint4 sc4 = *reinterpret_cast<const uint4 *>(scr + slot0);
+                float acc[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] = is_max ? -INFINITY : 0.f;
+                if (slot0 < sc.total) {
+                    for (int gh = 0; gh < p.G; ++gh) {
+                        const uint4 l4 = *reinterpret_cast<const uint4 *>(lg + (long long)gh * p.S + slot0);
+                        const T *lv = reinterpret_cast<const T *>(&l4);
+                        const float mg = s_m[gh], li = s_linv[gh];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const float pr = rnd<T>(__expf(Elem<T>::to_f(lv[j]) - mg) * li);
+                            const float e = rnd<T>(__fmul_rn(pr, w0));
+                            acc[j] = is_max ? fmaxf(acc[j], e) : acc[j] + e;
+                        }
+                    }
                 }
-                red = rnd<T>(reduce_group(e, p.G, p.head_reduction));
+                T *sv = reinterpret_cast<T *>(&sc4);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    float red = 0.f;
+                    if (slot0 + j < sc.total) red = rnd<T>(is_max ? acc[j] : acc[j] / (float)p.G);
+                    const float decayed = rnd<T>(__fmul_rn(Elem<T>::to_f(sv[j]), p.beta_pow));
+                    sv[j] = Elem<T>::from_f(__fadd_rn(decayed, red));
+                }
+                *reinterpret_cast<uint4 *>(scr + slot0) = sc4;
             }
-            const float decayed = rnd<T>(__fmul_rn(Elem<T>::to_f(scr[slot]), p.beta_pow));
-            scr[slot] = Elem<T>::from_f(__fadd_rn(decayed, red));
+        } else {
+            const int per_block = (p.S + p.finish_chunks - 1) / p.finish_chunks;
+            const int s_end = min(p.S, (int)(blockIdx.x + 1) * per_block);
+            for (int slot = blockIdx.x * per_block + tid; slot < s_end; slot += kFinishThreads) {
+                float red = 0.f;
+                if (slot < sc.total) {
+                    float e[kMaxG];
+                    for (int gh = 0; gh < p.G; ++gh) {
+                        const float pr = rnd<T>(__expf(Elem<T>::to_f(lg[(long long)gh * p.S + slot]) - s_m[gh]) * s_linv[gh]);
+                        e[gh] = rnd<T>(__fmul_rn(pr, w0));
+                    }
+                    red = rnd<T>(reduce_group(e, p.G, p.head_reduction));
+                }
+                const float decayed = rnd<T>(__fmul_rn(Elem<T>::to_f(scr[slot]), p.beta_pow));
+                scr[slot] = Elem<T>::from_f(__fadd_rn(decayed, red));
+            }
         }
     }
 
@@ -749,10 +808,14 @@ int launch_decode_tuned(const Dims &d, const ckv_layer_state *st, const void *q,
 
     static bool attr_set = false;
     if (!attr_set) {
-        CKV_CUDA_CHECK(cudaFuncSetAttribute(decode_stream_kernel<__nv_bfloat16>,
+        CKV_CUDA_CHECK(cudaFuncSetAttribute(decode_stream_kernel<__nv_bfloat16, 1>,
                                             cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmem));
-        CKV_CUDA_CHECK(cudaFuncSetAttribute(decode_stream_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            kStreamSmem));
+        CKV_CUDA_CHECK(cudaFuncSetAttribute(decode_stream_kernel<__nv_bfloat16, 2>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmem));
+        CKV_CUDA_CHECK(cudaFuncSetAttribute(decode_stream_kernel<__half, 1>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmem));
+        CKV_CUDA_CHECK(cudaFuncSetAttribute(decode_stream_kernel<__half, 2>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmem));
         attr_set = true;
     }
     const uint64_t lanes = (uint64_t)d.B * d.KVH;
@@ -787,7 +850,7 @@ int launch_decode_tuned(const Dims &d, const ckv_layer_state *st, const void *q,
     p.stream_grid = sm_count();
     int chunks = 1;
     if (ema) {
-        chunks = (int)((4 * (uint64_t)sm_count() + lanes - 1) / lanes);
+        chunks = (int)((8 * (uint64_t)sm_count() + lanes - 1) / lanes);
         chunks = chunks < 1 ? 1 : (chunks > 64 ? 64 : chunks);
     }
     p.finish_chunks = chunks;
@@ -810,10 +873,14 @@ int launch_decode_tuned(const Dims &d, const ckv_layer_state *st, const void *q,
 
     CKV_CUDA_CHECK(cudaMemsetAsync(p.status, 0, 4, stream));
     if (hook) hook->before(stream, "decode_stream_kernel");
-    if (d.dtype == CKV_BF16)
-        decode_stream_kernel<__nv_bfloat16><<<p.stream_grid, kStreamThreads, kStreamSmem, stream>>>(tmK, tmV, tmSK, tmSV, p);
-    else
-        decode_stream_kernel<__half><<<p.stream_grid, kStreamThreads, kStreamSmem, stream>>>(tmK, tmV, tmSK, tmSV, p);
+    const bool hi = d.G > 8;
+    if (d.dtype == CKV_BF16) {
+        if (hi) decode_stream_kernel<__nv_bfloat16, 2><<<p.stream_grid, kStreamThreads, kStreamSmem, stream>>>(tmK, tmV, tmSK, tmSV, p);
+        else decode_stream_kernel<__nv_bfloat16, 1><<<p.stream_grid, kStreamThreads, kStreamSmem, stream>>>(tmK, tmV, tmSK, tmSV, p);
+    } else {
+        if (hi) decode_stream_kernel<__half, 2><<<p.stream_grid, kStreamThreads, kStreamSmem, stream>>>(tmK, tmV, tmSK, tmSV, p);
+        else decode_stream_kernel<__half, 1><<<p.stream_grid, kStreamThreads, kStreamSmem, stream>>>(tmK, tmV, tmSK, tmSV, p);
+    }
     if (hook) hook->after(stream);
     CKV_CUDA_CHECK(cudaGetLastError());
     const dim3 grid(chunks, (unsigned)lanes);
