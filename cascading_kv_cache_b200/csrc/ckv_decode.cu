@@ -62,6 +62,8 @@ struct DecodeParams {
     void *logits;                                // [B*H][S]
     float *partials;                             // [(grid + lanes)][warps][G][130]
     void *new_scores;                            // [B*KVH]
+    void *rope_slots;                            // [sink rows padded to 64 | S][128]: cos|sin per slot
+    int sink_rows_pad;
     int B, KVH, H, G, NS, W, C, S;
     int ema, update, head_reduction, eager_fill, dtype;
     int stream_grid, finish_chunks;
@@ -222,12 +224,35 @@ __device__ __forceinline__ long long cta_first_tile(long long cta, long long n_t
     return (cta * n_tiles) / grid;
 }
 
+// ------------------------------------------------------------------------------ rope pre-pass
+// Positions depend only on the slot, never on the lane: write the cos|sin row of every sink and
+// cache slot once per step, in slot order, so that the stream kernel can fetch them with TMA.
+__global__ void __launch_bounds__(256) rope_slots_kernel(DecodeParams p) {
+    const Schedule sc = make_schedule(p);
+    const int n_rows = p.sink_rows_pad + p.S;
+    const uint4 *rope = reinterpret_cast<const uint4 *>(p.rope);
+    uint4 *dst = reinterpret_cast<uint4 *>(p.rope_slots);
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < (long long)n_rows * 16;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const int row = (int)(idx >> 4), c = (int)(idx & 15);
+        long long pos = 0;
+        if (row < p.sink_rows_pad) {
+            if (row < sc.sinks) pos = p.sink_pos[row];
+        } else {
+            const int slot = row - p.sink_rows_pad;
+            if (slot < sc.total) pos = p.pos[slot] + sc.shift;
+        }
+        pos = pos < 0 ? 0 : (pos >= p.rope_rows ? p.rope_rows - 1 : pos);
+        dst[idx] = rope[pos * 16 + c];
+    }
+}
+
 // ------------------------------------------------------------------------------ stream kernel
 template <typename T, int kRowHalves>
 __global__ void __launch_bounds__(kStreamThreads, 1)
 decode_stream_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                      const __grid_constant__ CUtensorMap tmSK, const __grid_constant__ CUtensorMap tmSV,
-                     DecodeParams p) {
+                     const __grid_constant__ CUtensorMap tmR, DecodeParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint64_t *full = reinterpret_cast<uint64_t *>(smem + kStages * kStageBytes);
@@ -239,7 +264,7 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
-            mbar_init(&full[s], 33);   // 32 cp.async arrivals + the expect_tx arrival
+            mbar_init(&full[s], 1);    // the producer's expect_tx arrival; TMA completes the bytes
             mbar_init(&empty[s], kComputeWarps);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -252,7 +277,8 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
 
     if (warp == kComputeWarps) {
         // ------------------------------------------------------------------ producer warp
-        const uint8_t *rope = reinterpret_cast<const uint8_t *>(p.rope);
+        // one elected lane issues six TMA boxes per tile: K lo/hi, V lo/hi and the cos / sin rows of
+        // the tile's slots from the slot-ordered image the pre-pass wrote
         const uint64_t pol_stream = l2_policy_evict_first(), pol_keep = l2_policy_evict_last();
         int it = 0;
         for (long long t = t_begin; t < t_end; ++t, ++it) {
@@ -261,44 +287,25 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
             const int ti = (int)(t % sc.tiles_per_lane);
             const bool sink_tile = ti < sc.n_sink_tiles;
             const int row0 = sink_tile ? ti * kTile : (ti - sc.n_sink_tiles) * kTile;
-            // positions of rows lane_id and lane_id + 32: issued before the wait so that their
-            // latency hides behind it
-            long long pos[2];
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int idx = row0 + lane_id + 32 * h;
-                if (sink_tile) pos[h] = idx < sc.sinks ? p.sink_pos[idx] : 0;
-                else pos[h] = idx < sc.total ? p.pos[idx] + sc.shift : 0;
-            }
             if (it >= kStages) {
                 if (!mbar_wait(&empty[s], ((it / kStages) & 1) ^ 1, p.status)) break;
             }
             uint8_t *stage = smem + s * kStageBytes;
             if (lane_id == 0) {
-                mbar_expect_tx(&full[s], 4 * kSubBytes);
+                mbar_expect_tx(&full[s], 6 * kSubBytes);
                 const int y = sink_tile ? lane * p.NS + row0 : lane * p.S + row0;
+                const int yr = sink_tile ? row0 : p.sink_rows_pad + row0;
                 const CUtensorMap *mk = sink_tile ? &tmSK : &tmK;
                 const CUtensorMap *mv = sink_tile ? &tmSV : &tmV;
                 tma_load_2d(stage + kOffK, mk, 0, y, &full[s], pol_stream);
                 tma_load_2d(stage + kOffK + kSubBytes, mk, 64, y, &full[s], pol_stream);
                 tma_load_2d(stage + kOffV, mv, 0, y, &full[s], pol_stream);
                 tma_load_2d(stage + kOffV + kSubBytes, mv, 64, y, &full[s], pol_stream);
+                tma_load_2d(stage + kOffCos, &tmR, 0, yr, &full[s], pol_keep);
+                tma_load_2d(stage + kOffSin, &tmR, 64, yr, &full[s], pol_keep);
             }
-            // cos|sin rows of the tile's positions: 16 chunks of 16 bytes per row, swizzled like K
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int r = lane_id + 32 * h;
-                const long long ps = pos[h] < 0 ? 0 : (pos[h] >= p.rope_rows ? p.rope_rows - 1 : pos[h]);
-                const uint8_t *srow = rope + ps * 256;
-                uint8_t *drow = stage + r * 128;
-#pragma unroll
-                for (int c = 0; c < 16; ++c)
-                    cp_async_16(drow + (c < 8 ? kOffCos : kOffSin) + (((c & 7) ^ (r & 7)) << 4), srow + c * 16,
-                                pol_keep);
-            }
-            cp_async_arrive_noinc(&full[s]);
+            __syncwarp();
         }
-        asm volatile("cp.async.wait_all;" ::: "memory");
     } else {
         // ----------------------------------------------------------------- consumer warps
         const int g = lane_id >> 2, tq = lane_id & 3;
@@ -750,7 +757,7 @@ int make_rows_map(CUtensorMap *tm, const void *base, uint64_t rows, int dtype) {
 size_t up256(size_t x) { return (x + 255) & ~(size_t)255; }
 
 struct DecodeScratch {
-    size_t status, sync, logits, partials, new_scores, total;
+    size_t status, sync, logits, partials, new_scores, rope_slots, total;
 };
 
 int sm_count() {
@@ -763,6 +770,8 @@ int sm_count() {
     return n;
 }
 
+int sink_rows_padded(const Dims &d) { return ((d.NS + kTile - 1) / kTile) * kTile; }
+
 DecodeScratch decode_scratch(const Dims &d) {
     DecodeScratch s;
     const size_t lanes = (size_t)d.B * d.KVH;
@@ -772,6 +781,8 @@ DecodeScratch decode_scratch(const Dims &d) {
     s.logits = off; off += up256((size_t)d.B * d.H * d.S * 2);
     s.partials = off; off += up256((size_t)(sm_count() + lanes) * kComputeWarps * d.G * kPartialStride * 4);
     s.new_scores = off; off += up256(lanes * 2);
+    off = (off + 1023) & ~(size_t)1023;
+    s.rope_slots = off; off += up256((size_t)(sink_rows_padded(d) + d.S + kTile) * 256);
     s.total = off;
     return s;
 }
@@ -819,12 +830,14 @@ int launch_decode_tuned(const Dims &d, const ckv_layer_state *st, const void *q,
         attr_set = true;
     }
     const uint64_t lanes = (uint64_t)d.B * d.KVH;
-    CUtensorMap tmK, tmV, tmSK, tmSV;
+    CUtensorMap tmK, tmV, tmSK, tmSV, tmR;
     int rc;
     if ((rc = make_rows_map(&tmK, st->key_cache, lanes * d.S, d.dtype)) != CKV_OK) return rc;
     if ((rc = make_rows_map(&tmV, st->value_cache, lanes * d.S, d.dtype)) != CKV_OK) return rc;
     if ((rc = make_rows_map(&tmSK, st->sink_keys, lanes * d.NS, d.dtype)) != CKV_OK) return rc;
     if ((rc = make_rows_map(&tmSV, st->sink_values, lanes * d.NS, d.dtype)) != CKV_OK) return rc;
+    if ((rc = make_rows_map(&tmR, (uint8_t *)workspace + s.rope_slots, (uint64_t)sink_rows_padded(d) + d.S, d.dtype)) != CKV_OK)
+        return rc;
 
     uint8_t *ws = (uint8_t *)workspace;
     DecodeParams p;
@@ -844,6 +857,8 @@ int launch_decode_tuned(const Dims &d, const ckv_layer_state *st, const void *q,
     p.logits = ws + s.logits;
     p.partials = (float *)(ws + s.partials);
     p.new_scores = ws + s.new_scores;
+    p.rope_slots = ws + s.rope_slots;
+    p.sink_rows_pad = sink_rows_padded(d);
     p.B = d.B; p.KVH = d.KVH; p.H = d.H; p.G = d.G; p.NS = d.NS; p.W = d.W; p.C = d.C; p.S = d.S;
     p.ema = ema; p.update = update; p.head_reduction = d.head_reduction; p.eager_fill = d.eager_fill;
     p.dtype = d.dtype;
@@ -872,14 +887,21 @@ int launch_decode_tuned(const Dims &d, const ckv_layer_state *st, const void *q,
     u.row_bytes = 256; u.esz = 2; u.dtype = d.dtype; u.eager_fill = d.eager_fill;
 
     CKV_CUDA_CHECK(cudaMemsetAsync(p.status, 0, 4, stream));
+    {
+        const long long work = (long long)(p.sink_rows_pad + d.S) * 16;
+        int blocks = (int)((work + 255) / 256);
+        blocks = blocks > 8 * sm_count() ? 8 * sm_count() : blocks;
+        rope_slots_kernel<<<blocks, 256, 0, stream>>>(p);
+        CKV_CUDA_CHECK(cudaGetLastError());
+    }
     if (hook) hook->before(stream, "decode_stream_kernel");
     const bool hi = d.G > 8;
     if (d.dtype == CKV_BF16) {
-        if (hi) decode_stream_kernel<__nv_bfloat16, 2><<<p.stream_grid, kStreamThreads, kStreamSmem, stream>>>(tmK, tmV, tmSK, tmSV, p);
-        else decode_stream_kernel<__nv_bfloat16, 1><<<p.stream_grid, kStreamThreads, kStreamSmem, stream>>>(tmK, tmV, tmSK, tmSV, p);
+        if (hi) decode_stream_kernel<__nv_bfloat16, 2><<<p.stream_grid, kStreamThreads, kStreamSmem, stream>>>(tmK, tmV, tmSK, tmSV, tmR, p);
+        else decode_stream_kernel<__nv_bfloat16, 1><<<p.stream_grid, kStreamThreads, kStreamSmem, stream>>>(tmK, tmV, tmSK, tmSV, tmR, p);
     } else {
-        if (hi) decode_stream_kernel<__half, 2><<<p.stream_grid, kStreamThreads, kStreamSmem, stream>>>(tmK, tmV, tmSK, tmSV, p);
-        else decode_stream_kernel<__half, 1><<<p.stream_grid, kStreamThreads, kStreamSmem, stream>>>(tmK, tmV, tmSK, tmSV, p);
+        if (hi) decode_stream_kernel<__half, 2><<<p.stream_grid, kStreamThreads, kStreamSmem, stream>>>(tmK, tmV, tmSK, tmSV, tmR, p);
+        else decode_stream_kernel<__half, 1><<<p.stream_grid, kStreamThreads, kStreamSmem, stream>>>(tmK, tmV, tmSK, tmSV, tmR, p);
     }
     if (hook) hook->after(stream);
     CKV_CUDA_CHECK(cudaGetLastError());
@@ -887,7 +909,7 @@ int launch_decode_tuned(const Dims &d, const ckv_layer_state *st, const void *q,
     if (d.dtype == CKV_BF16) decode_finish_kernel<__nv_bfloat16><<<grid, kFinishThreads, 0, stream>>>(p);
     else decode_finish_kernel<__half><<<grid, kFinishThreads, 0, stream>>>(p);
     CKV_CUDA_CHECK(cudaGetLastError());
-    note_launches(2);
+    note_launches(3);
     return CKV_OK;
 }
 
