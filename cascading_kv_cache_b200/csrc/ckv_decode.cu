@@ -34,9 +34,10 @@ constexpr int kStreamThreads = (kComputeWarps + 1) * 32;
 constexpr int kSubBytes = kTile * 128;          // one swizzled 64-row x 128-byte sub-tile
 constexpr int kStageBytes = 6 * kSubBytes;      // K lo | K hi | V lo | V hi | cos | sin
 constexpr int kOffK = 0, kOffV = 2 * kSubBytes, kOffCos = 4 * kSubBytes, kOffSin = 5 * kSubBytes;
-constexpr int kStreamSmem = kStages * kStageBytes + 1024 + 256;
-constexpr int kPartialStride = 130;             // m, l, out[128] per head row
 constexpr int kMaxG = 16;
+constexpr int kMergeBytes = (kMaxG * 128 + 2 * kComputeWarps * kMaxG) * 4;  // out[16][128] + m,l per warp
+constexpr int kStreamSmem = kStages * kStageBytes + 1024 + 256 + kMergeBytes;
+constexpr int kPartialStride = 130;             // m, l, out[128] per head row
 constexpr unsigned kSpinLimit = 1u << 24;       // bounded mbarrier waits (each probe also sleeps)
 constexpr int kFinishThreads = 256;
 
@@ -60,7 +61,7 @@ struct DecodeParams {
     int *status;                                 // [0] error flag
     unsigned int *sync;                          // [0] lanes done, [1 + lane] blocks done
     void *logits;                                // [B*H][S]
-    float *partials;                             // [(grid + lanes)][warps][G][130]
+    float *partials;                             // [(grid + lanes)][G][130]: one per (CTA, lane) segment
     void *new_scores;                            // [B*KVH]
     void *rope_slots;                            // [sink rows padded to 64 | S][128]: cos|sin per slot
     int sink_rows_pad;
@@ -280,11 +281,10 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         // one elected lane issues six TMA boxes per tile: K lo/hi, V lo/hi and the cos / sin rows of
         // the tile's slots from the slot-ordered image the pre-pass wrote
         const uint64_t pol_stream = l2_policy_evict_first(), pol_keep = l2_policy_evict_last();
-        int it = 0;
-        for (long long t = t_begin; t < t_end; ++t, ++it) {
+        int lane = (int)(t_begin / sc.tiles_per_lane), ti = (int)(t_begin % sc.tiles_per_lane);
+        const int n_it = (int)(t_end - t_begin);
+        for (int it = 0; it < n_it; ++it) {
             const int s = it % kStages;
-            const int lane = (int)(t / sc.tiles_per_lane);
-            const int ti = (int)(t % sc.tiles_per_lane);
             const bool sink_tile = ti < sc.n_sink_tiles;
             const int row0 = sink_tile ? ti * kTile : (ti - sc.n_sink_tiles) * kTile;
             if (it >= kStages) {
@@ -305,6 +305,10 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
                 tma_load_2d(stage + kOffSin, &tmR, 64, yr, &full[s], pol_keep);
             }
             __syncwarp();
+            if (++ti == sc.tiles_per_lane) {
+                ti = 0;
+                ++lane;
+            }
         }
     } else {
         // ----------------------------------------------------------------- consumer warps
@@ -316,35 +320,66 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         int cur_lane = -1;
         T *logits = reinterpret_cast<T *>(p.logits);
 
+        float *mg_out = reinterpret_cast<float *>(smem + kStages * kStageBytes + 256);   // [kMaxG][128]
+        float *mg_m = mg_out + kMaxG * 128;                                              // [warps][kMaxG]
+        float *mg_l = mg_m + kComputeWarps * kMaxG;
+        const int ctid = threadIdx.x;  // consumer threads are 0 .. 255
+        auto consumer_sync = [&]() { asm volatile("bar.sync 1, %0;" ::"n"(kComputeWarps * 32) : "memory"); };
+
+        // Merge the eight warps' (max, sum, out) of one (CTA, lane) segment in shared memory and
+        // write a single partial.  Runs once per segment, i.e. every few hundred tiles.
         auto flush = [&](int lane) {
-            // quad-reduce the row sums, then write this warp's partial of (CTA, lane)
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
                 l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
                 l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
             }
-            float *base = p.partials + ((long long)(blockIdx.x + lane) * kComputeWarps + warp) * p.G * kPartialStride;
+            for (int i = ctid; i < kMaxG * 128; i += kComputeWarps * 32) mg_out[i] = 0.f;
+            if (tq == 0) {
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    mg_m[warp * kMaxG + g + 8 * r] = m_run[r];
+                    mg_l[warp * kMaxG + g + 8 * r] = l_run[r];
+                }
+            }
+            consumer_sync();
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
                 const int row = g + 8 * r;
                 if (row < p.G) {
-                    float *pr = base + row * kPartialStride;
-                    if (tq == 0) {
-                        pr[0] = m_run[r];
-                        pr[1] = l_run[r];
-                    }
+                    float mx = -INFINITY;
 #pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        *reinterpret_cast<float2 *>(pr + 2 + 8 * j + 2 * tq) = make_float2(o[j][2 * r], o[j][2 * r + 1]);
+                    for (int w = 0; w < kComputeWarps; ++w) mx = fmaxf(mx, mg_m[w * kMaxG + row]);
+                    const float sc_w = (m_run[r] == -INFINITY) ? 0.f : __expf(m_run[r] - mx);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        atomicAdd(&mg_out[row * 128 + 8 * j + 2 * tq], o[j][2 * r] * sc_w);
+                        atomicAdd(&mg_out[row * 128 + 8 * j + 2 * tq + 1], o[j][2 * r + 1] * sc_w);
+                    }
                 }
             }
+            consumer_sync();
+            float *base = p.partials + (long long)(blockIdx.x + lane) * p.G * kPartialStride;
+            for (int i = ctid; i < p.G * 128; i += kComputeWarps * 32)
+                base[(i >> 7) * kPartialStride + 2 + (i & 127)] = mg_out[i];
+            if (ctid < p.G) {
+                float mx = -INFINITY, l = 0.f;
+                for (int w = 0; w < kComputeWarps; ++w) mx = fmaxf(mx, mg_m[w * kMaxG + ctid]);
+                for (int w = 0; w < kComputeWarps; ++w) {
+                    const float mw = mg_m[w * kMaxG + ctid];
+                    if (mw != -INFINITY) l += mg_l[w * kMaxG + ctid] * __expf(mw - mx);
+                }
+                base[ctid * kPartialStride] = mx;
+                base[ctid * kPartialStride + 1] = l;
+            }
+            consumer_sync();
         };
 
-        int it = 0;
-        for (long long t = t_begin; t < t_end; ++t, ++it) {
+        int lane = (int)(t_begin / sc.tiles_per_lane), ti = (int)(t_begin % sc.tiles_per_lane);
+        const int n_it = (int)(t_end - t_begin);
+        bool failed = false;
+        for (int it = 0; it < n_it; ++it) {
             const int s = it % kStages;
-            const int lane = (int)(t / sc.tiles_per_lane);
-            const int ti = (int)(t % sc.tiles_per_lane);
             if (lane != cur_lane) {
                 if (cur_lane >= 0) flush(cur_lane);
                 cur_lane = lane;
@@ -380,7 +415,10 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
                     }
                 }
             }
-            if (!mbar_wait(&full[s], (it / kStages) & 1, p.status)) break;
+            if (!mbar_wait(&full[s], (it / kStages) & 1, p.status)) {
+                failed = true;
+                break;
+            }
 
             const bool sink_tile = ti < sc.n_sink_tiles;
             const int row0 = sink_tile ? ti * kTile : (ti - sc.n_sink_tiles) * kTile;
@@ -474,8 +512,14 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
             }
             __syncwarp();
             if (lane_id == 0) mbar_arrive(&empty[s]);
+            if (++ti == sc.tiles_per_lane) {
+                ti = 0;
+                ++lane;
+            }
         }
-        if (cur_lane >= 0) flush(cur_lane);
+        // a failed wait already raised the status flag; the warps then leave without the block-wide
+        // merge (its barrier could otherwise wait for warps that left through another path)
+        if (cur_lane >= 0 && !failed && *((volatile int *)p.status) == 0) flush(cur_lane);
     }
 }
 
@@ -552,29 +596,36 @@ __global__ void __launch_bounds__(kFinishThreads) decode_finish_kernel(DecodePar
         cta_hi = cta_lo;
         while (cta_hi + 1 < p.stream_grid && cta_first_tile(cta_hi + 1, sc.n_tiles, p.stream_grid) < b_tile) ++cta_hi;
     }
-    // partial i of the lane: CTA cta_lo + i/warps, warp i%warps; CTAs with an empty range wrote nothing
-    const int n_parts = (cta_hi - cta_lo + 1) * kComputeWarps;
+    // partial i of the lane comes from CTA cta_lo + i; CTAs with an empty tile range wrote nothing
+    const int n_parts = cta_hi - cta_lo + 1;
     auto part = [&](int i, int row) -> const float * {
-        const int c = cta_lo + i / kComputeWarps;
+        const int c = cta_lo + i;
         if (cta_first_tile(c, sc.n_tiles, p.stream_grid) >= cta_first_tile(c + 1, sc.n_tiles, p.stream_grid))
             return nullptr;
-        return p.partials + ((long long)(cta_lo + lane) * kComputeWarps + i) * p.G * kPartialStride +
-               row * kPartialStride;
+        return p.partials + (long long)(c + lane) * p.G * kPartialStride + row * kPartialStride;
     };
-    if (tid < p.G) {
-        float m = s_snew[tid];
-        for (int i = 0; i < n_parts; ++i) {
-            const float *pr = part(i, tid);
+    // one warp per head: lanes stride over the partials
+    for (int gh = warp; gh < p.G; gh += kFinishThreads / 32) {
+        float m = s_snew[gh];
+        for (int i = lane_id; i < n_parts; i += 32) {
+            const float *pr = part(i, gh);
             if (pr) m = fmaxf(m, pr[0]);
         }
-        float l = __expf(s_snew[tid] - m);
-        for (int i = 0; i < n_parts; ++i) {
-            const float *pr = part(i, tid);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+        float l = 0.f;
+        for (int i = lane_id; i < n_parts; i += 32) {
+            const float *pr = part(i, gh);
             if (pr && pr[0] != -INFINITY) l += pr[1] * __expf(pr[0] - m);
         }
-        s_m[tid] = m;
-        s_linv[tid] = 1.f / l;
-        s_pnew[tid] = __expf(s_snew[tid] - m) / l;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
+        l += __expf(s_snew[gh] - m);
+        if (lane_id == 0) {
+            s_m[gh] = m;
+            s_linv[gh] = 1.f / l;
+            s_pnew[gh] = __expf(s_snew[gh] - m) / l;
+        }
     }
     __syncthreads();
 
@@ -779,7 +830,7 @@ DecodeScratch decode_scratch(const Dims &d) {
     s.status = off; off += 256;
     s.sync = off; off += up256((1 + lanes) * 4);
     s.logits = off; off += up256((size_t)d.B * d.H * d.S * 2);
-    s.partials = off; off += up256((size_t)(sm_count() + lanes) * kComputeWarps * d.G * kPartialStride * 4);
+    s.partials = off; off += up256((size_t)(sm_count() + lanes) * d.G * kPartialStride * 4);
     s.new_scores = off; off += up256(lanes * 2);
     off = (off + 1023) & ~(size_t)1023;
     s.rope_slots = off; off += up256((size_t)(sink_rows_padded(d) + d.S + kTile) * 256);
