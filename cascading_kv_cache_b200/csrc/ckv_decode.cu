@@ -29,7 +29,9 @@ namespace {
 
 constexpr int kTile = 64;                       // keys per stage
 constexpr int kStages = 4;
-constexpr int kComputeWarps = 8;                // each owns 8 keys of a tile
+constexpr int kGroupWarps = 8;                  // warps per consumer group: each owns 8 keys of a tile
+constexpr int kGroups = 2;                      // consumer groups working on alternate tiles
+constexpr int kComputeWarps = kGroupWarps * kGroups;
 constexpr int kStreamThreads = (kComputeWarps + 1) * 32;
 constexpr int kSubBytes = kTile * 128;          // one swizzled 64-row x 128-byte sub-tile
 constexpr int kStageBytes = 6 * kSubBytes;      // K lo | K hi | V lo | V hi | cos | sin
@@ -266,7 +268,7 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(&full[s], 1);    // the producer's expect_tx arrival; TMA completes the bytes
-            mbar_init(&empty[s], kComputeWarps);
+            mbar_init(&empty[s], kGroupWarps);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -312,22 +314,34 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         }
     } else {
         // ----------------------------------------------------------------- consumer warps
+        // Two groups of eight warps take alternate tiles; inside a group warp wk owns keys
+        // [8 wk, 8 wk + 8) of the tile.  Every warp walks all iterations so that lane changes (and
+        // the block-wide merge they trigger) are seen by all warps alike.
         const int g = lane_id >> 2, tq = lane_id & 3;
+        const int group = warp / kGroupWarps, wk = warp % kGroupWarps;
         const T *rope = reinterpret_cast<const T *>(p.rope);
         uint32_t qa[8][4];
-        float o[16][4];
+        float ot[kRowHalves][8][4];   // out^T: [dims 16 mt + g (+8)][heads 8 nh + 2 tq (+1)]
         float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
         int cur_lane = -1;
-        T *logits = reinterpret_cast<T *>(p.logits);
+        T *lrow[2] = {nullptr, nullptr};
 
         float *mg_out = reinterpret_cast<float *>(smem + kStages * kStageBytes + 256);   // [kMaxG][128]
         float *mg_m = mg_out + kMaxG * 128;                                              // [warps][kMaxG]
         float *mg_l = mg_m + kComputeWarps * kMaxG;
-        const int ctid = threadIdx.x;  // consumer threads are 0 .. 255
+        const int ctid = threadIdx.x;  // consumer threads are 0 .. kComputeWarps*32 - 1
         auto consumer_sync = [&]() { asm volatile("bar.sync 1, %0;" ::"n"(kComputeWarps * 32) : "memory"); };
 
-        // Merge the eight warps' (max, sum, out) of one (CTA, lane) segment in shared memory and
-        // write a single partial.  Runs once per segment, i.e. every few hundred tiles.
+        // loop-invariant shared-memory offsets of this thread's ldmatrix rows
+        const int krow = 8 * wk + (lane_id & 7);
+        const uint32_t rowoff = krow * 128;
+        const int sw = krow & 7;
+        uint32_t choff[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) choff[u] = rowoff + (uint32_t)(((4 * u + (lane_id >> 3)) ^ sw) << 4);
+
+        // Merge all warps' (max, sum, out) of one (CTA, lane) segment in shared memory and write a
+        // single partial.  Runs once per segment, i.e. every few hundred tiles.
         auto flush = [&](int lane) {
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
@@ -344,17 +358,20 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
             }
             consumer_sync();
 #pragma unroll
-            for (int r = 0; r < 2; ++r) {
-                const int row = g + 8 * r;
-                if (row < p.G) {
-                    float mx = -INFINITY;
+            for (int nh = 0; nh < kRowHalves; ++nh) {
 #pragma unroll
-                    for (int w = 0; w < kComputeWarps; ++w) mx = fmaxf(mx, mg_m[w * kMaxG + row]);
-                    const float sc_w = (m_run[r] == -INFINITY) ? 0.f : __expf(m_run[r] - mx);
+                for (int e = 0; e < 2; ++e) {
+                    const int head = 8 * nh + 2 * tq + e;
+                    if (head < p.G) {
+                        float mx = -INFINITY;
+                        for (int w = 0; w < kComputeWarps; ++w) mx = fmaxf(mx, mg_m[w * kMaxG + head]);
+                        const float mine = mg_m[warp * kMaxG + head];
+                        const float sc_w = (mine == -INFINITY) ? 0.f : __expf(mine - mx);
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        atomicAdd(&mg_out[row * 128 + 8 * j + 2 * tq], o[j][2 * r] * sc_w);
-                        atomicAdd(&mg_out[row * 128 + 8 * j + 2 * tq + 1], o[j][2 * r + 1] * sc_w);
+                        for (int mt = 0; mt < 8; ++mt) {
+                            atomicAdd(&mg_out[head * 128 + 16 * mt + g], ot[nh][mt][e] * sc_w);
+                            atomicAdd(&mg_out[head * 128 + 16 * mt + g + 8], ot[nh][mt][2 + e] * sc_w);
+                        }
                     }
                 }
             }
@@ -386,14 +403,17 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
                 m_run[0] = m_run[1] = -INFINITY;
                 l_run[0] = l_run[1] = 0.f;
 #pragma unroll
-                for (int j = 0; j < 16; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+                for (int nh = 0; nh < kRowHalves; ++nh)
+#pragma unroll
+                    for (int mt = 0; mt < 8; ++mt) ot[nh][mt][0] = ot[nh][mt][1] = ot[nh][mt][2] = ot[nh][mt][3] = 0.f;
                 // A fragments of q (rows = heads of the group), rotated at max_pos and scaled
                 const int b = lane / p.KVH, kvh = lane % p.KVH;
                 const T *crow = rope + (sc.max_pos < p.rope_rows ? sc.max_pos : p.rope_rows - 1) * 128;
 #pragma unroll
                 for (int r = 0; r < 2; ++r) {
                     const int row = g + 8 * r;
-                    if (row < p.G) {
+                    lrow[r] = reinterpret_cast<T *>(p.logits) + ((long long)b * p.H + kvh * p.G + row) * p.S;
+                    if (r < kRowHalves && row < p.G) {
                         const T *qrow = reinterpret_cast<const T *>(p.q) + b * p.qsb + (long long)(kvh * p.G + row) * p.qsh;
 #pragma unroll
                         for (int ks = 0; ks < 4; ++ks) {
@@ -415,103 +435,108 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
                     }
                 }
             }
-            if (!mbar_wait(&full[s], (it / kStages) & 1, p.status)) {
-                failed = true;
-                break;
-            }
-
-            const bool sink_tile = ti < sc.n_sink_tiles;
-            const int row0 = sink_tile ? ti * kTile : (ti - sc.n_sink_tiles) * kTile;
-            const long long limit = sink_tile ? sc.sinks : sc.total;
-            const int nvalid = (int)(limit - row0 < kTile ? limit - row0 : kTile);
-            const int key0 = 8 * warp;
-            if (key0 < nvalid) {
-                const uint32_t stage = smem_u32(smem + s * kStageBytes);
-                const int krow = key0 + (lane_id & 7);
-                const uint32_t rowoff = krow * 128;
-                const int sw = krow & 7;
-                float sacc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                for (int u = 0; u < 2; ++u) {
-                    // k-steps 2u, 2u+1 (dims < 64) with their partners 2u+4, 2u+5 (dims + 64)
-                    const uint32_t choff = (uint32_t)(((4 * u + (lane_id >> 3)) ^ sw) << 4);
-                    uint32_t kl[4], kh[4], cs[4], sn[4];
-                    ldsm_x4(stage + kOffK + rowoff + choff, kl[0], kl[1], kl[2], kl[3]);
-                    ldsm_x4(stage + kOffK + kSubBytes + rowoff + choff, kh[0], kh[1], kh[2], kh[3]);
-                    ldsm_x4(stage + kOffCos + rowoff + choff, cs[0], cs[1], cs[2], cs[3]);
-                    ldsm_x4(stage + kOffSin + rowoff + choff, sn[0], sn[1], sn[2], sn[3]);
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) rope_pair<T>(kl[e], kh[e], cs[e], sn[e], p.rs);
-                    Mma<T>::run(sacc, qa[2 * u], kl[0], kl[1]);
-                    Mma<T>::run(sacc, qa[2 * u + 1], kl[2], kl[3]);
-                    Mma<T>::run(sacc, qa[2 * u + 4], kh[0], kh[1]);
-                    Mma<T>::run(sacc, qa[2 * u + 5], kh[2], kh[3]);
+            if ((it & (kGroups - 1)) == group) {
+                if (!mbar_wait(&full[s], (it / kStages) & 1, p.status)) {
+                    failed = true;
+                    break;
                 }
-                // logits rounded to T (the reference's einsum output), masked past the valid keys
+                const bool sink_tile = ti < sc.n_sink_tiles;
+                const int row0 = sink_tile ? ti * kTile : (ti - sc.n_sink_tiles) * kTile;
+                const long long limit = sink_tile ? sc.sinks : sc.total;
+                const int nvalid = (int)(limit - row0 < kTile ? limit - row0 : kTile);
+                const int key0 = 8 * wk;
+                if (key0 < nvalid) {
+                    const uint32_t stage = smem_u32(smem + s * kStageBytes);
+                    float sacc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int key = key0 + 2 * tq + (e & 1);
-                    sacc[e] = key < nvalid ? rnd<T>(sacc[e]) : -INFINITY;
-                }
-                if (p.ema && !sink_tile) {
-                    const int b = lane / p.KVH, kvh = lane % p.KVH;
+                    for (int u = 0; u < 2; ++u) {
+                        // k-steps 2u, 2u+1 (dims < 64) with their partners 2u+4, 2u+5 (dims + 64)
+                        uint32_t kl[4], kh[4], cs[4], sn[4];
+                        ldsm_x4(stage + kOffK + choff[u], kl[0], kl[1], kl[2], kl[3]);
+                        ldsm_x4(stage + kOffK + kSubBytes + choff[u], kh[0], kh[1], kh[2], kh[3]);
+                        ldsm_x4(stage + kOffCos + choff[u], cs[0], cs[1], cs[2], cs[3]);
+                        ldsm_x4(stage + kOffSin + choff[u], sn[0], sn[1], sn[2], sn[3]);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) rope_pair<T>(kl[e], kh[e], cs[e], sn[e], p.rs);
+                        Mma<T>::run(sacc, qa[2 * u], kl[0], kl[1]);
+                        Mma<T>::run(sacc, qa[2 * u + 1], kl[2], kl[3]);
+                        Mma<T>::run(sacc, qa[2 * u + 4], kh[0], kh[1]);
+                        Mma<T>::run(sacc, qa[2 * u + 5], kh[2], kh[3]);
+                    }
+                    // logits rounded to T (the reference's einsum output), masked past the valid keys
+                    const int kk = key0 + 2 * tq;
+#pragma unroll
+                    for (int e = 0; e < 2 * kRowHalves; ++e) sacc[e] = (kk + (e & 1)) < nvalid ? rnd<T>(sacc[e]) : -INFINITY;
+                    if (p.ema && !sink_tile) {
+                        const int slot = row0 + kk;
+#pragma unroll
+                        for (int r = 0; r < kRowHalves; ++r) {
+                            if (g + 8 * r < p.G) {
+                                if (slot + 1 < p.S) {
+                                    typename Pack<T>::T2 v = Pack<T>::from_f2(make_float2(sacc[2 * r], sacc[2 * r + 1]));
+                                    *reinterpret_cast<typename Pack<T>::T2 *>(lrow[r] + slot) = v;
+                                } else if (slot < p.S) {
+                                    lrow[r][slot] = Elem<T>::from_f(sacc[2 * r]);
+                                }
+                            }
+                        }
+                    }
+                    // online softmax over this warp's 8 keys; P^T (keys x heads) is the B operand of PV
+                    uint32_t pb[kRowHalves];
+                    float corr[kRowHalves];
+                    bool rescale = false;
 #pragma unroll
                     for (int r = 0; r < kRowHalves; ++r) {
-                        const int row = g + 8 * r;
-                        if (row < p.G) {
-                            T *lrow = logits + ((long long)b * p.H + kvh * p.G + row) * p.S;
-                            const int slot = row0 + key0 + 2 * tq;
-                            if (slot + 1 < p.S) {
-                                typename Pack<T>::T2 v = Pack<T>::from_f2(make_float2(sacc[2 * r], sacc[2 * r + 1]));
-                                *reinterpret_cast<typename Pack<T>::T2 *>(lrow + slot) = v;
-                            } else if (slot < p.S) {
-                                lrow[slot] = Elem<T>::from_f(sacc[2 * r]);
+                        float mx = fmaxf(sacc[2 * r], sacc[2 * r + 1]);
+                        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                        const float m_new = fmaxf(m_run[r], mx);
+                        float p0 = 0.f, p1 = 0.f;
+                        corr[r] = 1.f;
+                        if (m_new != -INFINITY) {
+                            corr[r] = __expf(m_run[r] - m_new);
+                            p0 = __expf(sacc[2 * r] - m_new);
+                            p1 = __expf(sacc[2 * r + 1] - m_new);
+                        }
+                        m_run[r] = m_new;
+                        l_run[r] = l_run[r] * corr[r] + (p0 + p1);
+                        rescale |= corr[r] != 1.f;
+                        pb[r] = Pack<T>::to_u(Pack<T>::from_f2(make_float2(p0, p1)));
+                    }
+                    if (__any_sync(0xffffffffu, rescale)) {  // the running max rarely moves
+#pragma unroll
+                        for (int nh = 0; nh < kRowHalves; ++nh) {
+                            // this thread's out^T columns are heads 8 nh + 2 tq (+1); their factors sit in
+                            // the lanes whose row g is that head
+                            const float ca = __shfl_sync(0xffffffffu, corr[nh], (2 * tq) * 4);
+                            const float cb = __shfl_sync(0xffffffffu, corr[nh], (2 * tq + 1) * 4);
+#pragma unroll
+                            for (int mt = 0; mt < 8; ++mt) {
+                                ot[nh][mt][0] *= ca;
+                                ot[nh][mt][1] *= cb;
+                                ot[nh][mt][2] *= ca;
+                                ot[nh][mt][3] *= cb;
+                            }
+                        }
+                    }
+                    // out^T (128 dims x heads) += V^T (128 x 8 keys) * P^T (8 keys x heads)
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+#pragma unroll
+                        for (int cq = 0; cq < 2; ++cq) {
+                            uint32_t v0, v1, v2, v3;
+                            ldsm_x4_t(stage + kOffV + half * kSubBytes + choff[cq], v0, v1, v2, v3);
+#pragma unroll
+                            for (int nh = 0; nh < kRowHalves; ++nh) {
+                                MmaK8<T>::run(ot[nh][4 * half + 2 * cq], v0, v1, pb[nh]);
+                                MmaK8<T>::run(ot[nh][4 * half + 2 * cq + 1], v2, v3, pb[nh]);
                             }
                         }
                     }
                 }
-                // online softmax over this warp's 8 keys (rows g, and g+8 when the group is larger than 8)
-                uint32_t pa[2] = {0u, 0u};
-#pragma unroll
-                for (int r = 0; r < kRowHalves; ++r) {
-                    float mx = fmaxf(sacc[2 * r], sacc[2 * r + 1]);
-                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-                    const float m_new = fmaxf(m_run[r], mx);
-                    float corr = 1.f, p0 = 0.f, p1 = 0.f;
-                    if (m_new != -INFINITY) {
-                        corr = __expf(m_run[r] - m_new);
-                        p0 = __expf(sacc[2 * r] - m_new);
-                        p1 = __expf(sacc[2 * r + 1] - m_new);
-                    }
-                    m_run[r] = m_new;
-                    l_run[r] = l_run[r] * corr + (p0 + p1);
-                    if (__any_sync(0xffffffffu, corr != 1.f)) {  // the running max rarely moves
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            o[j][2 * r] *= corr;
-                            o[j][2 * r + 1] *= corr;
-                        }
-                    }
-                    pa[r] = Pack<T>::to_u(Pack<T>::from_f2(make_float2(p0, p1)));
-                }
-                // out += P (16 x 8 keys) * V (8 keys x 128)
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
-#pragma unroll
-                    for (int cq = 0; cq < 2; ++cq) {
-                        const uint32_t choff = (uint32_t)(((4 * cq + (lane_id >> 3)) ^ sw) << 4);
-                        uint32_t v0, v1, v2, v3;
-                        ldsm_x4_t(stage + kOffV + half * kSubBytes + rowoff + choff, v0, v1, v2, v3);
-                        MmaK8<T>::run(o[8 * half + 4 * cq], pa[0], pa[1], v0);
-                        MmaK8<T>::run(o[8 * half + 4 * cq + 1], pa[0], pa[1], v1);
-                        MmaK8<T>::run(o[8 * half + 4 * cq + 2], pa[0], pa[1], v2);
-                        MmaK8<T>::run(o[8 * half + 4 * cq + 3], pa[0], pa[1], v3);
-                    }
-                }
+                __syncwarp();
+                if (lane_id == 0) mbar_arrive(&empty[s]);
             }
-            __syncwarp();
-            if (lane_id == 0) mbar_arrive(&empty[s]);
             if (++ti == sc.tiles_per_lane) {
                 ti = 0;
                 ++lane;
