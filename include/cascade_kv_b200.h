@@ -157,6 +157,39 @@ int ckv_attention(const ckv_config *cfg, const ckv_layer_state *st,
                   void *workspace, size_t workspace_bytes,
                   int32_t flags, void *cuda_stream);
 
+/*
+ * ckv_attention for callers that may not allocate device memory.
+ * (No counterpart in the reference, whose Python layer allocates freely through torch.)
+ *
+ * Some hosts of this library cannot give it a workspace: a serving runtime that sized all of its
+ * device memory at start-up and forbids allocation afterwards, a plugin loaded into a process
+ * whose allocator it may not touch, or code running between the capture-safe calls of a
+ * framework.  For them the scratch comes from a fixed array of CKV_STATIC_SCRATCH_BYTES bytes
+ * that is part of this library's device image: every GPU that loads the library holds those bytes
+ * until the process exits.  Arguments are those of ckv_attention minus the workspace pair.
+ *
+ *  - Configurations whose ckv_attention_workspace_bytes() exceeds CKV_STATIC_SCRATCH_BYTES are
+ *    refused with CKV_E_WORKSPACE; use ckv_attention with your own buffer for those.
+ *  - The first call on each device looks up the array's device address (with that device
+ *    current); make that first call outside any stream capture.
+ *  - No cudaMalloc, cudaFree or other allocating routine is called, on any call.
+ *  - All calls on a device share the one array, and it keeps whatever the previous call left;
+ *    the words that must start at zero are cleared on the stream at the start of every call.
+ *    Two calls that can overlap on the GPU (different streams, no ordering between them) would
+ *    race on the array: order them.
+ */
+#define CKV_STATIC_SCRATCH_BYTES (8u << 20)
+size_t ckv_static_scratch_bytes(void);
+int ckv_attention_static(const ckv_config *cfg, const ckv_layer_state *st,
+                         const void *q, int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_t,
+                         const void *key, const void *value,
+                         int64_t kv_stride_b, int64_t kv_stride_h, int64_t kv_stride_t,
+                         int32_t n_tokens,
+                         const void *rope, int64_t rope_rows,
+                         const float *ema_w_cache, const void *ema_w_new,
+                         void *out, int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_t,
+                         int32_t flags, void *cuda_stream);
+
 /* Number of kernels the calling thread's last ckv_attention / ckv_cascade_update call launched. */
 int ckv_last_launch_count(void);
 
