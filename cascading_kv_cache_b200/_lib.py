@@ -11,7 +11,8 @@ import os
 import torch
 
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(PKG_DIR, "libckv_b200.so")
+# CKV_B200_LIB points at another build of the library (A/B timing of kernel variants)
+LIB_PATH = os.environ.get("CKV_B200_LIB") or os.path.join(PKG_DIR, "libckv_b200.so")
 
 CKV_F32, CKV_F16, CKV_BF16 = 0, 1, 2
 CKV_REDUCE = {"mean": 0, "max": 1, "median": 2}

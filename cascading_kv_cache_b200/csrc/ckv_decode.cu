@@ -213,7 +213,7 @@ __device__ __forceinline__ Schedule make_schedule(const DecodeParams &p) {
     s.seen = *p.seen;
     s.sinks = *p.stored_sinks;
     s.total = 0;
-    for (int i = 0; i < p.C; ++i) s.total += p.stored_tokens[i];
+    for (int i = 0; i < p.C; ++i) s.total += p.stored_tokens[i];  // uniform loads: the values stay warp-uniform
     s.shift = s.seen > p.NS ? p.NS : 0;
     s.max_pos = s.seen == 0 ? 0 : (s.seen <= p.NS ? s.seen : p.NS + s.total);
     s.n_sink_tiles = (int)((s.sinks + kTile - 1) / kTile);
@@ -572,6 +572,73 @@ __device__ __forceinline__ float reduce_group(const float *v, int n, int how) {
     return v[0];
 }
 
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// EMA pass over the cached slots of one lane, eight slots per thread and iteration:
+//   p = T(exp(logit - m) / l),  e = T(p * (1-beta)),  red = max or mean over the group,
+//   score = T(T(beta * score) + red)                       (cascade_attention.py:315-330)
+// exp(x - m) / l is evaluated as exp2(x*log2e + c) with c = -m*log2e - log2(l).
+template <typename T, bool kMax>
+__device__ __forceinline__ void ema_pass_vec(const DecodeParams &p, const Schedule &sc, const T *lg, T *scr,
+                                             const float *s_m, const float *s_linv, float w0, int tid) {
+    using P = Pack<T>;
+    constexpr float kLog2e = 1.4426950408889634f;
+    const int nvec = p.S / 8;
+    const int per_block = (nvec + p.finish_chunks - 1) / p.finish_chunks;
+    const int v_end = min(nvec, (int)(blockIdx.x + 1) * per_block);
+    float cg[8];
+#pragma unroll
+    for (int gh = 0; gh < 8; ++gh) cg[gh] = gh < p.G ? -s_m[gh] * kLog2e + __log2f(s_linv[gh]) : 0.f;
+    const float inv_g = 1.f / (float)p.G;
+    for (int v = blockIdx.x * per_block + tid; v < v_end; v += kFinishThreads) {
+        const int slot0 = v * 8;
+        uint4 sc4 = *reinterpret_cast<const uint4 *>(scr + slot0);
+        uint4 l4[8];
+        const bool any_valid = slot0 < sc.total;
+        if (any_valid) {
+#pragma unroll
+            for (int gh = 0; gh < 8; ++gh)
+                if (gh < p.G) l4[gh] = *reinterpret_cast<const uint4 *>(lg + (long long)gh * p.S + slot0);
+        }
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = kMax ? -INFINITY : 0.f;
+        if (any_valid) {
+#pragma unroll
+            for (int gh = 0; gh < 8; ++gh) {
+                if (gh < p.G) {
+                    const uint32_t *lw = reinterpret_cast<const uint32_t *>(&l4[gh]);
+#pragma unroll
+                    for (int jj = 0; jj < 4; ++jj) {
+                        const float2 l = P::to_f2(P::from_u(lw[jj]));
+                        const float2 pr = P::to_f2(P::from_f2(make_float2(ex2_approx(fmaf(l.x, kLog2e, cg[gh])),
+                                                                          ex2_approx(fmaf(l.y, kLog2e, cg[gh])))));
+                        const float2 e = P::to_f2(P::from_f2(make_float2(__fmul_rn(pr.x, w0), __fmul_rn(pr.y, w0))));
+                        acc[2 * jj] = kMax ? fmaxf(acc[2 * jj], e.x) : acc[2 * jj] + e.x;
+                        acc[2 * jj + 1] = kMax ? fmaxf(acc[2 * jj + 1], e.y) : acc[2 * jj + 1] + e.y;
+                    }
+                }
+            }
+        }
+        uint32_t *sw = reinterpret_cast<uint32_t *>(&sc4);
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+            float2 red = make_float2(0.f, 0.f);
+            if (slot0 + 2 * jj < sc.total) red.x = kMax ? acc[2 * jj] : acc[2 * jj] * inv_g;
+            if (slot0 + 2 * jj + 1 < sc.total) red.y = kMax ? acc[2 * jj + 1] : acc[2 * jj + 1] * inv_g;
+            red = P::to_f2(P::from_f2(red));
+            const float2 old = P::to_f2(P::from_u(sw[jj]));
+            const float2 dec = P::to_f2(P::from_f2(make_float2(__fmul_rn(old.x, p.beta_pow), __fmul_rn(old.y, p.beta_pow))));
+            sw[jj] = P::to_u(P::from_f2(make_float2(__fadd_rn(dec.x, red.x), __fadd_rn(dec.y, red.y))));
+        }
+        *reinterpret_cast<uint4 *>(scr + slot0) = sc4;
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kFinishThreads) decode_finish_kernel(DecodeParams p) {
     __shared__ float s_m[kMaxG], s_linv[kMaxG], s_snew[kMaxG], s_pnew[kMaxG];
@@ -674,41 +741,9 @@ __global__ void __launch_bounds__(kFinishThreads) decode_finish_kernel(DecodePar
         const float w0 = p.ema_w_cache[0];
         const T *lg = reinterpret_cast<const T *>(p.logits) + ((long long)b * p.H + kvh * p.G) * p.S;
         T *scr = reinterpret_cast<T *>(p.score_cache) + (long long)lane * p.S;
-        if (p.S % 8 == 0 && p.head_reduction != CKV_REDUCE_MEDIAN) {
-            // eight slots per thread: one 16-byte load per head row and one for the scores
-            const int nvec = p.S / 8;
-            const int per_block = (nvec + p.finish_chunks - 1) / p.finish_chunks;
-            const int v_end = min(nvec, (int)(blockIdx.x + 1) * per_block);
-            const bool is_max = p.head_reduction == CKV_REDUCE_MAX;
-            for (int v = blockIdx.x * per_block + tid; v < v_end; v += kFinishThreads) {
-                const int slot0 = v * 8;
-                uint4 sc4 = *reinterpret_cast<const uint4 *>(scr + slot0);
-                float acc[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) acc[j] = is_max ? -INFINITY : 0.f;
-                if (slot0 < sc.total) {
-                    for (int gh = 0; gh < p.G; ++gh) {
-                        const uint4 l4 = *reinterpret_cast<const uint4 *>(lg + (long long)gh * p.S + slot0);
-                        const T *lv = reinterpret_cast<const T *>(&l4);
-                        const float mg = s_m[gh], li = s_linv[gh];
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const float pr = rnd<T>(__expf(Elem<T>::to_f(lv[j]) - mg) * li);
-                            const float e = rnd<T>(__fmul_rn(pr, w0));
-                            acc[j] = is_max ? fmaxf(acc[j], e) : acc[j] + e;
-                        }
-                    }
-                }
-                T *sv = reinterpret_cast<T *>(&sc4);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    float red = 0.f;
-                    if (slot0 + j < sc.total) red = rnd<T>(is_max ? acc[j] : acc[j] / (float)p.G);
-                    const float decayed = rnd<T>(__fmul_rn(Elem<T>::to_f(sv[j]), p.beta_pow));
-                    sv[j] = Elem<T>::from_f(__fadd_rn(decayed, red));
-                }
-                *reinterpret_cast<uint4 *>(scr + slot0) = sc4;
-            }
+        if (p.S % 8 == 0 && p.head_reduction != CKV_REDUCE_MEDIAN && p.G <= 8) {
+            if (p.head_reduction == CKV_REDUCE_MAX) ema_pass_vec<T, true>(p, sc, lg, scr, s_m, s_linv, w0, tid);
+            else ema_pass_vec<T, false>(p, sc, lg, scr, s_m, s_linv, w0, tid);
         } else {
             const int per_block = (p.S + p.finish_chunks - 1) / p.finish_chunks;
             const int s_end = min(p.S, (int)(blockIdx.x + 1) * per_block);
@@ -730,12 +765,13 @@ __global__ void __launch_bounds__(kFinishThreads) decode_finish_kernel(DecodePar
 
     // 5. lane-invariant state after this token: lane 0's blocks rewrite positions / masks of their
     //    slots from the advanced counters (nothing in this kernel reads them)
+    if (tid < p.C) {
+        s_new_stored[tid] = p.stored_tokens[tid];
+        s_new_start[tid] = p.start_indices[tid];
+        s_every[tid] = p.every_n[tid];
+    }
+    __syncthreads();
     if (tid == 0) {
-        for (int i = 0; i < p.C; ++i) {
-            s_new_stored[i] = p.stored_tokens[i];
-            s_new_start[i] = p.start_indices[i];
-            s_every[i] = p.every_n[i];
-        }
         long long sinks = sc.sinks;
         advance_counters(s_new_stored, s_new_start, sinks, sc.seen, s_every, 1, p.NS, p.W, p.C, p.S, p.eager_fill);
         long long total = 0;
@@ -941,7 +977,7 @@ int launch_decode_tuned(const Dims &d, const ckv_layer_state *st, const void *q,
     p.stream_grid = sm_count();
     int chunks = 1;
     if (ema) {
-        chunks = (int)((8 * (uint64_t)sm_count() + lanes - 1) / lanes);
+        chunks = (int)((4 * (uint64_t)sm_count()) / lanes);  // one wave of blocks
         chunks = chunks < 1 ? 1 : (chunks > 64 ? 64 : chunks);
     }
     p.finish_chunks = chunks;
