@@ -253,10 +253,8 @@ def main():
         barrier()
         ms_e2e_total = ev2.elapsed_time(ev3)
 
-    t = torch.tensor([ms_total, ms_e2e_total], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_total, ms_e2e_total = t.tolist()
+    from cascading_kv_cache_b200.dist_utils import max_over_ranks
+    ms_total, ms_e2e_total = max_over_ranks([ms_total, ms_e2e_total], device=dev)
 
     nbytes = algorithmic_bytes(w)
     ms_step = ms_total / steps
