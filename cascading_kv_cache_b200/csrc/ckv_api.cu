@@ -90,6 +90,10 @@ extern "C" size_t ckv_attention_workspace_bytes(const ckv_config *cfg, int32_t n
         const size_t t = decode_workspace_bytes(d);
         n = t > n ? t : n;
     }
+    if (prefill_tuned_supported(d, n_tokens)) {
+        const size_t t = prefill_workspace_bytes(d, n_tokens);
+        n = t > n ? t : n;
+    }
     return n;
 }
 
@@ -148,6 +152,11 @@ extern "C" int ckv_attention(const ckv_config *cfg, const ckv_layer_state *st, c
         return launch_decode_tuned(d, st, q, q_stride_b, q_stride_h, key, value, kv_stride_b, kv_stride_h, rope,
                                    rope_rows, ema_w_cache, ema_w_new, out, o_stride_b, o_stride_h, workspace,
                                    workspace_bytes, flags, (cudaStream_t)cuda_stream, active_profile_hook());
+    if (!(flags & CKV_ATTN_FORCE_GENERIC) && prefill_tuned_supported(d, n_tokens))
+        return launch_prefill_tuned(d, st, q, q_stride_b, q_stride_h, q_stride_t, key, value, kv_stride_b, kv_stride_h,
+                                    kv_stride_t, n_tokens, rope, rope_rows, ema_w_cache, ema_w_new, out, o_stride_b,
+                                    o_stride_h, o_stride_t, workspace, workspace_bytes, flags,
+                                    (cudaStream_t)cuda_stream, active_profile_hook());
     return launch_attention_generic(d, st, q, q_stride_b, q_stride_h, q_stride_t, key, value, kv_stride_b,
                                     kv_stride_h, kv_stride_t, n_tokens, rope, rope_rows, ema_w_cache, ema_w_new, out,
                                     o_stride_b, o_stride_h, o_stride_t, workspace, workspace_bytes, flags,

@@ -114,4 +114,12 @@ int launch_decode_tuned(const Dims &d, const ckv_layer_state *st, const void *q,
                         int64_t osh, void *workspace, size_t workspace_bytes, int flags, cudaStream_t stream,
                         ProfileHook *hook);
 
+bool prefill_tuned_supported(const Dims &d, int n_tokens);
+size_t prefill_workspace_bytes(const Dims &d, int n_tokens);
+int launch_prefill_tuned(const Dims &d, const ckv_layer_state *st, const void *q, int64_t qsb, int64_t qsh,
+                         int64_t qst, const void *key, const void *value, int64_t ksb, int64_t ksh, int64_t kst,
+                         int n_tokens, const void *rope, int64_t rope_rows, const float *ema_w_cache,
+                         const void *ema_w_new, void *out, int64_t osb, int64_t osh, int64_t ost, void *workspace,
+                         size_t workspace_bytes, int flags, cudaStream_t stream, ProfileHook *hook);
+
 }  // namespace ckv

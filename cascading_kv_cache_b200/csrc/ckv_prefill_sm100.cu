@@ -1,0 +1,756 @@
+// Chunked prefill over the cascading cache for 16-bit caches with head_dim 128, on the Blackwell
+// tensor cores (tcgen05.mma with accumulators in tensor memory, operands staged by TMA).
+//
+//   1. prefill_prep_kernel   rotate+scale the chunk's queries and every VALID key (sinks, cached
+//                            slots, the chunk itself) at its cache position into scratch, compacted
+//                            so that key row r of a lane is [sinks | cached | new][r]; copy the
+//                            values alongside.  (reference: cascade_attention.py:141-166, :284-291)
+//   2. prefill_attn_kernel   one CTA per (batch, head, 128-query tile), two phases over the key tiles:
+//                            A: S = Q K^T (tcgen05), running row max / sum;
+//                            B: S again, P = T(exp(S - max) / sum) exactly normalised, out += P V
+//                               (tcgen05, out in tensor memory), and per-column EMA partial sums of
+//                               this query tile (cascade_attention.py:293-323).
+//   3. prefill_scores_kernel sums the partials over query tiles in a fixed order, reduces over the
+//                            GQA group, applies score = T(T(beta^K score) + ema) (:231-248, :329-330).
+//   4. the cache update of the chunk (ckv_update.cu).
+//
+// Warp roles in prefill_attn_kernel (320 threads): warp 0 TMA producer, warp 1 MMA issuer and
+// tensor-memory owner, warps 2-5 softmax (one query row per thread = one tensor-memory lane),
+// warps 6-9 column scores (one key column per thread, reading P from shared memory).
+// Every mbarrier wait is bounded; on a time-out the status word is raised and all roles leave.
+#include <cuda.h>
+
+#include "ckv_common.cuh"
+
+namespace ckv {
+
+namespace {
+
+constexpr int kBM = 128, kBN = 128;
+constexpr int kSubBytes = 128 * 128;          // [128 rows x 64 elements] 16-bit, 128-byte swizzled
+constexpr int kTileBytes = 2 * kSubBytes;     // [128 x 128]
+constexpr int kOffQ = 0;
+constexpr int kOffK = kTileBytes;             // 2 stages
+constexpr int kOffV = 3 * kTileBytes;         // 2 stages
+constexpr int kOffP = 5 * kTileBytes;
+constexpr int kOffBar = 6 * kTileBytes;
+constexpr int kOffW = kOffBar + 256;          // float w_cache of the tile's 128 rows
+constexpr int kAttnSmem = kOffW + 512 + 1024; // + alignment slack
+constexpr int kAttnThreads = 320;
+constexpr unsigned kSpin = 1u << 22;
+constexpr int kTmemCols = 512;
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct PrefillParams {
+    // inputs
+    const void *q, *key, *val;
+    long long qsb, qsh, qst, ksb, ksh, kst;   // elements
+    const void *rope;
+    long long rope_rows;
+    const float *ema_w_cache;
+    const void *ema_w_new;
+    void *out;
+    long long osb, osh, ost;
+    // state
+    const void *sink_k, *sink_v, *cache_k, *cache_v;
+    void *cache_s;
+    const long long *pos, *sink_pos, *stored_tokens, *stored_sinks, *seen;
+    // scratch
+    int *status;
+    void *qs;          // [B*H][Kpad][128]
+    void *kcat;        // [B*KVH][Rpad][128]
+    void *vcat;        // [B*KVH][Rpad][128]
+    float *colpart;    // [B*H][nQT][Rpad]
+    void *new_scores;  // [B*KVH][K]
+    int B, KVH, H, G, NS, S, C, K, Kpad, Rpad, nQT;
+    int ema, head_reduction;
+    float rs, beta_pow;
+};
+
+struct Extents {
+    long long seen, sinks, total, shift, max_pos;
+    int n_cached;  // valid sink + cached rows
+};
+
+__device__ __forceinline__ Extents make_extents(const PrefillParams &p) {
+    Extents e;
+    e.seen = *p.seen;
+    e.sinks = *p.stored_sinks;
+    e.total = 0;
+    for (int i = 0; i < p.C; ++i) e.total += p.stored_tokens[i];
+    e.shift = e.seen > p.NS ? p.NS : 0;
+    e.max_pos = e.seen == 0 ? 0 : (e.seen <= p.NS ? e.seen : p.NS + e.total);
+    e.n_cached = (int)(e.sinks + e.total);
+    return e;
+}
+
+// ------------------------------------------------------------------------------------ prep
+template <typename T>
+__global__ void __launch_bounds__(256) prefill_prep_kernel(PrefillParams p) {
+    const Extents e = make_extents(p);
+    const long long n_krows = (long long)p.B * p.KVH * p.Rpad;
+    const long long n_qrows = (long long)p.B * p.H * p.Kpad;
+    const int r_valid = e.n_cached + p.K;
+    const T *rope = reinterpret_cast<const T *>(p.rope);
+    // one thread per (row, pair of dims d and d+64 in steps of 8): 8 threads x 16 bytes cover a half row
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < (n_krows + n_qrows) * 8;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const long long rowi = idx >> 3;
+        const int c = (int)(idx & 7);  // dims [8c, 8c+8) and [64+8c, 64+8c+8)
+        const T *src = nullptr, *vsrc = nullptr;
+        T *dst, *vdst = nullptr;
+        long long pos = 0;
+        if (rowi < n_krows) {
+            const int r = (int)(rowi % p.Rpad);
+            const long long lane = rowi / p.Rpad;
+            const int b = (int)(lane / p.KVH), h = (int)(lane % p.KVH);
+            dst = reinterpret_cast<T *>(p.kcat) + rowi * 128;
+            vdst = reinterpret_cast<T *>(p.vcat) + rowi * 128;
+            if (r < e.sinks) {
+                src = reinterpret_cast<const T *>(p.sink_k) + (lane * p.NS + r) * 128;
+                vsrc = reinterpret_cast<const T *>(p.sink_v) + (lane * p.NS + r) * 128;
+                pos = p.sink_pos[r];
+            } else if (r < e.n_cached) {
+                const int slot = r - (int)e.sinks;
+                src = reinterpret_cast<const T *>(p.cache_k) + (lane * p.S + slot) * 128;
+                vsrc = reinterpret_cast<const T *>(p.cache_v) + (lane * p.S + slot) * 128;
+                pos = p.pos[slot] + e.shift;
+            } else if (r < r_valid) {
+                const int j = r - e.n_cached;
+                src = reinterpret_cast<const T *>(p.key) + b * p.ksb + h * p.ksh + (long long)j * p.kst;
+                vsrc = reinterpret_cast<const T *>(p.val) + b * p.ksb + h * p.ksh + (long long)j * p.kst;
+                pos = e.max_pos + j;
+            }
+        } else {
+            const long long qr = rowi - n_krows;
+            const int j = (int)(qr % p.Kpad);
+            const long long bh = qr / p.Kpad;
+            const int b = (int)(bh / p.H), h = (int)(bh % p.H);
+            dst = reinterpret_cast<T *>(p.qs) + qr * 128;
+            if (j < p.K) {
+                src = reinterpret_cast<const T *>(p.q) + b * p.qsb + h * p.qsh + (long long)j * p.qst;
+                pos = e.max_pos + j;
+            }
+        }
+        uint4 lo4 = make_uint4(0, 0, 0, 0), hi4 = lo4;
+        if (src) {
+            pos = pos < 0 ? 0 : (pos >= p.rope_rows ? p.rope_rows - 1 : pos);
+            const uint4 xl = *reinterpret_cast<const uint4 *>(src + 8 * c);
+            const uint4 xh = *reinterpret_cast<const uint4 *>(src + 64 + 8 * c);
+            const uint4 cs = *reinterpret_cast<const uint4 *>(rope + pos * 128 + 8 * c);
+            const uint4 sn = *reinterpret_cast<const uint4 *>(rope + pos * 128 + 64 + 8 * c);
+            const T *l = reinterpret_cast<const T *>(&xl), *hh = reinterpret_cast<const T *>(&xh);
+            const T *cc = reinterpret_cast<const T *>(&cs), *ss = reinterpret_cast<const T *>(&sn);
+            T *ol = reinterpret_cast<T *>(&lo4), *oh = reinterpret_cast<T *>(&hi4);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float lo = Elem<T>::to_f(l[i]), hi = Elem<T>::to_f(hh[i]);
+                const float cf = Elem<T>::to_f(cc[i]), sf = Elem<T>::to_f(ss[i]);
+                const float rl = rnd<T>(__fadd_rn(rnd<T>(__fmul_rn(lo, cf)), rnd<T>(__fmul_rn(-hi, sf))));
+                const float rh = rnd<T>(__fadd_rn(rnd<T>(__fmul_rn(hi, cf)), rnd<T>(__fmul_rn(lo, sf))));
+                ol[i] = Elem<T>::from_f(__fmul_rn(rl, p.rs));
+                oh[i] = Elem<T>::from_f(__fmul_rn(rh, p.rs));
+            }
+        }
+        *reinterpret_cast<uint4 *>(dst + 8 * c) = lo4;
+        *reinterpret_cast<uint4 *>(dst + 64 + 8 * c) = hi4;
+        if (vdst) {
+            uint4 v0 = make_uint4(0, 0, 0, 0), v1 = v0;
+            if (vsrc) {
+                v0 = *reinterpret_cast<const uint4 *>(vsrc + 8 * c);
+                v1 = *reinterpret_cast<const uint4 *>(vsrc + 64 + 8 * c);
+            }
+            *reinterpret_cast<uint4 *>(vdst + 8 * c) = v0;
+            *reinterpret_cast<uint4 *>(vdst + 64 + 8 * c) = v1;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------- PTX helpers
+__device__ __forceinline__ uint32_t s_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void bar_init(uint64_t *bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void bar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void bar_expect_tx(uint64_t *bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool bar_try(uint64_t *bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(s_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool bar_wait(uint64_t *bar, unsigned parity, int *status) {
+    for (unsigned n = 0; n < kSpin; ++n) {
+        if (bar_try(bar, parity)) return true;
+        if (n > 32) __nanosleep(128);
+        if ((n & 255) == 255 && *((volatile int *)status) != 0) return false;
+    }
+    atomicExch(status, 2);
+    return false;
+}
+__device__ __forceinline__ void tma_2d(void *dst, const CUtensorMap *tm, int x, int y, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(s_u32(dst)), "l"(tm), "r"(s_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ex2f(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Shared-memory matrix descriptors (128-byte swizzle, rows of 128 bytes, 8-row groups of 1024 bytes).
+// K-major: the reduction dimension is contiguous inside the 128-byte row (Q, K, P tiles).
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t saddr) {
+    uint64_t d = (uint64_t)((saddr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;              // leading byte offset: unused for swizzled K-major
+    d |= (uint64_t)(1024 >> 4) << 32;    // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;              // descriptor version of this architecture
+    d |= (uint64_t)2 << 61;              // 128-byte swizzle
+    return d;
+}
+// MN-major: the N dimension (64 elements) is contiguous inside the row, rows step along K (V tile).
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t saddr, uint32_t n_atom_stride_bytes) {
+    uint64_t d = (uint64_t)((saddr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)(n_atom_stride_bytes >> 4) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// Instruction descriptor of tcgen05.mma kind::f16: fp32 accumulate (bits 4-5 = 1), operand formats
+// (bits 7-9 / 10-12: 0 = f16, 1 = bf16), B major-ness (bit 16), N >> 3 (bits 17-22), M >> 4 (bits 24-28).
+template <typename T> __device__ __forceinline__ uint32_t instr_desc(bool b_mn_major);
+template <> __device__ __forceinline__ uint32_t instr_desc<__nv_bfloat16>(bool b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(kBN >> 3) << 17) |
+           ((uint32_t)(kBM >> 4) << 24);
+}
+template <> __device__ __forceinline__ uint32_t instr_desc<__half>(bool b_mn_major) {
+    return (1u << 4) | (0u << 7) | (0u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(kBN >> 3) << 17) |
+           ((uint32_t)(kBM >> 4) << 24);
+}
+
+template <typename T> struct P2;
+template <> struct P2<__nv_bfloat16> {
+    static __device__ __forceinline__ uint32_t pack(float a, float b) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<uint32_t *>(&v);
+    }
+};
+template <> struct P2<__half> {
+    static __device__ __forceinline__ uint32_t pack(float a, float b) {
+        __half2 v = __floats2half2_rn(a, b);
+        return *reinterpret_cast<uint32_t *>(&v);
+    }
+};
+
+// ------------------------------------------------------------------------------ attention kernel
+template <typename T>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, PrefillParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kOffBar);
+    uint64_t *q_full = bars + 0, *k_full = bars + 1, *k_empty = bars + 3, *v_full = bars + 5, *v_empty = bars + 7;
+    uint64_t *s_full = bars + 9, *s_free = bars + 11, *p_full = bars + 13, *p_free = bars + 14, *o_full = bars + 15;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 16);
+    float *w_rows = reinterpret_cast<float *>(smem + kOffW);
+
+    const int warp = threadIdx.x >> 5, lane_id = threadIdx.x & 31;
+    const int qt = blockIdx.x;
+    const int bh = blockIdx.y;
+    const int b = bh / p.H, h = bh % p.H;
+    const long long lane = (long long)b * p.KVH + h / p.G;
+    const Extents e = make_extents(p);
+    const int q_hi = min(p.K, kBM * (qt + 1));               // queries of this tile end here
+    const int n_keys = e.n_cached + q_hi;                    // keys any row of the tile may see
+    const int nT = (n_keys + kBN - 1) / kBN;
+
+    if (threadIdx.x == 0) {
+        bar_init(q_full, 1);
+        for (int i = 0; i < 2; ++i) {
+            bar_init(&k_full[i], 1);
+            bar_init(&k_empty[i], 1);
+            bar_init(&v_full[i], 1);
+            bar_init(&v_empty[i], 1);
+            bar_init(&s_full[i], 1);
+            bar_init(&s_free[i], 4);
+        }
+        bar_init(p_full, 4);
+        bar_init(p_free, 5);
+        bar_init(o_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (threadIdx.x >= 192 && threadIdx.x < 320) {
+        const int r = threadIdx.x - 192;
+        const int qg = qt * kBM + r;
+        w_rows[r] = (p.ema && qg < p.K) ? p.ema_w_cache[qg] : 0.f;
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s_u32(tmem_slot)), "r"(kTmemCols));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t tm_s[2] = {tmem, tmem + 128u};
+    const uint32_t tm_o = tmem + 256u;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane_id == 0) {
+            bar_expect_tx(q_full, kTileBytes);
+            const int yq = bh * p.Kpad + qt * kBM;
+            tma_2d(smem + kOffQ, &tmQ, 0, yq, q_full);
+            tma_2d(smem + kOffQ + kSubBytes, &tmQ, 64, yq, q_full);
+            for (int g = 0; g < 2 * nT; ++g) {
+                const int j = g < nT ? g : g - nT;
+                const int st = g & 1;
+                if (g >= 2 && !bar_wait(&k_empty[st], ((g >> 1) - 1) & 1, p.status)) break;
+                const int y = (int)(lane * p.Rpad) + j * kBN;
+                bar_expect_tx(&k_full[st], kTileBytes);
+                tma_2d(smem + kOffK + st * kTileBytes, &tmK, 0, y, &k_full[st]);
+                tma_2d(smem + kOffK + st * kTileBytes + kSubBytes, &tmK, 64, y, &k_full[st]);
+                if (g >= nT) {
+                    const int vs = j & 1;
+                    if (j >= 2 && !bar_wait(&v_empty[vs], ((j >> 1) - 1) & 1, p.status)) break;
+                    bar_expect_tx(&v_full[vs], kTileBytes);
+                    tma_2d(smem + kOffV + vs * kTileBytes, &tmV, 0, y, &v_full[vs]);
+                    tma_2d(smem + kOffV + vs * kTileBytes + kSubBytes, &tmV, 64, y, &v_full[vs]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane_id == 0) {
+            const uint32_t id_qk = instr_desc<T>(false), id_pv = instr_desc<T>(true);
+            const uint32_t q_addr = s_u32(smem + kOffQ), p_addr = s_u32(smem + kOffP);
+            bool ok = bar_wait(q_full, 0, p.status);
+            auto do_pv = [&](int j) -> bool {
+                const int vs = j & 1;
+                if (!bar_wait(p_full, j & 1, p.status)) return false;
+                if (!bar_wait(&v_full[vs], (j >> 1) & 1, p.status)) return false;
+                tc_fence_after();
+                const uint32_t v_addr = s_u32(smem + kOffV + vs * kTileBytes);
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint64_t da = desc_k_major(p_addr + (ks >> 2) * kSubBytes + (ks & 3) * 32);
+                    const uint64_t db = desc_mn_major(v_addr + ks * 2048, kSubBytes);
+                    tc_mma(tm_o, da, db, id_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                }
+                tc_commit(&v_empty[vs]);
+                tc_commit(p_free);
+                return true;
+            };
+            for (int g = 0; ok && g < 2 * nT; ++g) {
+                const int st = g & 1;
+                if (!bar_wait(&k_full[st], (g >> 1) & 1, p.status)) { ok = false; break; }
+                if (g >= 2 && !bar_wait(&s_free[st], ((g >> 1) - 1) & 1, p.status)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t k_addr = s_u32(smem + kOffK + st * kTileBytes);
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint64_t da = desc_k_major(q_addr + (ks >> 2) * kSubBytes + (ks & 3) * 32);
+                    const uint64_t db = desc_k_major(k_addr + (ks >> 2) * kSubBytes + (ks & 3) * 32);
+                    tc_mma(tm_s[st], da, db, id_qk, ks > 0 ? 1u : 0u);
+                }
+                tc_commit(&k_empty[st]);
+                tc_commit(&s_full[st]);
+                if (g > nT) ok = do_pv(g - nT - 1);
+            }
+            if (ok) ok = do_pv(nT - 1);
+            if (ok) tc_commit(o_full);
+        }
+    } else if (warp < 6) {
+        // ---------------------------------------------------------------- softmax warps
+        const int quarter = warp & 3;
+        const int row = 32 * quarter + lane_id;
+        const int qg = qt * kBM + row;
+        const bool row_ok = qg < p.K;
+        const int row_limit = e.n_cached + (row_ok ? qg + 1 : 0);   // columns < row_limit are visible
+        const uint32_t lane_base = (uint32_t)(32 * quarter) << 16;
+        float m_run = -INFINITY, l_run = 0.f;
+        bool ok = true;
+        // phase A: row max and sum of exp over the logits rounded to T
+        for (int g = 0; ok && g < nT; ++g) {
+            const int st = g & 1;
+            if (!bar_wait(&s_full[st], (g >> 1) & 1, p.status)) { ok = false; break; }
+            tc_fence_after();
+#pragma unroll 1
+            for (int ch = 0; ch < 4; ++ch) {
+                uint32_t v[32];
+                tc_ld32(tm_s[st] + lane_base + ch * 32, v);
+                const int col0 = g * kBN + ch * 32;
+                float mx = m_run;
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    const float s = (col0 + c) < row_limit ? rnd<T>(__uint_as_float(v[c])) : -INFINITY;
+                    v[c] = __float_as_uint(s);
+                    mx = fmaxf(mx, s);
+                }
+                if (mx != -INFINITY) {
+                    const float mneg = -mx * kLog2e;
+                    float sum = 0.f;
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) sum += ex2f(fmaf(__uint_as_float(v[c]), kLog2e, mneg));
+                    l_run = l_run * ex2f(fmaf(m_run, kLog2e, mneg)) + sum;
+                    m_run = mx;
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane_id == 0) bar_arrive(&s_free[st]);
+        }
+        // phase B: exactly normalised probabilities
+        const float cshift = (l_run > 0.f) ? (-m_run * kLog2e - __log2f(l_run)) : 0.f;
+        uint8_t *p_row = smem + kOffP + row * 128;
+        for (int jb = 0; ok && jb < nT; ++jb) {
+            const int g = nT + jb, st = g & 1;
+            if (!bar_wait(&s_full[st], (g >> 1) & 1, p.status)) { ok = false; break; }
+            tc_fence_after();
+            if (jb >= 1 && !bar_wait(p_free, (jb - 1) & 1, p.status)) { ok = false; break; }
+#pragma unroll 1
+            for (int ch = 0; ch < 4; ++ch) {
+                uint32_t v[32];
+                tc_ld32(tm_s[st] + lane_base + ch * 32, v);
+                const int col0 = jb * kBN + ch * 32;
+                uint32_t pk[16];
+#pragma unroll
+                for (int c = 0; c < 32; c += 2) {
+                    float p0 = 0.f, p1 = 0.f;
+                    if (col0 + c < row_limit) p0 = ex2f(fmaf(rnd<T>(__uint_as_float(v[c])), kLog2e, cshift));
+                    if (col0 + c + 1 < row_limit) p1 = ex2f(fmaf(rnd<T>(__uint_as_float(v[c + 1])), kLog2e, cshift));
+                    pk[c >> 1] = P2<T>::pack(p0, p1);
+                }
+                // 32 columns = 4 chunks of 16 bytes inside sub-tile ch/2
+                uint8_t *sub = p_row + (ch >> 1) * kSubBytes;
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const int chunk = (ch & 1) * 4 + q4;
+                    *reinterpret_cast<uint4 *>(sub + ((chunk ^ (row & 7)) << 4)) =
+                        make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
+                }
+            }
+            tc_fence_before();
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane_id == 0) {
+                bar_arrive(&s_free[st]);
+                bar_arrive(p_full);
+            }
+        }
+        // epilogue: out row from tensor memory
+        if (ok && bar_wait(o_full, 0, p.status)) {
+            tc_fence_after();
+            T *orow = reinterpret_cast<T *>(p.out) + b * p.osb + h * p.osh + (long long)qg * p.ost;
+#pragma unroll 1
+            for (int ch = 0; ch < 4; ++ch) {
+                uint32_t v[32];
+                tc_ld32(tm_o + lane_base + ch * 32, v);
+                if (row_ok) {
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        uint4 o4;
+                        o4.x = P2<T>::pack(__uint_as_float(v[8 * q4]), __uint_as_float(v[8 * q4 + 1]));
+                        o4.y = P2<T>::pack(__uint_as_float(v[8 * q4 + 2]), __uint_as_float(v[8 * q4 + 3]));
+                        o4.z = P2<T>::pack(__uint_as_float(v[8 * q4 + 4]), __uint_as_float(v[8 * q4 + 5]));
+                        o4.w = P2<T>::pack(__uint_as_float(v[8 * q4 + 6]), __uint_as_float(v[8 * q4 + 7]));
+                        *reinterpret_cast<uint4 *>(orow + ch * 32 + 8 * q4) = o4;
+                    }
+                }
+            }
+        }
+        tc_fence_before();
+    } else {
+        // ---------------------------------------------------------------- column-score warps
+        const int col_t = threadIdx.x - 192;       // column of the tile owned by this thread
+        const int sub = col_t >> 6, cc = col_t & 63;
+        const int chunk = cc >> 3, within = (cc & 7) * 2;
+        const T *w_new = reinterpret_cast<const T *>(p.ema_w_new);
+        float *part = p.colpart + ((long long)bh * p.nQT + qt) * p.Rpad;
+        for (int jb = 0; jb < nT; ++jb) {
+            if (!bar_wait(p_full, jb & 1, p.status)) break;
+            if (p.ema) {
+                const int col = jb * kBN + col_t;
+                float acc = 0.f;
+                if (col >= (int)e.sinks && col < n_keys) {
+                    const uint8_t *base = smem + kOffP + sub * kSubBytes + within;
+                    if (col < e.n_cached) {
+#pragma unroll 8
+                        for (int r = 0; r < kBM; ++r) {
+                            const T pv = *reinterpret_cast<const T *>(base + r * 128 + ((chunk ^ (r & 7)) << 4));
+                            acc = fmaf(Elem<T>::to_f(pv), w_rows[r], acc);
+                        }
+                    } else {
+                        const int i = col - e.n_cached;      // new token index
+                        const int r0 = max(0, i - qt * kBM);
+                        for (int r = r0; r < kBM; ++r) {
+                            const int qg = qt * kBM + r;
+                            if (qg >= p.K) break;
+                            const T pv = *reinterpret_cast<const T *>(base + r * 128 + ((chunk ^ (r & 7)) << 4));
+                            acc += rnd<T>(__fmul_rn(Elem<T>::to_f(pv), Elem<T>::to_f(w_new[qg - i])));
+                        }
+                    }
+                    part[col] = acc;
+                }
+            }
+            __syncwarp();
+            if (lane_id == 0) bar_arrive(p_free);
+        }
+    }
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols));
+    }
+}
+
+// ----------------------------------------------------------------------------------- score reduce
+__device__ __forceinline__ float reduce_heads_pf(const float *v, int n, int how) {
+    if (how == CKV_REDUCE_MAX) {
+        float m = v[0];
+        for (int i = 1; i < n; ++i) m = fmaxf(m, v[i]);
+        return m;
+    }
+    if (how == CKV_REDUCE_MEAN) {
+        float s = 0.f;
+        for (int i = 0; i < n; ++i) s += v[i];
+        return s / (float)n;
+    }
+    const int want = (n - 1) / 2;
+    for (int i = 0; i < n; ++i) {
+        int less = 0, eq = 0;
+        for (int j = 0; j < n; ++j) {
+            less += v[j] < v[i];
+            eq += v[j] == v[i];
+        }
+        if (less <= want && want < less + eq) return v[i];
+    }
+    return v[0];
+}
+
+// One thread per (lane, column): columns are cached slots 0..S-1 then the K new tokens.
+template <typename T>
+__global__ void __launch_bounds__(256) prefill_scores_kernel(PrefillParams p) {
+    const Extents e = make_extents(p);
+    const int ncol = p.S + p.K;
+    const long long n = (long long)p.B * p.KVH * ncol;
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n) return;
+    const int col = (int)(idx % ncol);
+    const int lane = (int)(idx / ncol);
+    const int b = lane / p.KVH, kvh = lane % p.KVH;
+    float v[16];
+    float red = 0.f;
+    const bool is_new = col >= p.S;
+    if (is_new || col < e.total) {
+        const int r = is_new ? e.n_cached + (col - p.S) : (int)e.sinks + col;      // row of the compacted key matrix
+        const int qt0 = is_new ? (col - p.S) / kBM : 0;                            // first query tile that sees it
+        for (int gh = 0; gh < p.G; ++gh) {
+            const float *part = p.colpart + ((long long)(b * p.H + kvh * p.G + gh) * p.nQT) * p.Rpad + r;
+            float s = 0.f;
+            for (int qt = qt0; qt < p.nQT; ++qt) s += part[(long long)qt * p.Rpad];
+            v[gh] = rnd<T>(s);
+        }
+        red = rnd<T>(reduce_heads_pf(v, p.G, p.head_reduction));
+    }
+    if (!is_new) {
+        T *sc = reinterpret_cast<T *>(p.cache_s) + (long long)lane * p.S + col;
+        const float decayed = rnd<T>(__fmul_rn(Elem<T>::to_f(*sc), p.beta_pow));
+        *sc = Elem<T>::from_f(__fadd_rn(decayed, red));
+    } else {
+        reinterpret_cast<T *>(p.new_scores)[(long long)lane * p.K + (col - p.S)] = Elem<T>::from_f(red);
+    }
+}
+
+// ------------------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+// [rows, 128] 16-bit row-major, boxes of 128 rows x 64 elements, 128-byte swizzle
+int rows_map_128(CUtensorMap *tm, const void *base, uint64_t rows, int dtype) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail(CKV_E_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    const cuuint64_t dims[2] = {128, rows};
+    const cuuint64_t strides[1] = {256};
+    const cuuint32_t box[2] = {64, 128};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(tm, dtype == CKV_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                          const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(CKV_E_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return CKV_OK;
+}
+
+size_t a256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+struct PrefillScratch {
+    size_t status, qs, kcat, vcat, colpart, new_scores, total;
+    int Kpad, Rpad, nQT;
+};
+
+PrefillScratch prefill_scratch(const Dims &d, int K) {
+    PrefillScratch s;
+    s.nQT = (K + kBM - 1) / kBM;
+    s.Kpad = s.nQT * kBM;
+    s.Rpad = ((d.NS + d.S + K + kBN - 1) / kBN) * kBN;
+    size_t off = 0;
+    s.status = off; off += 1024;
+    s.qs = off; off += a256((size_t)d.B * d.H * s.Kpad * 256);
+    s.kcat = off; off += a256((size_t)d.B * d.KVH * s.Rpad * 256);
+    s.vcat = off; off += a256((size_t)d.B * d.KVH * s.Rpad * 256);
+    s.colpart = off; off += a256((size_t)d.B * d.H * s.nQT * s.Rpad * 4);
+    s.new_scores = off; off += a256((size_t)d.B * d.KVH * K * 2);
+    s.total = off;
+    return s;
+}
+
+}  // namespace
+
+bool prefill_tuned_supported(const Dims &d, int n_tokens) {
+    return n_tokens >= 2 && (d.dtype == CKV_BF16 || d.dtype == CKV_F16) && d.D == 128 && d.G <= 16 &&
+           !d.homogeneous && d.NS >= 1;
+}
+
+size_t prefill_workspace_bytes(const Dims &d, int n_tokens) { return prefill_scratch(d, n_tokens).total; }
+
+int launch_prefill_tuned(const Dims &d, const ckv_layer_state *st, const void *q, int64_t qsb, int64_t qsh,
+                         int64_t qst, const void *key, const void *value, int64_t ksb, int64_t ksh, int64_t kst,
+                         int n_tokens, const void *rope, int64_t rope_rows, const float *ema_w_cache,
+                         const void *ema_w_new, void *out, int64_t osb, int64_t osh, int64_t ost, void *workspace,
+                         size_t workspace_bytes, int flags, cudaStream_t stream, ProfileHook *hook) {
+    const PrefillScratch s = prefill_scratch(d, n_tokens);
+    if (!workspace || workspace_bytes < s.total)
+        return fail(CKV_E_WORKSPACE, "workspace of %zu bytes, need %zu", workspace_bytes, s.total);
+    if (rope_rows <= (int64_t)d.NS + d.S + n_tokens)
+        return fail(CKV_E_ARG, "rope table has %lld rows, need more than %d", (long long)rope_rows,
+                    d.NS + d.S + n_tokens);
+    const bool update = (flags & CKV_ATTN_UPDATE) != 0;
+    const bool ema = update && d.admission == CKV_ADMIT_EMA;
+    if (ema && (!ema_w_cache || !ema_w_new)) return fail(CKV_E_ARG, "EMA rule needs ema_w_cache and ema_w_new");
+    const uintptr_t ptrs = (uintptr_t)q | (uintptr_t)key | (uintptr_t)value | (uintptr_t)out | (uintptr_t)rope |
+                           (uintptr_t)st->key_cache | (uintptr_t)st->value_cache | (uintptr_t)st->sink_keys |
+                           (uintptr_t)st->sink_values | (uintptr_t)workspace;
+    const int64_t strides[] = {qsb, qsh, qst, ksb, ksh, kst, osb, osh, ost};
+    bool aligned = ptrs % 16 == 0;
+    for (int64_t sv : strides) aligned = aligned && (sv * 2) % 16 == 0;
+    if (!aligned) return fail(CKV_E_ARG, "q/key/value/out rows must be 16-byte aligned");
+
+    static bool attr_set = false;
+    if (!attr_set) {
+        CKV_CUDA_CHECK(cudaFuncSetAttribute(prefill_attn_kernel<__nv_bfloat16>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));
+        CKV_CUDA_CHECK(cudaFuncSetAttribute(prefill_attn_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            kAttnSmem));
+        attr_set = true;
+    }
+    uint8_t *ws = (uint8_t *)workspace;
+    PrefillParams p;
+    p.q = q; p.key = key; p.val = value;
+    p.qsb = qsb; p.qsh = qsh; p.qst = qst; p.ksb = ksb; p.ksh = ksh; p.kst = kst;
+    p.rope = rope; p.rope_rows = rope_rows;
+    p.ema_w_cache = ema_w_cache; p.ema_w_new = ema_w_new;
+    p.out = out; p.osb = osb; p.osh = osh; p.ost = ost;
+    p.sink_k = st->sink_keys; p.sink_v = st->sink_values; p.cache_k = st->key_cache; p.cache_v = st->value_cache;
+    p.cache_s = st->score_cache;
+    p.pos = (const long long *)st->pos; p.sink_pos = (const long long *)st->sink_pos;
+    p.stored_tokens = (const long long *)st->stored_tokens; p.stored_sinks = (const long long *)st->stored_sinks;
+    p.seen = (const long long *)st->seen_tokens;
+    p.status = (int *)(ws + s.status);
+    p.qs = ws + s.qs; p.kcat = ws + s.kcat; p.vcat = ws + s.vcat;
+    p.colpart = (float *)(ws + s.colpart); p.new_scores = ws + s.new_scores;
+    p.B = d.B; p.KVH = d.KVH; p.H = d.H; p.G = d.G; p.NS = d.NS; p.S = d.S; p.C = d.C;
+    p.K = n_tokens; p.Kpad = s.Kpad; p.Rpad = s.Rpad; p.nQT = s.nQT;
+    p.ema = ema; p.head_reduction = d.head_reduction;
+    p.rs = (float)sqrt(1.0 / sqrt((double)d.D));
+    p.beta_pow = (float)pow(d.beta, (double)n_tokens);
+
+    CUtensorMap tmQ, tmK, tmV;
+    int rc;
+    if ((rc = rows_map_128(&tmQ, p.qs, (uint64_t)d.B * d.H * s.Kpad, d.dtype)) != CKV_OK) return rc;
+    if ((rc = rows_map_128(&tmK, p.kcat, (uint64_t)d.B * d.KVH * s.Rpad, d.dtype)) != CKV_OK) return rc;
+    if ((rc = rows_map_128(&tmV, p.vcat, (uint64_t)d.B * d.KVH * s.Rpad, d.dtype)) != CKV_OK) return rc;
+
+    CKV_CUDA_CHECK(cudaMemsetAsync(p.status, 0, 4, stream));
+    const long long prep_work = ((long long)d.B * d.KVH * s.Rpad + (long long)d.B * d.H * s.Kpad) * 8;
+    int prep_blocks = (int)((prep_work + 255) / 256);
+    if (prep_blocks > 148 * 16) prep_blocks = 148 * 16;
+    const dim3 grid(s.nQT, d.B * d.H);
+    if (d.dtype == CKV_BF16) {
+        prefill_prep_kernel<__nv_bfloat16><<<prep_blocks, 256, 0, stream>>>(p);
+        if (hook) hook->before(stream, "prefill_attn_kernel");
+        prefill_attn_kernel<__nv_bfloat16><<<grid, kAttnThreads, kAttnSmem, stream>>>(tmQ, tmK, tmV, p);
+        if (hook) hook->after(stream);
+    } else {
+        prefill_prep_kernel<__half><<<prep_blocks, 256, 0, stream>>>(p);
+        if (hook) hook->before(stream, "prefill_attn_kernel");
+        prefill_attn_kernel<__half><<<grid, kAttnThreads, kAttnSmem, stream>>>(tmQ, tmK, tmV, p);
+        if (hook) hook->after(stream);
+    }
+    CKV_CUDA_CHECK(cudaGetLastError());
+    int launches = 2;
+    if (ema) {
+        const long long n = (long long)d.B * d.KVH * (d.S + n_tokens);
+        if (d.dtype == CKV_BF16) prefill_scores_kernel<__nv_bfloat16><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(p);
+        else prefill_scores_kernel<__half><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(p);
+        CKV_CUDA_CHECK(cudaGetLastError());
+        launches += 1;
+    }
+    note_launches(launches);
+    if (update) {
+        const void *scores = ema ? p.new_scores : nullptr;
+        return launch_update_serial(d, st, key, value, ksb, ksh, kst, scores, (int64_t)d.KVH * n_tokens, n_tokens, 1,
+                                    n_tokens, stream);
+    }
+    return CKV_OK;
+}
+
+}  // namespace ckv

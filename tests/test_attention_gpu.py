@@ -193,3 +193,28 @@ def test_decode_on_full_cache(spec):
         same = (a == b).float().mean().item()
         assert same >= 0.97, same   # scores are 16-bit: equal bits almost everywhere
         assert torch.allclose(a, b, rtol=2e-2, atol=1e-8)
+
+
+def test_tuned_kernels_are_the_ones_that_run():
+    """16-bit, head_dim 128: chunks go through the tcgen05 prefill kernel and single tokens through the
+    streaming decode kernel (the library's event hook reports the dominant kernel of each call)."""
+    from cascading_kv_cache_b200 import CascadingKVCache, cascade_attention, profiling
+    cache = CascadingKVCache(128, 4, 1, 2, 128, 512, device="cuda:0", dtype=torch.bfloat16, layers=1)
+    g = torch.Generator().manual_seed(3)
+    mk = lambda h, n: torch.randn(1, h, n, 128, generator=g).bfloat16().cuda()
+
+    def chunk(_):
+        cascade_attention(mk(8, 200), mk(2, 200), mk(2, 200), cache, 0)
+
+    def token(_):
+        cascade_attention(mk(8, 1), mk(2, 1), mk(2, 1), cache, 0)
+
+    def generic(_):
+        cascade_attention(mk(8, 1), mk(2, 1), mk(2, 1), cache, 0, force_generic=True)
+
+    assert profiling.time_dominant_kernel(chunk, 2)[2] == "prefill_attn_kernel"
+    assert profiling.last_launch_count() == 5       # prep, attention, scores, update walk, update finalize
+    assert profiling.time_dominant_kernel(token, 2)[2] == "decode_stream_kernel"
+    assert profiling.last_launch_count() == 3       # cos/sin image, stream, finish
+    assert profiling.time_dominant_kernel(generic, 1)[2] == "attn_rows_kernel"
+    assert cache.kernel_status() == 0
