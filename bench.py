@@ -133,6 +133,67 @@ def time_cpu_port(w, steps, warmup, batch_sample=1):
     return sum(times) / len(times), threads, nbytes
 
 
+PREFILL = dict(B=1, H=32, KVH=8, D=128, NS=4, W=8192, C=4, K=4096, theta=500000.0, beta=0.9999,
+               admission="ema", head_reduction="max", seed=2)
+
+
+def measured_peak_tflops():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            d = json.load(open(path))
+            return float(d["bf16_tflops"]), float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured"
+        except Exception:
+            pass
+    return 1590.0, 1400.0, "fallback"
+
+
+def run_prefill_leg(dev, chunks=6, warm=2):
+    """Chunked prefill at the c3 shapes (batch 1, 32/8 heads, 4 sinks, 4 x 8192 slots, chunk 4096, EMA rule)
+    on a full cache: attention of the chunk + fused score/cache update per chunk."""
+    from cascading_kv_cache_b200 import CascadingKVCache, cascade_attention, profiling
+    from cascading_kv_cache_b200.synthetic import populate_steady_state, prefill_algorithmic_flops
+    w = PREFILL
+    B, H, KVH, D, NS, W, C, K = (w[k] for k in ("B", "H", "KVH", "D", "NS", "W", "C", "K"))
+    S = W * C
+    dt = torch.bfloat16
+    cache = CascadingKVCache(W, NS, B, KVH, D, S, device=dev, dtype=dt, head_reduction=w["head_reduction"],
+                             layers=1, eager_fill=True, admission=w["admission"])
+    populate_steady_state(cache, 0, seed=w["seed"], beta=w["beta"])
+    g = torch.Generator(device=dev).manual_seed(77)
+    pool = 3
+    qs = torch.randn(pool, B, H, K, D, generator=g, device=dev).to(dt)
+    ks = torch.randn(pool, B, KVH, K, D, generator=g, device=dev).to(dt)
+    vs = torch.randn(pool, B, KVH, K, D, generator=g, device=dev).to(dt)
+    out = torch.empty(B, H, K, D, device=dev, dtype=dt)
+
+    def step(i):
+        j = i % pool
+        cascade_attention(qs[j], ks[j], vs[j], cache, 0, rope_theta=w["theta"], out=out)
+
+    for i in range(warm):
+        step(i)
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for i in range(chunks):
+        step(i)
+    ev1.record()
+    torch.cuda.synchronize()
+    ms_chunk = ev0.elapsed_time(ev1) / chunks
+    k_ms, _, k_name = profiling.time_dominant_kernel(step, n_steps=3)
+    launches = profiling.last_launch_count()
+    torch.cuda.synchronize()
+    flops = prefill_algorithmic_flops(B, H, D, K, NS + S)
+    burst, sustained, kind = measured_peak_tflops()
+    return {"workload": "c3_chunked_prefill_full_cache", "chunk_tokens": K, "tokens_per_s": K / (ms_chunk * 1e-3),
+            "ms_per_chunk": ms_chunk, "algorithmic_tflop_per_chunk": flops / 1e12,
+            "tflops": flops / (ms_chunk * 1e-3) / 1e12, "kernel": k_name, "kernel_ms": k_ms,
+            "kernel_tflops": flops / (k_ms * 1e-3) / 1e12, "peak_tflops": burst, "peak_kind": kind,
+            "kernel_frac_of_peak": flops / (k_ms * 1e-3) / 1e12 / burst, "launches_per_chunk": launches,
+            "status": cache.kernel_status()}
+
+
 def run_reference(args, w, rank, world):
     if rank != 0:
         return
@@ -164,6 +225,9 @@ def main():
     ap.add_argument("--batch", type=int, default=0, help="override the batch (smaller cases for profiler captures)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiler captures)")
     ap.add_argument("--no-profile", action="store_true", help="skip the per-kernel event timing")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the chunked-prefill leg")
+    ap.add_argument("--prefill-only", action="store_true", help="run only the chunked-prefill leg (profiler captures)")
+    ap.add_argument("--prefill-chunks", type=int, default=6)
     args = ap.parse_args()
     w = dict(WORKLOADS[args.workload])
     if args.batch > 0:
@@ -175,6 +239,11 @@ def main():
 
     if args.impl == "reference":
         run_reference(args, w, rank, world)
+        return
+    if args.prefill_only:
+        torch.cuda.set_device(local_rank)
+        print(json.dumps({"prefill": run_prefill_leg(torch.device("cuda", local_rank), chunks=args.prefill_chunks,
+                                                     warm=1)}), flush=True)
         return
 
     import torch.distributed as dist
@@ -292,6 +361,9 @@ def main():
                          "kernel": prof["kernel"], "kernel_ms": prof["ms"],
                          "step_frac": (nbytes / (ms_step * 1e-3) / 1e9) / peak},
         }
+        if not args.no_prefill:
+            del qs, ks, vs
+            line["prefill"] = run_prefill_leg(dev)
         if not args.no_cpu_baseline:
             sec, threads, cpu_bytes = time_cpu_port(w, steps=2, warmup=1)
             line["cpu_baseline"] = {
