@@ -21,7 +21,8 @@ CKV_ATTN_UPDATE = 1
 CKV_ATTN_FORCE_GENERIC = 2
 DTYPE_CODE = {torch.float32: CKV_F32, torch.float16: CKV_F16, torch.bfloat16: CKV_BF16}
 
-EXPORTS = ("ckv_abi_version", "ckv_last_error", "ckv_cascade_update", "ckv_attention_workspace_bytes",
+EXPORTS = ("ckv_abi_version", "ckv_last_error", "ckv_cascade_update", "ckv_update_workspace_bytes",
+           "ckv_attention_workspace_bytes",
            "ckv_attention", "ckv_last_launch_count", "ckv_profile_enable", "ckv_profile_read", "ckv_read_status",
            "ckv_static_scratch_bytes", "ckv_attention_static")
 
@@ -58,7 +59,9 @@ def load():
     lib.ckv_abi_version.restype = ctypes.c_int
     lib.ckv_last_error.restype = ctypes.c_char_p
     lib.ckv_cascade_update.restype = ctypes.c_int
-    lib.ckv_cascade_update.argtypes = [cfgp, stp, vp, vp, i64, i64, i64, vp, i64, i64, i64, i32, vp]
+    lib.ckv_cascade_update.argtypes = [cfgp, stp, vp, vp, i64, i64, i64, vp, i64, i64, i64, i32, vp, sz, vp]
+    lib.ckv_update_workspace_bytes.restype = sz
+    lib.ckv_update_workspace_bytes.argtypes = [cfgp, i32]
     lib.ckv_attention_workspace_bytes.restype = sz
     lib.ckv_attention_workspace_bytes.argtypes = [cfgp, i32]
     lib.ckv_attention.restype = ctypes.c_int

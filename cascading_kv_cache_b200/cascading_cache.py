@@ -181,6 +181,7 @@ class CascadingKVCache(Cache):
         self.sink_values = [z(B, H, max(NS, 1), D)[:, :, :NS] for _ in range(L)]
 
         self._workspace = None
+        self.force_serial_update = False   # tests: take the one-warp-per-lane update also for chunks
         self._rope_tables = {}
         self._ema_weights = {}
         self._cfg_cache = {}
@@ -241,6 +242,9 @@ class CascadingKVCache(Cache):
         if self._workspace is None or self._workspace.numel() < nbytes:
             self._workspace = torch.empty(nbytes + 256, device=self.device, dtype=torch.uint8)
         return self._workspace
+
+    def workspace_bytes(self) -> int:
+        return 0 if self._workspace is None else self._workspace.numel() - 256
 
     def workspace_ptr(self) -> int:
         return (self._workspace.data_ptr() + 255) & ~255
@@ -341,9 +345,14 @@ class CascadingKVCache(Cache):
                 s = s.to(device=self.device, dtype=self.dtype)
             s_ptr, ss = ctypes.c_void_p(s.data_ptr()), s.stride()
         cfg, st = self.ckv_config(layer_idx), self.ckv_state(layer_idx)
+        ws_ptr, ws_bytes = None, 0
+        if K >= 2 and not self.force_serial_update:
+            ws_bytes = self._lib.ckv_update_workspace_bytes(ctypes.byref(cfg), K)
+            self.workspace(ws_bytes)
+            ws_ptr = self.workspace_ptr()
         rc = self._lib.ckv_cascade_update(
             ctypes.byref(cfg), ctypes.byref(st), k.data_ptr(), v.data_ptr(), k.stride(0), k.stride(1), k.stride(2),
-            s_ptr, ss[0], ss[1], ss[2], K, _lib.current_stream_ptr(self.device))
+            s_ptr, ss[0], ss[1], ss[2], K, ws_ptr, ws_bytes, _lib.current_stream_ptr(self.device))
         _lib.check(rc, "ckv_cascade_update")
         self.note_tokens_seen(layer_idx, K)
         return self.get_vals(layer_idx)

@@ -67,7 +67,7 @@ extern "C" const char *ckv_last_error(void) { return g_error; }
 extern "C" int ckv_cascade_update(const ckv_config *cfg, const ckv_layer_state *st, const void *key, const void *value,
                                   int64_t kv_stride_b, int64_t kv_stride_h, int64_t kv_stride_t, const void *scores,
                                   int64_t s_stride_b, int64_t s_stride_h, int64_t s_stride_t, int32_t n_tokens,
-                                  void *cuda_stream) {
+                                  void *workspace, size_t workspace_bytes, void *cuda_stream) {
     Dims d;
     int rc = make_dims(cfg, &d);
     if (rc != CKV_OK) return rc;
@@ -78,8 +78,14 @@ extern "C" int ckv_cascade_update(const ckv_config *cfg, const ckv_layer_state *
     if (d.NS > 0 && (!st->sink_keys || !st->sink_values || !st->sink_mask || !st->sink_pos))
         return fail(CKV_E_ARG, "sink buffers are null");
     g_launches = 0;
-    return launch_update_serial(d, st, key, value, kv_stride_b, kv_stride_h, kv_stride_t, scores, s_stride_b,
-                                s_stride_h, s_stride_t, n_tokens, (cudaStream_t)cuda_stream);
+    return launch_update(d, st, key, value, kv_stride_b, kv_stride_h, kv_stride_t, scores, s_stride_b, s_stride_h,
+                         s_stride_t, n_tokens, workspace, workspace_bytes, (cudaStream_t)cuda_stream);
+}
+
+extern "C" size_t ckv_update_workspace_bytes(const ckv_config *cfg, int32_t n_tokens) {
+    Dims d;
+    if (make_dims(cfg, &d) != CKV_OK || n_tokens < 1) return 0;
+    return update_chunk_workspace_bytes(d, n_tokens);
 }
 
 extern "C" size_t ckv_attention_workspace_bytes(const ckv_config *cfg, int32_t n_tokens) {

@@ -294,7 +294,7 @@ __global__ void reduce_ema_kernel(GenericParams p) {
 size_t align_up(size_t x) { return (x + 255) & ~(size_t)255; }
 
 struct Scratch {
-    size_t q_rs, k_rot, row_m, row_l, raw, new_scores, total;
+    size_t q_rs, k_rot, row_m, row_l, raw, new_scores, upd, upd_bytes, total;
 };
 
 Scratch scratch_layout(const Dims &d, int K) {
@@ -306,6 +306,8 @@ Scratch scratch_layout(const Dims &d, int K) {
     s.row_l = off; off += align_up((size_t)d.B * d.H * K * 4);
     s.raw = off; off += align_up((size_t)d.B * d.H * (d.S + K) * 4);
     s.new_scores = off; off += align_up((size_t)d.B * d.KVH * K * d.esz);
+    s.upd_bytes = update_chunk_workspace_bytes(d, K);
+    s.upd = off; off += s.upd_bytes;
     s.total = off;
     return s;
 }
@@ -388,8 +390,8 @@ int launch_attention_generic(const Dims &d, const ckv_layer_state *st, const voi
     if (rc != CKV_OK) return rc;
     if (update) {
         const void *scores = ema ? p.new_scores : nullptr;
-        return launch_update_serial(d, st, key, value, ksb, ksh, kst, scores, (int64_t)d.KVH * n_tokens, n_tokens, 1,
-                                    n_tokens, stream);
+        return launch_update(d, st, key, value, ksb, ksh, kst, scores, (int64_t)d.KVH * n_tokens, n_tokens, 1,
+                             n_tokens, ws + s.upd, s.upd_bytes, stream);
     }
     return CKV_OK;
 }

@@ -91,6 +91,21 @@ int launch_update_serial(const Dims &d, const ckv_layer_state *st, const void *k
                          int64_t ksb, int64_t ksh, int64_t kst, const void *scores, int64_t ssb, int64_t ssh,
                          int64_t sst, int n_tokens, cudaStream_t stream);
 
+size_t update_chunk_workspace_bytes(const Dims &d, int n_tokens);
+int launch_update_chunk(const Dims &d, const ckv_layer_state *st, const void *key, const void *value, int64_t ksb,
+                        int64_t ksh, int64_t kst, const void *scores, int64_t ssb, int64_t ssh, int64_t sst,
+                        int n_tokens, void *workspace, size_t workspace_bytes, cudaStream_t stream);
+// Parallel chunk update when a workspace is available and the chunk has more than one token,
+// otherwise the one-warp-per-lane walk.
+inline int launch_update(const Dims &d, const ckv_layer_state *st, const void *key, const void *value, int64_t ksb,
+                         int64_t ksh, int64_t kst, const void *scores, int64_t ssb, int64_t ssh, int64_t sst,
+                         int n_tokens, void *workspace, size_t workspace_bytes, cudaStream_t stream) {
+    if (n_tokens >= 2 && workspace && workspace_bytes >= update_chunk_workspace_bytes(d, n_tokens))
+        return launch_update_chunk(d, st, key, value, ksb, ksh, kst, scores, ssb, ssh, sst, n_tokens, workspace,
+                                   workspace_bytes, stream);
+    return launch_update_serial(d, st, key, value, ksb, ksh, kst, scores, ssb, ssh, sst, n_tokens, stream);
+}
+
 size_t generic_workspace_bytes(const Dims &d, int n_tokens);
 int launch_attention_generic(const Dims &d, const ckv_layer_state *st, const void *q, int64_t qsb, int64_t qsh,
                              int64_t qst, const void *key, const void *value, int64_t ksb, int64_t ksh, int64_t kst,

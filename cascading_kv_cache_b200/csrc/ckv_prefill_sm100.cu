@@ -633,7 +633,7 @@ int rows_map_128(CUtensorMap *tm, const void *base, uint64_t rows, int dtype) {
 size_t a256(size_t x) { return (x + 255) & ~(size_t)255; }
 
 struct PrefillScratch {
-    size_t status, qs, kcat, vcat, colpart, new_scores, total;
+    size_t status, qs, kcat, vcat, colpart, new_scores, upd, upd_bytes, total;
     int Kpad, Rpad, nQT;
 };
 
@@ -649,6 +649,8 @@ PrefillScratch prefill_scratch(const Dims &d, int K) {
     s.vcat = off; off += a256((size_t)d.B * d.KVH * s.Rpad * 256);
     s.colpart = off; off += a256((size_t)d.B * d.H * s.nQT * s.Rpad * 4);
     s.new_scores = off; off += a256((size_t)d.B * d.KVH * K * 2);
+    s.upd_bytes = update_chunk_workspace_bytes(d, K);
+    s.upd = off; off += s.upd_bytes;
     s.total = off;
     return s;
 }
@@ -747,8 +749,8 @@ int launch_prefill_tuned(const Dims &d, const ckv_layer_state *st, const void *q
     note_launches(launches);
     if (update) {
         const void *scores = ema ? p.new_scores : nullptr;
-        return launch_update_serial(d, st, key, value, ksb, ksh, kst, scores, (int64_t)d.KVH * n_tokens, n_tokens, 1,
-                                    n_tokens, stream);
+        return launch_update(d, st, key, value, ksb, ksh, kst, scores, (int64_t)d.KVH * n_tokens, n_tokens, 1,
+                             n_tokens, ws + s.upd, s.upd_bytes, stream);
     }
     return CKV_OK;
 }

@@ -112,13 +112,17 @@ const char *ckv_last_error(void);
  *               the last dimension is contiguous and every row 16-byte aligned.
  *   scores      [B, >=KVH, n_tokens] cache dtype with element strides, or NULL = all zero
  *               (only heads < KVH are read, as in the reference).
+ *   workspace   ckv_update_workspace_bytes(cfg, n_tokens) bytes of scratch for the parallel chunk
+ *               update (256-byte aligned).  NULL / too small selects the one-warp-per-lane walk,
+ *               which needs no scratch, gives the same result and is much slower for long chunks.
  * seen_tokens is advanced by n_tokens on the device.
  */
+size_t ckv_update_workspace_bytes(const ckv_config *cfg, int32_t n_tokens);
 int ckv_cascade_update(const ckv_config *cfg, const ckv_layer_state *st,
                        const void *key, const void *value,
                        int64_t kv_stride_b, int64_t kv_stride_h, int64_t kv_stride_t,
                        const void *scores, int64_t s_stride_b, int64_t s_stride_h, int64_t s_stride_t,
-                       int32_t n_tokens, void *cuda_stream);
+                       int32_t n_tokens, void *workspace, size_t workspace_bytes, void *cuda_stream);
 
 /* Bytes of scratch ckv_attention needs for calls of up to n_tokens query tokens. */
 size_t ckv_attention_workspace_bytes(const ckv_config *cfg, int32_t n_tokens);

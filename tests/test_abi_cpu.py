@@ -35,11 +35,11 @@ def test_argument_errors_do_not_need_a_gpu():
     cfg = _lib.CkvConfig(batch=1, kv_heads=3, q_heads=4, head_dim=8, num_sinks=1, window=4, cascades=2, dtype=0)
     assert lib.ckv_attention_workspace_bytes(ctypes.byref(cfg), 4) == 0  # q_heads not a multiple of kv_heads
     st = _lib.CkvLayerState()
-    rc = lib.ckv_cascade_update(ctypes.byref(cfg), ctypes.byref(st), None, None, 0, 0, 0, None, 0, 0, 0, 1, None)
+    rc = lib.ckv_cascade_update(ctypes.byref(cfg), ctypes.byref(st), None, None, 0, 0, 0, None, 0, 0, 0, 1, None, 0, None)
     assert rc == -1 and b"multiple" in lib.ckv_last_error()
     cfg.q_heads = 6
     assert lib.ckv_attention_workspace_bytes(ctypes.byref(cfg), 4) > 0
-    rc = lib.ckv_cascade_update(ctypes.byref(cfg), ctypes.byref(st), None, None, 0, 0, 0, None, 0, 0, 0, 1, None)
+    rc = lib.ckv_cascade_update(ctypes.byref(cfg), ctypes.byref(st), None, None, 0, 0, 0, None, 0, 0, 0, 1, None, 0, None)
     assert rc == -1 and b"null" in lib.ckv_last_error()
 
 

@@ -54,6 +54,7 @@ def test_golden_stride_streams(name):
         k, v = k.repeat(1, 1, 1, D4), v.repeat(1, 1, 1, D4)
         D = D4
     cache, ref = make_pair(W, C, NS, B, H, D, torch.float32, False)
+    cache.force_serial_update = N % 2 == 1      # alternate between the two update kernels
     rng = np.random.default_rng(N)
     cuts = sorted({0, N, *rng.integers(0, N + 1, size=5).tolist()})
     for a, b in zip(cuts[:-1], cuts[1:]):
@@ -80,17 +81,21 @@ CASES = [
     (8, 8, 3, 1, 2, 32, torch.bfloat16, True, "pow2-1-4", 1500, 50),
     (8, 4, 0, 1, 2, 32, torch.float32, True, "pow4", 400, 9),
     (512, 4, 4, 1, 8, 128, torch.float32, False, "pow2", 5000, 512),
+    (64, 4, 4, 1, 2, 128, torch.bfloat16, True, "pow2", 9000, 4500),
+    (256, 4, 64, 2, 2, 128, torch.bfloat16, True, "pow2", 6000, 2048),
 ]
 
 
 @pytest.mark.parametrize("case", CASES, ids=lambda c: f"W{c[0]}C{c[1]}NS{c[2]}-{str(c[6])[6:]}-{c[8]}-k{c[10]}")
 @pytest.mark.parametrize("rule", ["stride", "ema"])
-def test_update_matches_oracle(case, rule):
+@pytest.mark.parametrize("path", ["parallel", "serial"])
+def test_update_matches_oracle(case, rule, path):
     """Random streams; under 'ema' every token arrives with a random score and the score cache is
     perturbed between calls as the attention would, so the score-driven branch is exercised."""
     W, C, NS, B, H, D, dtype, eager_fill, func, N, chunk = case
     g = torch.Generator().manual_seed(W * 1000 + C * 100 + NS + N)
     cache, ref = make_pair(W, C, NS, B, H, D, dtype, eager_fill, func)
+    cache.force_serial_update = path == "serial"
     done = 0
     while done < N:
         n = min(chunk, N - done)
