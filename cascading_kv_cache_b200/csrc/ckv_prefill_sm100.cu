@@ -7,18 +7,25 @@
 //                            values alongside.  (reference: cascade_attention.py:141-166, :284-291)
 //   2. prefill_attn_kernel   one CTA per (batch, head, 128-query tile), two phases over the key tiles:
 //                            A: S = Q K^T (tcgen05), running row max / sum;
-//                            B: S again, P = T(exp(S - max) / sum) exactly normalised, out += P V
-//                               (tcgen05, out in tensor memory), and per-column EMA partial sums of
-//                               this query tile (cascade_attention.py:293-323).
+//                            B: S^T = K Q^T, P^T = T(exp(S^T - max) / sum) exactly normalised,
+//                               out^T += V^T P^T (tcgen05, out^T in tensor memory), and the EMA
+//                               partial sum of every key over this query tile
+//                               (cascade_attention.py:293-323).
 //   3. prefill_scores_kernel sums the partials over query tiles in a fixed order, reduces over the
 //                            GQA group, applies score = T(T(beta^K score) + ema) (:231-248, :329-330).
 //   4. the cache update of the chunk (ckv_update.cu).
 //
 // Warp roles in prefill_attn_kernel (320 threads): warp 0 TMA producer, warp 1 MMA issuer and
-// tensor-memory owner, warps 2-5 softmax (one query row per thread = one tensor-memory lane),
-// warps 6-9 column scores (one key column per thread, reading P from shared memory).
+// tensor-memory owner, warps 2-9 softmax (two warps per 32-lane quarter of tensor memory, each taking
+// 64 of a tile's 128 columns).  Phase B runs TRANSPOSED (S^T = K Q^T, out^T = V^T P^T): a thread
+// then owns one key row, so the EMA score of that key is simply its row sum of P^T -- no
+// cross-thread column reduction and no extra warps.
 // Every mbarrier wait is bounded; on a time-out the status word is raised and all roles leave.
 #include <cuda.h>
+
+#include <stdlib.h>
+
+#include <type_traits>
 
 #include "ckv_common.cuh"
 
@@ -35,7 +42,7 @@ constexpr int kOffV = 3 * kTileBytes;         // 2 stages
 constexpr int kOffP = 5 * kTileBytes;
 constexpr int kOffBar = 6 * kTileBytes;
 constexpr int kOffW = kOffBar + 256;          // float w_cache of the tile's 128 rows
-constexpr int kAttnSmem = kOffW + 512 + 1024; // + alignment slack
+constexpr int kAttnSmem = kOffW + 3584 + 1024; // per-query constants, stats exchange, column partial + slack
 constexpr int kAttnThreads = 320;
 constexpr unsigned kSpin = 1u << 22;
 constexpr int kTmemCols = 512;
@@ -64,6 +71,7 @@ struct PrefillParams {
     void *new_scores;  // [B*KVH][K]
     int B, KVH, H, G, NS, S, C, K, Kpad, Rpad, nQT;
     int ema, head_reduction;
+    int dbg;           // timing experiments only: 1 = skip phase A, 2 = skip phase B, 4 = skip softmax math
     float rs, beta_pow;
 };
 
@@ -189,8 +197,8 @@ __device__ __forceinline__ bool bar_try(uint64_t *bar, unsigned parity) {
 __device__ __forceinline__ bool bar_wait(uint64_t *bar, unsigned parity, int *status) {
     for (unsigned n = 0; n < kSpin; ++n) {
         if (bar_try(bar, parity)) return true;
-        if (n > 32) __nanosleep(128);
-        if ((n & 255) == 255 && *((volatile int *)status) != 0) return false;
+        if (n > 4096) __nanosleep(64);
+        if ((n & 1023) == 1023 && *((volatile int *)status) != 0) return false;
     }
     atomicExch(status, 2);
     return false;
@@ -222,8 +230,8 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
           "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
           "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
         : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ float ex2f(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -249,23 +257,16 @@ __device__ __forceinline__ uint64_t desc_mn_major(uint32_t saddr, uint32_t n_ato
     d |= (uint64_t)2 << 61;
     return d;
 }
-// Instruction descriptor of tcgen05.mma kind::f16: fp32 accumulate (bits 4-5 = 1), operand formats
-// (bits 7-9 / 10-12: 0 = f16, 1 = bf16), B major-ness (bit 16), N >> 3 (bits 17-22), M >> 4 (bits 24-28).
-template <typename T> __device__ __forceinline__ uint32_t instr_desc(bool b_mn_major);
-template <> __device__ __forceinline__ uint32_t instr_desc<__nv_bfloat16>(bool b_mn_major) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(kBN >> 3) << 17) |
-           ((uint32_t)(kBM >> 4) << 24);
-}
-template <> __device__ __forceinline__ uint32_t instr_desc<__half>(bool b_mn_major) {
-    return (1u << 4) | (0u << 7) | (0u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(kBN >> 3) << 17) |
-           ((uint32_t)(kBM >> 4) << 24);
-}
-
 template <typename T> struct P2;
 template <> struct P2<__nv_bfloat16> {
     static __device__ __forceinline__ uint32_t pack(float a, float b) {
         __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
         return *reinterpret_cast<uint32_t *>(&v);
+    }
+    // a and b already hold bf16-representable values (round_to_t): their upper halves ARE the bf16
+    // bits, so packing is one byte permute instead of a conversion
+    static __device__ __forceinline__ uint32_t pack_rounded(float a, float b) {
+        return __byte_perm(__float_as_uint(a), __float_as_uint(b), 0x7632);
     }
 };
 template <> struct P2<__half> {
@@ -273,10 +274,33 @@ template <> struct P2<__half> {
         __half2 v = __floats2half2_rn(a, b);
         return *reinterpret_cast<uint32_t *>(&v);
     }
+    static __device__ __forceinline__ uint32_t pack_rounded(float a, float b) { return pack(a, b); }
 };
 
 // ------------------------------------------------------------------------------ attention kernel
-template <typename T>
+// Round an fp32 value to the precision of T on the FMA pipe (Veltkamp split): the logits and the
+// probabilities are rounded where the reference's torch ops round them, without touching the
+// conversion unit that the exponentials already saturate.
+template <typename T> __device__ __forceinline__ float round_to_t(float x);
+template <> __device__ __forceinline__ float round_to_t<__nv_bfloat16>(float x) {
+    const float c = __fmul_rn(x, 65537.0f);
+    return __fsub_rn(c, __fsub_rn(c, x));
+}
+template <> __device__ __forceinline__ float round_to_t<__half>(float x) {
+    const float c = __fmul_rn(x, 8193.0f);
+    return __fsub_rn(c, __fsub_rn(c, x));
+}
+
+__device__ __forceinline__ void softmax_sync() { asm volatile("bar.sync 2, 256;" ::: "memory"); }
+
+// Instruction descriptor: fp32 accumulate, operand format, A / B major-ness, N, M.
+template <typename T> __device__ __forceinline__ uint32_t idesc(bool a_mn, bool b_mn) {
+    const uint32_t fmt = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
+           ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+}
+
+template <typename T, bool kEma>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, PrefillParams p) {
@@ -286,7 +310,11 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     uint64_t *q_full = bars + 0, *k_full = bars + 1, *k_empty = bars + 3, *v_full = bars + 5, *v_empty = bars + 7;
     uint64_t *s_full = bars + 9, *s_free = bars + 11, *p_full = bars + 13, *p_free = bars + 14, *o_full = bars + 15;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 16);
-    float *w_rows = reinterpret_cast<float *>(smem + kOffW);
+    float *c_q = reinterpret_cast<float *>(smem + kOffW);       // [128] softmax shift of each query of the tile
+    float *w_q = c_q + 128;                                     // [128] EMA weight of each query
+    float *x_m = w_q + 128;                                     // [2][128] stats exchange between column halves
+    float *x_l = x_m + 256;
+    float *colsum = x_l + 256;                                  // [128] second half's column partial
 
     const int warp = threadIdx.x >> 5, lane_id = threadIdx.x & 31;
     const int qt = blockIdx.x;
@@ -294,9 +322,10 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const int b = bh / p.H, h = bh % p.H;
     const long long lane = (long long)b * p.KVH + h / p.G;
     const Extents e = make_extents(p);
-    const int q_hi = min(p.K, kBM * (qt + 1));               // queries of this tile end here
-    const int n_keys = e.n_cached + q_hi;                    // keys any row of the tile may see
+    const int q_hi = min(p.K, kBM * (qt + 1));
+    const int n_keys = e.n_cached + q_hi;
     const int nT = (n_keys + kBN - 1) / kBN;
+    const int nTA = (p.dbg & 1) ? 0 : nT, nTB = (p.dbg & 2) ? 0 : nT;
 
     if (threadIdx.x == 0) {
         bar_init(q_full, 1);
@@ -306,17 +335,12 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             bar_init(&v_full[i], 1);
             bar_init(&v_empty[i], 1);
             bar_init(&s_full[i], 1);
-            bar_init(&s_free[i], 4);
+            bar_init(&s_free[i], 8);
         }
-        bar_init(p_full, 4);
-        bar_init(p_free, 5);
+        bar_init(p_full, 8);
+        bar_init(p_free, 1);
         bar_init(o_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (threadIdx.x >= 192 && threadIdx.x < 320) {
-        const int r = threadIdx.x - 192;
-        const int qg = qt * kBM + r;
-        w_rows[r] = (p.ema && qg < p.K) ? p.ema_w_cache[qg] : 0.f;
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s_u32(tmem_slot)), "r"(kTmemCols));
@@ -336,15 +360,15 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             const int yq = bh * p.Kpad + qt * kBM;
             tma_2d(smem + kOffQ, &tmQ, 0, yq, q_full);
             tma_2d(smem + kOffQ + kSubBytes, &tmQ, 64, yq, q_full);
-            for (int g = 0; g < 2 * nT; ++g) {
-                const int j = g < nT ? g : g - nT;
+            for (int g = 0; g < nTA + nTB; ++g) {
+                const int j = g < nTA ? g : g - nTA;
                 const int st = g & 1;
                 if (g >= 2 && !bar_wait(&k_empty[st], ((g >> 1) - 1) & 1, p.status)) break;
                 const int y = (int)(lane * p.Rpad) + j * kBN;
                 bar_expect_tx(&k_full[st], kTileBytes);
                 tma_2d(smem + kOffK + st * kTileBytes, &tmK, 0, y, &k_full[st]);
                 tma_2d(smem + kOffK + st * kTileBytes + kSubBytes, &tmK, 64, y, &k_full[st]);
-                if (g >= nT) {
+                if (g >= nTA) {
                     const int vs = j & 1;
                     if (j >= 2 && !bar_wait(&v_empty[vs], ((j >> 1) - 1) & 1, p.status)) break;
                     bar_expect_tx(&v_full[vs], kTileBytes);
@@ -356,7 +380,8 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
         if (lane_id == 0) {
-            const uint32_t id_qk = instr_desc<T>(false), id_pv = instr_desc<T>(true);
+            const uint32_t id_kk = idesc<T>(false, false);   // both operands K-major (Q K^T and K Q^T)
+            const uint32_t id_pv = idesc<T>(true, true);     // out^T = V^T P^T: both operands MN-major
             const uint32_t q_addr = s_u32(smem + kOffQ), p_addr = s_u32(smem + kOffP);
             bool ok = bar_wait(q_full, 0, p.status);
             auto do_pv = [&](int j) -> bool {
@@ -367,169 +392,247 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 const uint32_t v_addr = s_u32(smem + kOffV + vs * kTileBytes);
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {
-                    const uint64_t da = desc_k_major(p_addr + (ks >> 2) * kSubBytes + (ks & 3) * 32);
-                    const uint64_t db = desc_mn_major(v_addr + ks * 2048, kSubBytes);
+                    const uint64_t da = desc_mn_major(v_addr + ks * 2048, kSubBytes);   // V^T: dims x keys
+                    const uint64_t db = desc_mn_major(p_addr + ks * 2048, kSubBytes);   // P^T: keys x queries
                     tc_mma(tm_o, da, db, id_pv, (j > 0 || ks > 0) ? 1u : 0u);
                 }
                 tc_commit(&v_empty[vs]);
                 tc_commit(p_free);
                 return true;
             };
-            for (int g = 0; ok && g < 2 * nT; ++g) {
+            for (int g = 0; ok && g < nTA + nTB; ++g) {
                 const int st = g & 1;
                 if (!bar_wait(&k_full[st], (g >> 1) & 1, p.status)) { ok = false; break; }
                 if (g >= 2 && !bar_wait(&s_free[st], ((g >> 1) - 1) & 1, p.status)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t k_addr = s_u32(smem + kOffK + st * kTileBytes);
+                const bool transposed = g >= nTA;  // phase B: S^T = K Q^T (rows = keys)
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {
-                    const uint64_t da = desc_k_major(q_addr + (ks >> 2) * kSubBytes + (ks & 3) * 32);
-                    const uint64_t db = desc_k_major(k_addr + (ks >> 2) * kSubBytes + (ks & 3) * 32);
-                    tc_mma(tm_s[st], da, db, id_qk, ks > 0 ? 1u : 0u);
+                    const uint32_t off = (ks >> 2) * kSubBytes + (ks & 3) * 32;
+                    const uint64_t dq = desc_k_major(q_addr + off), dk = desc_k_major(k_addr + off);
+                    tc_mma(tm_s[st], transposed ? dk : dq, transposed ? dq : dk, id_kk, ks > 0 ? 1u : 0u);
                 }
                 tc_commit(&k_empty[st]);
                 tc_commit(&s_full[st]);
-                if (g > nT) ok = do_pv(g - nT - 1);
+                if (g > nTA) ok = do_pv(g - nTA - 1);
             }
-            if (ok) ok = do_pv(nT - 1);
+            if (ok && nTB > 0) ok = do_pv(nTB - 1);
             if (ok) tc_commit(o_full);
         }
-    } else if (warp < 6) {
-        // ---------------------------------------------------------------- softmax warps
+    } else {
+        // ---------------------------------------------------------------- softmax warps (8)
+        // tensor-memory lane = 32*quarter + lane_id; the two warps of a quarter split the 128 columns
         const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;
         const int row = 32 * quarter + lane_id;
-        const int qg = qt * kBM + row;
-        const bool row_ok = qg < p.K;
-        const int row_limit = e.n_cached + (row_ok ? qg + 1 : 0);   // columns < row_limit are visible
         const uint32_t lane_base = (uint32_t)(32 * quarter) << 16;
-        float m_run = -INFINITY, l_run = 0.f;
         bool ok = true;
-        // phase A: row max and sum of exp over the logits rounded to T
-        for (int g = 0; ok && g < nT; ++g) {
-            const int st = g & 1;
-            if (!bar_wait(&s_full[st], (g >> 1) & 1, p.status)) { ok = false; break; }
-            tc_fence_after();
-#pragma unroll 1
-            for (int ch = 0; ch < 4; ++ch) {
-                uint32_t v[32];
-                tc_ld32(tm_s[st] + lane_base + ch * 32, v);
-                const int col0 = g * kBN + ch * 32;
-                float mx = m_run;
+
+        // ---- phase A: rows are queries; running max and sum over the logits rounded to T
+        {
+            const int qg = qt * kBM + row;
+            const bool row_ok = qg < p.K;
+            const int row_limit = e.n_cached + (row_ok ? qg + 1 : 0);     // visible columns: [0, row_limit)
+            float m_run = -INFINITY, l_run = 0.f;
+            for (int g = 0; g < nTA; ++g) {
+                const int st = g & 1;
+                // after a failed (timed-out) wait the warp keeps walking the loop without waiting, so
+                // that the block-wide barriers below are still reached by everyone
+                if (ok) ok = bar_wait(&s_full[st], (g >> 1) & 1, p.status);
+                tc_fence_after();
+                const bool full_tile = (g + 1) * kBN <= e.n_cached + qt * kBM + 1 && (qt + 1) * kBM <= p.K;
+                uint32_t va[2][32];
+                tc_ld32(tm_s[st] + lane_base + 64 * half, va[0]);
+                tc_ld32(tm_s[st] + lane_base + 64 * half + 32, va[1]);
+                tc_ld_wait();
+                // the accumulator can be overwritten as soon as it is in registers
+                tc_fence_before();
+                __syncwarp();
+                if (lane_id == 0) bar_arrive(&s_free[st]);
+                if (p.dbg & 4) continue;
 #pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    const float s = (col0 + c) < row_limit ? rnd<T>(__uint_as_float(v[c])) : -INFINITY;
-                    v[c] = __float_as_uint(s);
-                    mx = fmaxf(mx, s);
-                }
-                if (mx != -INFINITY) {
-                    const float mneg = -mx * kLog2e;
-                    float sum = 0.f;
+                for (int ch = 0; ch < 2; ++ch) {
+                    uint32_t (&v)[32] = va[ch];
+                    const int cbase = 64 * half + 32 * ch;
+                    const int col0 = g * kBN + cbase;
+                    float mx = m_run;
+                    if (full_tile) {
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) sum += ex2f(fmaf(__uint_as_float(v[c]), kLog2e, mneg));
-                    l_run = l_run * ex2f(fmaf(m_run, kLog2e, mneg)) + sum;
-                    m_run = mx;
+                        for (int c = 0; c < 32; ++c) {
+                            const float s = round_to_t<T>(__uint_as_float(v[c]));
+                            v[c] = __float_as_uint(s);
+                            mx = fmaxf(mx, s);
+                        }
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) {
+                            const float s = (col0 + c) < row_limit ? round_to_t<T>(__uint_as_float(v[c])) : -INFINITY;
+                            v[c] = __float_as_uint(s);
+                            mx = fmaxf(mx, s);
+                        }
+                    }
+                    if (mx != -INFINITY) {
+                        const float mneg = -mx * kLog2e;
+                        float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+                        for (int c = 0; c < 32; c += 2) {
+                            sum0 += ex2f(fmaf(__uint_as_float(v[c]), kLog2e, mneg));
+                            sum1 += ex2f(fmaf(__uint_as_float(v[c + 1]), kLog2e, mneg));
+                        }
+                        l_run = l_run * ex2f(fmaf(m_run, kLog2e, mneg)) + (sum0 + sum1);
+                        m_run = mx;
+                    }
                 }
             }
+            // combine the two column halves of each row; publish shift and EMA weight per query
+            x_m[half * 128 + row] = m_run;
+            x_l[half * 128 + row] = l_run;
+            softmax_sync();
+            if (half == 0) {
+                const float m0 = x_m[row], m1 = x_m[128 + row];
+                const float mm = fmaxf(m0, m1);
+                float cq = -INFINITY;
+                if (row_ok && mm != -INFINITY) {
+                    const float l = x_l[row] * (m0 == -INFINITY ? 0.f : ex2f((m0 - mm) * kLog2e)) +
+                                    x_l[128 + row] * (m1 == -INFINITY ? 0.f : ex2f((m1 - mm) * kLog2e));
+                    cq = -mm * kLog2e - __log2f(l);
+                }
+                c_q[row] = cq;
+                w_q[row] = (kEma && row_ok) ? p.ema_w_cache[qg] : 0.f;
+            }
+            softmax_sync();
+        }
+
+        // ---- phase B: rows are keys (S^T); this thread owns key `key`, queries [64 half, 64 half + 64)
+        const T *w_new = reinterpret_cast<const T *>(p.ema_w_new);
+        float *part = p.colpart + ((long long)bh * p.nQT + qt) * p.Rpad;
+        uint8_t *pt_row = smem + kOffP + half * kSubBytes + row * 128;
+        for (int jb = 0; jb < nTB; ++jb) {
+            const int g = nTA + jb, st = g & 1;
+            if (ok) ok = bar_wait(&s_full[st], (g >> 1) & 1, p.status);
+            tc_fence_after();
+            const int key = jb * kBN + row;                      // row of the compacted key matrix
+            const bool key_ok = key < n_keys;
+            const bool is_new = key >= e.n_cached;
+            // query q of the tile sees this key iff  qt*128 + q >= key - n_cached
+            const int q_min = key_ok ? key - e.n_cached - qt * kBM : kBM;
+            const bool full_tile = (jb + 1) * kBN <= e.n_cached + qt * kBM + 1 && (qt + 1) * kBM <= p.K;
+            float acc = 0.f;
+            uint32_t va[2][32];
+            tc_ld32(tm_s[st] + lane_base + 64 * half, va[0]);
+            tc_ld32(tm_s[st] + lane_base + 64 * half + 32, va[1]);
+            tc_ld_wait();
             tc_fence_before();
             __syncwarp();
             if (lane_id == 0) bar_arrive(&s_free[st]);
-        }
-        // phase B: exactly normalised probabilities
-        const float cshift = (l_run > 0.f) ? (-m_run * kLog2e - __log2f(l_run)) : 0.f;
-        uint8_t *p_row = smem + kOffP + row * 128;
-        for (int jb = 0; ok && jb < nT; ++jb) {
-            const int g = nT + jb, st = g & 1;
-            if (!bar_wait(&s_full[st], (g >> 1) & 1, p.status)) { ok = false; break; }
-            tc_fence_after();
-            if (jb >= 1 && !bar_wait(p_free, (jb - 1) & 1, p.status)) { ok = false; break; }
-#pragma unroll 1
-            for (int ch = 0; ch < 4; ++ch) {
-                uint32_t v[32];
-                tc_ld32(tm_s[st] + lane_base + ch * 32, v);
-                const int col0 = jb * kBN + ch * 32;
-                uint32_t pk[16];
+            uint32_t pk[2][16];
+            // every key of the tile is a cached one and every (key, query) pair is visible: the common
+            // case, kept free of per-element control flow so that the exponentials overlap
+            const bool fast_tile = full_tile && (jb + 1) * kBN <= e.n_cached;
+            if (p.dbg & 4) {
 #pragma unroll
-                for (int c = 0; c < 32; c += 2) {
-                    float p0 = 0.f, p1 = 0.f;
-                    if (col0 + c < row_limit) p0 = ex2f(fmaf(rnd<T>(__uint_as_float(v[c])), kLog2e, cshift));
-                    if (col0 + c + 1 < row_limit) p1 = ex2f(fmaf(rnd<T>(__uint_as_float(v[c + 1])), kLog2e, cshift));
-                    pk[c >> 1] = P2<T>::pack(p0, p1);
+                for (int i = 0; i < 16; ++i) pk[0][i] = pk[1][i] = va[0][i];
+            } else if (fast_tile) {
+                float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+                for (int ch = 0; ch < 2; ++ch) {
+                    uint32_t (&v)[32] = va[ch];
+                    const int qbase = 64 * half + 32 * ch;
+#pragma unroll
+                    for (int c4 = 0; c4 < 32; c4 += 4) {
+                        const float4 cq4 = *reinterpret_cast<const float4 *>(c_q + qbase + c4);
+                        const float p0 = round_to_t<T>(ex2f(fmaf(round_to_t<T>(__uint_as_float(v[c4])), kLog2e, cq4.x)));
+                        const float p1 = round_to_t<T>(ex2f(fmaf(round_to_t<T>(__uint_as_float(v[c4 + 1])), kLog2e, cq4.y)));
+                        const float p2 = round_to_t<T>(ex2f(fmaf(round_to_t<T>(__uint_as_float(v[c4 + 2])), kLog2e, cq4.z)));
+                        const float p3 = round_to_t<T>(ex2f(fmaf(round_to_t<T>(__uint_as_float(v[c4 + 3])), kLog2e, cq4.w)));
+                        if (kEma) {
+                            const float4 wq4 = *reinterpret_cast<const float4 *>(w_q + qbase + c4);
+                            acc0 = fmaf(p0, wq4.x, acc0);
+                            acc1 = fmaf(p1, wq4.y, acc1);
+                            acc0 = fmaf(p2, wq4.z, acc0);
+                            acc1 = fmaf(p3, wq4.w, acc1);
+                        }
+                        pk[ch][(c4 >> 1)] = P2<T>::pack_rounded(p0, p1);
+                        pk[ch][(c4 >> 1) + 1] = P2<T>::pack_rounded(p2, p3);
+                    }
                 }
-                // 32 columns = 4 chunks of 16 bytes inside sub-tile ch/2
-                uint8_t *sub = p_row + (ch >> 1) * kSubBytes;
+                acc = acc0 + acc1;
+            } else
+#pragma unroll
+            for (int ch = 0; ch < 2; ++ch) {
+                uint32_t (&v)[32] = va[ch];
+                const int qbase = 64 * half + 32 * ch;
+#pragma unroll
+                for (int c4 = 0; c4 < 32; c4 += 4) {
+                    const float4 cq4 = *reinterpret_cast<const float4 *>(c_q + qbase + c4);
+                    const float4 wq4 = *reinterpret_cast<const float4 *>(w_q + qbase + c4);
+                    const float cqv[4] = {cq4.x, cq4.y, cq4.z, cq4.w};
+                    const float wqv[4] = {wq4.x, wq4.y, wq4.z, wq4.w};
+                    float pr[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const float s = round_to_t<T>(__uint_as_float(v[c4 + u]));
+                        float pv = ex2f(fmaf(s, kLog2e, cqv[u]));
+                        if (!full_tile && (qbase + c4 + u) < q_min) pv = 0.f;
+                        pr[u] = round_to_t<T>(pv);
+                        if (kEma) {
+                            if (!is_new) {
+                                acc = fmaf(pr[u], wqv[u], acc);
+                            } else if (pr[u] != 0.f) {
+                                const int d = qt * kBM + qbase + c4 + u - (key - e.n_cached);
+                                acc += round_to_t<T>(__fmul_rn(pr[u], Elem<T>::to_f(w_new[d])));
+                            }
+                        }
+                    }
+                    pk[ch][(c4 >> 1)] = P2<T>::pack_rounded(pr[0], pr[1]);
+                    pk[ch][(c4 >> 1) + 1] = P2<T>::pack_rounded(pr[2], pr[3]);
+                }
+            }
+            // P^T of the previous tile must have been consumed before this one overwrites it
+            if (ok && jb >= 1) ok = bar_wait(p_free, (jb - 1) & 1, p.status);
+#pragma unroll
+            for (int ch = 0; ch < 2; ++ch) {
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
-                    const int chunk = (ch & 1) * 4 + q4;
-                    *reinterpret_cast<uint4 *>(sub + ((chunk ^ (row & 7)) << 4)) =
-                        make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
+                    const int chunk = ch * 4 + q4;
+                    *reinterpret_cast<uint4 *>(pt_row + ((chunk ^ (row & 7)) << 4)) =
+                        make_uint4(pk[ch][4 * q4], pk[ch][4 * q4 + 1], pk[ch][4 * q4 + 2], pk[ch][4 * q4 + 3]);
                 }
             }
-            tc_fence_before();
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
-            if (lane_id == 0) {
-                bar_arrive(&s_free[st]);
-                bar_arrive(p_full);
+            if (lane_id == 0) bar_arrive(p_full);
+            if (kEma) {
+                // column EMA partial of this query tile = row sum of P^T over both query halves
+                if (half == 1) colsum[row] = acc;
+                softmax_sync();
+                if (half == 0 && key_ok && key >= (int)e.sinks) part[key] = acc + colsum[row];
+                softmax_sync();
             }
         }
-        // epilogue: out row from tensor memory
+
+        // ---- epilogue: out^T lives in tensor memory, lane = dim, column = query
         if (ok && bar_wait(o_full, 0, p.status)) {
             tc_fence_after();
-            T *orow = reinterpret_cast<T *>(p.out) + b * p.osb + h * p.osh + (long long)qg * p.ost;
+            const int d = row;
 #pragma unroll 1
-            for (int ch = 0; ch < 4; ++ch) {
+            for (int ch = 0; ch < 2; ++ch) {
                 uint32_t v[32];
-                tc_ld32(tm_o + lane_base + ch * 32, v);
-                if (row_ok) {
+                const int qbase = 64 * half + 32 * ch;
+                tc_ld32(tm_o + lane_base + qbase, v);
+                tc_ld_wait();
 #pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) {
-                        uint4 o4;
-                        o4.x = P2<T>::pack(__uint_as_float(v[8 * q4]), __uint_as_float(v[8 * q4 + 1]));
-                        o4.y = P2<T>::pack(__uint_as_float(v[8 * q4 + 2]), __uint_as_float(v[8 * q4 + 3]));
-                        o4.z = P2<T>::pack(__uint_as_float(v[8 * q4 + 4]), __uint_as_float(v[8 * q4 + 5]));
-                        o4.w = P2<T>::pack(__uint_as_float(v[8 * q4 + 6]), __uint_as_float(v[8 * q4 + 7]));
-                        *reinterpret_cast<uint4 *>(orow + ch * 32 + 8 * q4) = o4;
+                for (int c = 0; c < 32; ++c) {
+                    const int qg = qt * kBM + qbase + c;
+                    if (qg < p.K) {
+                        T *orow = reinterpret_cast<T *>(p.out) + b * p.osb + h * p.osh + (long long)qg * p.ost;
+                        orow[d] = Elem<T>::from_f(__uint_as_float(v[c]));
                     }
                 }
             }
         }
         tc_fence_before();
-    } else {
-        // ---------------------------------------------------------------- column-score warps
-        const int col_t = threadIdx.x - 192;       // column of the tile owned by this thread
-        const int sub = col_t >> 6, cc = col_t & 63;
-        const int chunk = cc >> 3, within = (cc & 7) * 2;
-        const T *w_new = reinterpret_cast<const T *>(p.ema_w_new);
-        float *part = p.colpart + ((long long)bh * p.nQT + qt) * p.Rpad;
-        for (int jb = 0; jb < nT; ++jb) {
-            if (!bar_wait(p_full, jb & 1, p.status)) break;
-            if (p.ema) {
-                const int col = jb * kBN + col_t;
-                float acc = 0.f;
-                if (col >= (int)e.sinks && col < n_keys) {
-                    const uint8_t *base = smem + kOffP + sub * kSubBytes + within;
-                    if (col < e.n_cached) {
-#pragma unroll 8
-                        for (int r = 0; r < kBM; ++r) {
-                            const T pv = *reinterpret_cast<const T *>(base + r * 128 + ((chunk ^ (r & 7)) << 4));
-                            acc = fmaf(Elem<T>::to_f(pv), w_rows[r], acc);
-                        }
-                    } else {
-                        const int i = col - e.n_cached;      // new token index
-                        const int r0 = max(0, i - qt * kBM);
-                        for (int r = r0; r < kBM; ++r) {
-                            const int qg = qt * kBM + r;
-                            if (qg >= p.K) break;
-                            const T pv = *reinterpret_cast<const T *>(base + r * 128 + ((chunk ^ (r & 7)) << 4));
-                            acc += rnd<T>(__fmul_rn(Elem<T>::to_f(pv), Elem<T>::to_f(w_new[qg - i])));
-                        }
-                    }
-                    part[col] = acc;
-                }
-            }
-            __syncwarp();
-            if (lane_id == 0) bar_arrive(p_free);
-        }
     }
     __syncthreads();
     if (warp == 1) {
@@ -688,10 +791,14 @@ int launch_prefill_tuned(const Dims &d, const ckv_layer_state *st, const void *q
 
     static bool attr_set = false;
     if (!attr_set) {
-        CKV_CUDA_CHECK(cudaFuncSetAttribute(prefill_attn_kernel<__nv_bfloat16>,
+        CKV_CUDA_CHECK(cudaFuncSetAttribute(prefill_attn_kernel<__nv_bfloat16, true>,
                                             cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));
-        CKV_CUDA_CHECK(cudaFuncSetAttribute(prefill_attn_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            kAttnSmem));
+        CKV_CUDA_CHECK(cudaFuncSetAttribute(prefill_attn_kernel<__nv_bfloat16, false>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));
+        CKV_CUDA_CHECK(cudaFuncSetAttribute(prefill_attn_kernel<__half, true>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));
+        CKV_CUDA_CHECK(cudaFuncSetAttribute(prefill_attn_kernel<__half, false>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));
         attr_set = true;
     }
     uint8_t *ws = (uint8_t *)workspace;
@@ -714,6 +821,10 @@ int launch_prefill_tuned(const Dims &d, const ckv_layer_state *st, const void *q
     p.ema = ema; p.head_reduction = d.head_reduction;
     p.rs = (float)sqrt(1.0 / sqrt((double)d.D));
     p.beta_pow = (float)pow(d.beta, (double)n_tokens);
+    {
+        const char *dbg = getenv("CKV_PREFILL_DEBUG");
+        p.dbg = dbg ? atoi(dbg) : 0;
+    }
 
     CUtensorMap tmQ, tmK, tmV;
     int rc;
@@ -729,12 +840,14 @@ int launch_prefill_tuned(const Dims &d, const ckv_layer_state *st, const void *q
     if (d.dtype == CKV_BF16) {
         prefill_prep_kernel<__nv_bfloat16><<<prep_blocks, 256, 0, stream>>>(p);
         if (hook) hook->before(stream, "prefill_attn_kernel");
-        prefill_attn_kernel<__nv_bfloat16><<<grid, kAttnThreads, kAttnSmem, stream>>>(tmQ, tmK, tmV, p);
+        if (ema) prefill_attn_kernel<__nv_bfloat16, true><<<grid, kAttnThreads, kAttnSmem, stream>>>(tmQ, tmK, tmV, p);
+        else prefill_attn_kernel<__nv_bfloat16, false><<<grid, kAttnThreads, kAttnSmem, stream>>>(tmQ, tmK, tmV, p);
         if (hook) hook->after(stream);
     } else {
         prefill_prep_kernel<__half><<<prep_blocks, 256, 0, stream>>>(p);
         if (hook) hook->before(stream, "prefill_attn_kernel");
-        prefill_attn_kernel<__half><<<grid, kAttnThreads, kAttnSmem, stream>>>(tmQ, tmK, tmV, p);
+        if (ema) prefill_attn_kernel<__half, true><<<grid, kAttnThreads, kAttnSmem, stream>>>(tmQ, tmK, tmV, p);
+        else prefill_attn_kernel<__half, false><<<grid, kAttnThreads, kAttnSmem, stream>>>(tmQ, tmK, tmV, p);
         if (hook) hook->after(stream);
     }
     CKV_CUDA_CHECK(cudaGetLastError());
