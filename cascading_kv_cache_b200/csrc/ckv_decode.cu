@@ -1,17 +1,22 @@
 // Single-token decode over the cascading cache for 16-bit caches with head_dim 128.
 //
+// Kernel 0, rope_slots_kernel: cache positions do not depend on the lane, so the cos|sin row of every
+//   slot is written once per step in slot order (an L2-resident image that TMA can stream).
+//
 // Kernel 1, decode_stream_kernel (HBM-bound, persistent, one CTA per SM):
 //   The valid keys of all lanes form one flat stream of 64-key tiles; every CTA takes a
 //   contiguous range of that stream (a split of the key dimension that ignores lane borders, so
 //   all SMs stream the same number of bytes).  A producer warp moves each tile into a 4-stage
-//   shared-memory ring: K and V through TMA (cp.async.bulk.tensor, 128-byte swizzle) and the
-//   cos/sin rows of the tile's cache positions through 16-byte cp.async gathers, all completing
-//   on one mbarrier per stage.  Four consumer warps each own 16 keys of a tile: ldmatrix K and
-//   cos/sin fragments, RoPE in packed 16-bit arithmetic on the fragments (the same rounding
-//   points as the reference: cascade_attention.py:31-35, :284-291), QK^T and PV on mma.sync
-//   m16n8k16 with the GQA group as the M dimension, online softmax per warp.  It writes one
-//   (max, sum, out[G][128]) partial per (CTA, lane, warp) and, under the EMA rule, the logits of
-//   every cached slot in the cache dtype (the rounding point of the reference's einsum output).
+//   shared-memory ring with six TMA boxes (cp.async.bulk.tensor, 128-byte swizzle, mbarrier
+//   completion): K lo/hi and V lo/hi from the cache (L2 evict-first) and the cos / sin rows of the
+//   tile's slots from the image (L2 evict-last).  Sixteen consumer warps in two groups take
+//   alternate tiles; in a group, warp w owns keys [8w, 8w+8): ldmatrix of K and cos/sin fragments,
+//   RoPE in packed 16-bit arithmetic on the fragments (the same rounding points as the reference:
+//   cascade_attention.py:31-35, :284-291), QK^T on mma.sync m16n8k16 with the GQA group as the M
+//   dimension, logits rounded to the cache dtype, online softmax per warp, and
+//   out^T += V^T P^T on mma.sync m16n8k8 (dims as M).  At a lane border the warps merge their
+//   (max, sum, out) in shared memory into one partial per (CTA, lane); under the EMA rule the
+//   logits of every cached slot are also stored (the rounding point of the reference's einsum).
 //
 // Kernel 2, decode_finish_kernel: merges the partials with the new token's own logit, writes the
 //   output, turns logits into probabilities, reduces them over the GQA group, applies
@@ -124,13 +129,6 @@ __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *tm, in
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
         " [%0], [%1, {%3, %4}], [%2], %5;"
         ::"r"(smem_u32(dst)), "l"(tm), "r"(smem_u32(bar)), "r"(x), "r"(y), "l"(policy) : "memory");
-}
-__device__ __forceinline__ void cp_async_16(void *dst, const void *src, uint64_t policy) {
-    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;"
-                 ::"r"(smem_u32(dst)), "l"(src), "l"(policy) : "memory");
-}
-__device__ __forceinline__ void cp_async_arrive_noinc(uint64_t *bar) {
-    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"

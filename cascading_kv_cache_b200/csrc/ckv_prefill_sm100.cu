@@ -37,12 +37,12 @@ constexpr int kBM = 128, kBN = 128;
 constexpr int kSubBytes = 128 * 128;          // [128 rows x 64 elements] 16-bit, 128-byte swizzled
 constexpr int kTileBytes = 2 * kSubBytes;     // [128 x 128]
 constexpr int kOffQ = 0;
-constexpr int kOffK = kTileBytes;             // 2 stages
-constexpr int kOffV = 3 * kTileBytes;         // 2 stages
-constexpr int kOffP = 5 * kTileBytes;
+constexpr int kRing = 4;                      // K and V tiles share one ring, in the order they are consumed
+constexpr int kOffRing = kTileBytes;
+constexpr int kOffP = (1 + kRing) * kTileBytes;
 constexpr int kOffBar = 6 * kTileBytes;
 constexpr int kOffW = kOffBar + 256;          // float w_cache of the tile's 128 rows
-constexpr int kAttnSmem = kOffW + 3584 + 1024; // per-query constants, stats exchange, column partial + slack
+constexpr int kAttnSmem = kOffW + 4096 + 1024; // per-query constants, stats exchange, column partial + slack
 constexpr int kAttnThreads = 320;
 constexpr unsigned kSpin = 1u << 22;
 constexpr int kTmemCols = 512;
@@ -220,6 +220,25 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
 }
+// A operand read from tensor memory (lane = row, two 16-bit elements per 32-bit column)
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+          "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+          "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+          "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        : "memory");
+}
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -307,14 +326,15 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kOffBar);
-    uint64_t *q_full = bars + 0, *k_full = bars + 1, *k_empty = bars + 3, *v_full = bars + 5, *v_empty = bars + 7;
+    uint64_t *q_full = bars + 0, *r_full = bars + 1, *r_empty = bars + 1 + kRing;
     uint64_t *s_full = bars + 9, *s_free = bars + 11, *p_full = bars + 13, *p_free = bars + 14, *o_full = bars + 15;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 16);
+    uint64_t *qt_ready = bars + 17;                             // Q copied into tensor memory
     float *c_q = reinterpret_cast<float *>(smem + kOffW);       // [128] softmax shift of each query of the tile
     float *w_q = c_q + 128;                                     // [128] EMA weight of each query
     float *x_m = w_q + 128;                                     // [2][128] stats exchange between column halves
     float *x_l = x_m + 256;
-    float *colsum = x_l + 256;                                  // [128] second half's column partial
+    float *colsum = x_l + 256;                                  // [2][128] second half's column partial
 
     const int warp = threadIdx.x >> 5, lane_id = threadIdx.x & 31;
     const int qt = blockIdx.x;
@@ -329,17 +349,18 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
     if (threadIdx.x == 0) {
         bar_init(q_full, 1);
+        for (int i = 0; i < kRing; ++i) {
+            bar_init(&r_full[i], 1);
+            bar_init(&r_empty[i], 1);
+        }
         for (int i = 0; i < 2; ++i) {
-            bar_init(&k_full[i], 1);
-            bar_init(&k_empty[i], 1);
-            bar_init(&v_full[i], 1);
-            bar_init(&v_empty[i], 1);
             bar_init(&s_full[i], 1);
             bar_init(&s_free[i], 8);
         }
         bar_init(p_full, 8);
         bar_init(p_free, 1);
         bar_init(o_full, 1);
+        bar_init(qt_ready, 4);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -352,6 +373,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const uint32_t tmem = *tmem_slot;
     const uint32_t tm_s[2] = {tmem, tmem + 128u};
     const uint32_t tm_o = tmem + 256u;
+    const uint32_t tm_q = tmem + 384u;   // Q as an A operand: 128 lanes x 64 columns of packed pairs
 
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
@@ -360,22 +382,29 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             const int yq = bh * p.Kpad + qt * kBM;
             tma_2d(smem + kOffQ, &tmQ, 0, yq, q_full);
             tma_2d(smem + kOffQ + kSubBytes, &tmQ, 64, yq, q_full);
-            for (int g = 0; g < nTA + nTB; ++g) {
-                const int j = g < nTA ? g : g - nTA;
-                const int st = g & 1;
-                if (g >= 2 && !bar_wait(&k_empty[st], ((g >> 1) - 1) & 1, p.status)) break;
-                const int y = (int)(lane * p.Rpad) + j * kBN;
-                bar_expect_tx(&k_full[st], kTileBytes);
-                tma_2d(smem + kOffK + st * kTileBytes, &tmK, 0, y, &k_full[st]);
-                tma_2d(smem + kOffK + st * kTileBytes + kSubBytes, &tmK, 64, y, &k_full[st]);
-                if (g >= nTA) {
-                    const int vs = j & 1;
-                    if (j >= 2 && !bar_wait(&v_empty[vs], ((j >> 1) - 1) & 1, p.status)) break;
-                    bar_expect_tx(&v_full[vs], kTileBytes);
-                    tma_2d(smem + kOffV + vs * kTileBytes, &tmV, 0, y, &v_full[vs]);
-                    tma_2d(smem + kOffV + vs * kTileBytes + kSubBytes, &tmV, 64, y, &v_full[vs]);
+            // tiles are loaded in exactly the order the MMA warp consumes them:
+            //   phase A: K_0 .. K_{n-1};   phase B: K_0, K_1, V_0, K_2, V_1, ..., K_{n-1}, V_{n-2}, V_{n-1}
+            int n_load = 0;
+            bool ok = true;
+            auto load_tile = [&](const CUtensorMap *tm, int j) {
+                const int slot = n_load % kRing;
+                if (n_load >= kRing && !bar_wait(&r_empty[slot], ((n_load / kRing) - 1) & 1, p.status)) {
+                    ok = false;
+                    return;
                 }
+                const int y = (int)(lane * p.Rpad) + j * kBN;
+                uint8_t *dst = smem + kOffRing + slot * kTileBytes;
+                bar_expect_tx(&r_full[slot], kTileBytes);
+                tma_2d(dst, tm, 0, y, &r_full[slot]);
+                tma_2d(dst + kSubBytes, tm, 64, y, &r_full[slot]);
+                ++n_load;
+            };
+            for (int g = 0; ok && g < nTA; ++g) load_tile(&tmK, g);
+            for (int jb = 0; ok && jb < nTB; ++jb) {
+                load_tile(&tmK, jb);
+                if (ok && jb >= 1) load_tile(&tmV, jb - 1);
             }
+            if (ok && nTB > 0) load_tile(&tmV, nTB - 1);
         }
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
@@ -383,39 +412,55 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             const uint32_t id_kk = idesc<T>(false, false);   // both operands K-major (Q K^T and K Q^T)
             const uint32_t id_pv = idesc<T>(true, true);     // out^T = V^T P^T: both operands MN-major
             const uint32_t q_addr = s_u32(smem + kOffQ), p_addr = s_u32(smem + kOffP);
-            bool ok = bar_wait(q_full, 0, p.status);
-            auto do_pv = [&](int j) -> bool {
-                const int vs = j & 1;
-                if (!bar_wait(p_full, j & 1, p.status)) return false;
-                if (!bar_wait(&v_full[vs], (j >> 1) & 1, p.status)) return false;
+            bool ok = bar_wait(q_full, 0, p.status) && bar_wait(qt_ready, 0, p.status);
+            int n_use = 0;     // tiles consumed from the ring, same order as the producer's loads
+            auto ring_wait = [&](uint32_t &addr, int &slot) -> bool {
+                slot = n_use % kRing;
+                if (!bar_wait(&r_full[slot], (n_use / kRing) & 1, p.status)) return false;
+                addr = s_u32(smem + kOffRing + slot * kTileBytes);
+                ++n_use;
+                return true;
+            };
+            auto do_qk = [&](int g, bool transposed) -> bool {
+                const int st = g & 1;
+                uint32_t k_addr;
+                int slot;
+                if (!ring_wait(k_addr, slot)) return false;
+                if (g >= 2 && !bar_wait(&s_free[st], ((g >> 1) - 1) & 1, p.status)) return false;
                 tc_fence_after();
-                const uint32_t v_addr = s_u32(smem + kOffV + vs * kTileBytes);
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint32_t off = (ks >> 2) * kSubBytes + (ks & 3) * 32;
+                    const uint64_t dk = desc_k_major(k_addr + off);
+                    // phase A: S = Q K^T with Q read from tensor memory (halves the shared-memory reads);
+                    // phase B: S^T = K Q^T with both operands in shared memory
+                    if (transposed) tc_mma(tm_s[st], dk, desc_k_major(q_addr + off), id_kk, ks > 0 ? 1u : 0u);
+                    else tc_mma_ts(tm_s[st], tm_q + ks * 8, dk, id_kk, ks > 0 ? 1u : 0u);
+                }
+                tc_commit(&r_empty[slot]);
+                tc_commit(&s_full[st]);
+                return true;
+            };
+            auto do_pv = [&](int j) -> bool {
+                uint32_t v_addr;
+                int slot;
+                if (!bar_wait(p_full, j & 1, p.status)) return false;
+                if (!ring_wait(v_addr, slot)) return false;
+                tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {
                     const uint64_t da = desc_mn_major(v_addr + ks * 2048, kSubBytes);   // V^T: dims x keys
                     const uint64_t db = desc_mn_major(p_addr + ks * 2048, kSubBytes);   // P^T: keys x queries
                     tc_mma(tm_o, da, db, id_pv, (j > 0 || ks > 0) ? 1u : 0u);
                 }
-                tc_commit(&v_empty[vs]);
+                tc_commit(&r_empty[slot]);
                 tc_commit(p_free);
                 return true;
             };
-            for (int g = 0; ok && g < nTA + nTB; ++g) {
-                const int st = g & 1;
-                if (!bar_wait(&k_full[st], (g >> 1) & 1, p.status)) { ok = false; break; }
-                if (g >= 2 && !bar_wait(&s_free[st], ((g >> 1) - 1) & 1, p.status)) { ok = false; break; }
-                tc_fence_after();
-                const uint32_t k_addr = s_u32(smem + kOffK + st * kTileBytes);
-                const bool transposed = g >= nTA;  // phase B: S^T = K Q^T (rows = keys)
-#pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {
-                    const uint32_t off = (ks >> 2) * kSubBytes + (ks & 3) * 32;
-                    const uint64_t dq = desc_k_major(q_addr + off), dk = desc_k_major(k_addr + off);
-                    tc_mma(tm_s[st], transposed ? dk : dq, transposed ? dq : dk, id_kk, ks > 0 ? 1u : 0u);
-                }
-                tc_commit(&k_empty[st]);
-                tc_commit(&s_full[st]);
-                if (g > nTA) ok = do_pv(g - nTA - 1);
+            for (int g = 0; ok && g < nTA; ++g) ok = do_qk(g, false);
+            for (int jb = 0; ok && jb < nTB; ++jb) {
+                ok = do_qk(nTA + jb, true);          // phase B: S^T = K Q^T (rows = keys)
+                if (ok && jb >= 1) ok = do_pv(jb - 1);
             }
             if (ok && nTB > 0) ok = do_pv(nTB - 1);
             if (ok) tc_commit(o_full);
@@ -429,7 +474,28 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const uint32_t lane_base = (uint32_t)(32 * quarter) << 16;
         bool ok = true;
 
-        // ---- phase A: rows are queries; running max and sum over the logits rounded to T
+        // ---- Q tile -> tensor memory (rows = lanes, the row's 64 words in order)
+        ok = bar_wait(q_full, 0, p.status);
+        if (half == 0) {
+            uint32_t qw[2][32];
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+                const uint4 w4 = *reinterpret_cast<const uint4 *>(smem + kOffQ + (c >> 3) * kSubBytes + row * 128 +
+                                                                  (((c & 7) ^ (row & 7)) << 4));
+                qw[c >> 3][4 * (c & 7)] = w4.x;
+                qw[c >> 3][4 * (c & 7) + 1] = w4.y;
+                qw[c >> 3][4 * (c & 7) + 2] = w4.z;
+                qw[c >> 3][4 * (c & 7) + 3] = w4.w;
+            }
+            tc_st32(tm_q + lane_base, qw[0]);
+            tc_st32(tm_q + lane_base + 32, qw[1]);
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            tc_fence_before();
+            __syncwarp();
+            if (lane_id == 0) bar_arrive(qt_ready);
+        }
+
+        // ---- phase A: rows are queries; running max and sum of exp over the logits rounded to T
         {
             const int qg = qt * kBM + row;
             const bool row_ok = qg < p.K;
@@ -457,6 +523,9 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     const int cbase = 64 * half + 32 * ch;
                     const int col0 = g * kBN + cbase;
                     float mx = m_run;
+                    // the statistics must be those of the logits ROUNDED to T: in a peaked row a single
+                    // logit carries the sum, and its rounding (up to 2^-9 of its value) moves every
+                    // probability of the row by far more than T's resolution
                     if (full_tile) {
 #pragma unroll
                         for (int c = 0; c < 32; ++c) {
@@ -605,10 +674,10 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             if (lane_id == 0) bar_arrive(p_full);
             if (kEma) {
                 // column EMA partial of this query tile = row sum of P^T over both query halves
-                if (half == 1) colsum[row] = acc;
+                // double-buffered by tile parity: the barrier of the next tile orders the reuse
+                if (half == 1) colsum[(jb & 1) * 128 + row] = acc;
                 softmax_sync();
-                if (half == 0 && key_ok && key >= (int)e.sinks) part[key] = acc + colsum[row];
-                softmax_sync();
+                if (half == 0 && key_ok && key >= (int)e.sinks) part[key] = acc + colsum[(jb & 1) * 128 + row];
             }
         }
 
