@@ -297,17 +297,55 @@ template <> struct P2<__half> {
 };
 
 // ------------------------------------------------------------------------------ attention kernel
-// Round an fp32 value to the precision of T on the FMA pipe (Veltkamp split): the logits and the
-// probabilities are rounded where the reference's torch ops round them, without touching the
-// conversion unit that the exponentials already saturate.
+// Round an fp32 value to the precision of T with two integer operations on its bits (add half an
+// ulp of T, clear the low mantissa bits): round-half-up, which differs from the reference's
+// round-to-nearest-even only on exact ties.  Used on the masked / diagonal tiles.
 template <typename T> __device__ __forceinline__ float round_to_t(float x);
 template <> __device__ __forceinline__ float round_to_t<__nv_bfloat16>(float x) {
-    const float c = __fmul_rn(x, 65537.0f);
-    return __fsub_rn(c, __fsub_rn(c, x));
+    return __uint_as_float((__float_as_uint(x) + 0x8000u) & 0xFFFF0000u);
 }
 template <> __device__ __forceinline__ float round_to_t<__half>(float x) {
-    const float c = __fmul_rn(x, 8193.0f);
-    return __fsub_rn(c, __fsub_rn(c, x));
+    return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
+}
+
+// Packed fp32 pairs (one instruction for two elements on this architecture).
+__device__ __forceinline__ uint64_t pk2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void upk2(uint64_t v, float &lo, float &hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+// Veltkamp split on the FMA pipe: c = x * (2^s + 1); hi = c - (c - x) is x rounded to nearest with
+// 24 - s significant bits, i.e. to the precision of T (s = 16 for bf16, 13 for fp16).
+template <typename T> __device__ __forceinline__ uint64_t round2_to_t(uint64_t x2) {
+    const float cst = std::is_same<T, __nv_bfloat16>::value ? 65537.0f : 8193.0f;
+    const uint64_t c2 = mul2(x2, pk2(cst, cst));
+    return sub2(c2, sub2(c2, x2));
 }
 
 __device__ __forceinline__ void softmax_sync() { asm volatile("bar.sync 2, 256;" ::: "memory"); }
@@ -517,41 +555,47 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 __syncwarp();
                 if (lane_id == 0) bar_arrive(&s_free[st]);
                 if (p.dbg & 4) continue;
+                // the statistics must be those of the logits ROUNDED to T: in a peaked row a single
+                // logit carries the sum, and its rounding (up to 2^-9 of its value) moves every
+                // probability of the row by far more than T's resolution
+                uint64_t r2[2][16];
+                float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
                 for (int ch = 0; ch < 2; ++ch) {
-                    uint32_t (&v)[32] = va[ch];
-                    const int cbase = 64 * half + 32 * ch;
-                    const int col0 = g * kBN + cbase;
-                    float mx = m_run;
-                    // the statistics must be those of the logits ROUNDED to T: in a peaked row a single
-                    // logit carries the sum, and its rounding (up to 2^-9 of its value) moves every
-                    // probability of the row by far more than T's resolution
-                    if (full_tile) {
+                    const int col0 = g * kBN + 64 * half + 32 * ch;
 #pragma unroll
-                        for (int c = 0; c < 32; ++c) {
-                            const float s = round_to_t<T>(__uint_as_float(v[c]));
-                            v[c] = __float_as_uint(s);
-                            mx = fmaxf(mx, s);
+                    for (int c = 0; c < 32; c += 2) {
+                        uint64_t r = pk2(__uint_as_float(va[ch][c]), __uint_as_float(va[ch][c + 1]));
+                        if (!(p.dbg & 16)) r = round2_to_t<T>(r);
+                        float s0, s1;
+                        upk2(r, s0, s1);
+                        if (!full_tile) {
+                            if ((col0 + c) >= row_limit) s0 = -INFINITY;
+                            if ((col0 + c + 1) >= row_limit) s1 = -INFINITY;
+                            r = pk2(s0, s1);
                         }
-                    } else {
-#pragma unroll
-                        for (int c = 0; c < 32; ++c) {
-                            const float s = (col0 + c) < row_limit ? round_to_t<T>(__uint_as_float(v[c])) : -INFINITY;
-                            v[c] = __float_as_uint(s);
-                            mx = fmaxf(mx, s);
-                        }
+                        r2[ch][c >> 1] = r;
+                        mx[(c >> 1) & 1] = max3(mx[(c >> 1) & 1], s0, s1);
                     }
-                    if (mx != -INFINITY) {
-                        const float mneg = -mx * kLog2e;
-                        float sum0 = 0.f, sum1 = 0.f;
+                }
+                const float m_new = max3(mx[0], mx[1], m_run);
+                if (m_new != -INFINITY) {
+                    const float mneg = -m_new * kLog2e;
+                    const uint64_t mneg2 = pk2(mneg, mneg), l2e2 = pk2(kLog2e, kLog2e);
+                    uint64_t sum2[2] = {0ull, 0ull};
 #pragma unroll
-                        for (int c = 0; c < 32; c += 2) {
-                            sum0 += ex2f(fmaf(__uint_as_float(v[c]), kLog2e, mneg));
-                            sum1 += ex2f(fmaf(__uint_as_float(v[c + 1]), kLog2e, mneg));
+                    for (int ch = 0; ch < 2; ++ch)
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            float a0, a1;
+                            upk2(fma2(r2[ch][i], l2e2, mneg2), a0, a1);
+                            if (p.dbg & 8) sum2[i & 1] = add2(sum2[i & 1], pk2(a0, a1));
+                            else sum2[i & 1] = add2(sum2[i & 1], pk2(ex2f(a0), ex2f(a1)));
                         }
-                        l_run = l_run * ex2f(fmaf(m_run, kLog2e, mneg)) + (sum0 + sum1);
-                        m_run = mx;
-                    }
+                    float t0, t1;
+                    upk2(add2(sum2[0], sum2[1]), t0, t1);
+                    l_run = l_run * ex2f(fmaf(m_run, kLog2e, mneg)) + (t0 + t1);
+                    m_run = m_new;
                 }
             }
             // combine the two column halves of each row; publish shift and EMA weight per query
@@ -603,30 +647,38 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
                 for (int i = 0; i < 16; ++i) pk[0][i] = pk[1][i] = va[0][i];
             } else if (fast_tile) {
-                float acc0 = 0.f, acc1 = 0.f;
+                uint64_t acc2[2] = {0ull, 0ull};
+                const uint64_t l2e2 = pk2(kLog2e, kLog2e);
 #pragma unroll
                 for (int ch = 0; ch < 2; ++ch) {
                     uint32_t (&v)[32] = va[ch];
                     const int qbase = 64 * half + 32 * ch;
 #pragma unroll
                     for (int c4 = 0; c4 < 32; c4 += 4) {
-                        const float4 cq4 = *reinterpret_cast<const float4 *>(c_q + qbase + c4);
-                        const float p0 = round_to_t<T>(ex2f(fmaf(round_to_t<T>(__uint_as_float(v[c4])), kLog2e, cq4.x)));
-                        const float p1 = round_to_t<T>(ex2f(fmaf(round_to_t<T>(__uint_as_float(v[c4 + 1])), kLog2e, cq4.y)));
-                        const float p2 = round_to_t<T>(ex2f(fmaf(round_to_t<T>(__uint_as_float(v[c4 + 2])), kLog2e, cq4.z)));
-                        const float p3 = round_to_t<T>(ex2f(fmaf(round_to_t<T>(__uint_as_float(v[c4 + 3])), kLog2e, cq4.w)));
+                        // per-query constants arrive as two packed pairs per 16-byte load
+                        const ulonglong2 cq = *reinterpret_cast<const ulonglong2 *>(c_q + qbase + c4);
+                        const uint64_t sa = round2_to_t<T>(pk2(__uint_as_float(v[c4]), __uint_as_float(v[c4 + 1])));
+                        const uint64_t sb = round2_to_t<T>(pk2(__uint_as_float(v[c4 + 2]), __uint_as_float(v[c4 + 3])));
+                        float a0, a1, b0, b1;
+                        upk2(fma2(sa, l2e2, cq.x), a0, a1);
+                        upk2(fma2(sb, l2e2, cq.y), b0, b1);
+                        const uint64_t pa = round2_to_t<T>(pk2(ex2f(a0), ex2f(a1)));
+                        const uint64_t pb = round2_to_t<T>(pk2(ex2f(b0), ex2f(b1)));
                         if (kEma) {
-                            const float4 wq4 = *reinterpret_cast<const float4 *>(w_q + qbase + c4);
-                            acc0 = fmaf(p0, wq4.x, acc0);
-                            acc1 = fmaf(p1, wq4.y, acc1);
-                            acc0 = fmaf(p2, wq4.z, acc0);
-                            acc1 = fmaf(p3, wq4.w, acc1);
+                            const ulonglong2 wq = *reinterpret_cast<const ulonglong2 *>(w_q + qbase + c4);
+                            acc2[0] = fma2(pa, wq.x, acc2[0]);
+                            acc2[1] = fma2(pb, wq.y, acc2[1]);
                         }
+                        float p0, p1, p2, p3;
+                        upk2(pa, p0, p1);
+                        upk2(pb, p2, p3);
                         pk[ch][(c4 >> 1)] = P2<T>::pack_rounded(p0, p1);
                         pk[ch][(c4 >> 1) + 1] = P2<T>::pack_rounded(p2, p3);
                     }
                 }
-                acc = acc0 + acc1;
+                float t0, t1;
+                upk2(add2(acc2[0], acc2[1]), t0, t1);
+                acc = t0 + t1;
             } else
 #pragma unroll
             for (int ch = 0; ch < 2; ++ch) {

@@ -85,7 +85,12 @@ def test_streams_against_oracle(spec, force_generic):
                                  eager_fill=eager, beta=beta)
     is16 = dtype != torch.float32
     steps = [chunk] * n_chunks + [1] * n_dec
-    worst = 0.0
+    # 16-bit scores tie often, and one flipped admission changes what a slot holds for the rest of the
+    # stream.  Under the EMA rule in 16 bits the comparison is therefore teacher-forced: every step
+    # starts from the oracle's state, outputs and admissions of that step are compared, then the GPU
+    # cache is re-synchronised.  Everything else is compared free-running.
+    teacher = is16 and rule == "ema"
+    step_agree = []
     for n in steps:
         q = torch.randn(B, H, n, D, generator=g).to(dtype)
         k = torch.randn(B, KVH, n, D, generator=g).to(dtype)
@@ -99,21 +104,26 @@ def test_streams_against_oracle(spec, force_generic):
                                 head_reduction=red, force_generic=force_generic).float().cpu()
         ok, err = close_enough(got, want.float(), is16)
         assert ok, err
+        if teacher:
+            valid = ~ref.mask[0]
+            assert torch.equal(cache.pos[0].cpu()[valid], ref.pos[0][valid])
+            step_agree.append((cache.og_pos[0].cpu()[valid] == ref.og_pos[0][valid]).float().mean().item())
+            copy_state_to_gpu(ref, cache)
     assert cache.kernel_status() == 0
     valid = ~ref.mask[0]
     assert torch.equal(cache.mask[0].cpu(), ref.mask[0])
     assert torch.equal(cache.pos[0].cpu()[valid], ref.pos[0][valid])
     assert torch.equal(cache.stored_tokens[0].cpu(), ref.stored_tokens[0])
     assert torch.equal(cache.start_indices[0].cpu(), ref.start_indices[0])
+    if teacher:
+        # per step, the tokens admitted / kept agree on (almost) every slot
+        assert min(step_agree) >= 0.98 and sum(step_agree) / len(step_agree) >= 0.995, step_agree
+        return
     agree = (cache.og_pos[0].cpu()[valid] == ref.og_pos[0][valid]).float().mean().item()
     if rule == "stride":
         assert agree == 1.0
-    elif not is16:
-        assert agree >= 0.999, agree
     else:
-        # 16-bit scores tie often; the two sides round attention probabilities at slightly different
-        # points, so a small fraction of score-driven decisions may differ on such short streams
-        assert agree >= 0.97, agree
+        assert agree >= 0.999, agree
 
 
 def test_attention_without_update_leaves_state_untouched():
