@@ -36,13 +36,13 @@ namespace {
 constexpr int kBM = 128, kBN = 128;
 constexpr int kSubBytes = 128 * 128;          // [128 rows x 64 elements] 16-bit, 128-byte swizzled
 constexpr int kTileBytes = 2 * kSubBytes;     // [128 x 128]
-constexpr int kOffQ = 0;
-constexpr int kRing = 4;                      // K and V tiles share one ring, in the order they are consumed
-constexpr int kOffRing = kTileBytes;
-constexpr int kOffP = (1 + kRing) * kTileBytes;
-constexpr int kOffBar = 6 * kTileBytes;
+constexpr int kOffQ = 0;                      // two Q tiles (the head pair)
+constexpr int kRing = 3;                      // K and V tiles share one ring, in the order they are consumed
+constexpr int kOffRing = 2 * kTileBytes;
+constexpr int kOffP = (2 + kRing) * kTileBytes;
+constexpr int kOffBar = (3 + kRing) * kTileBytes;
 constexpr int kOffW = kOffBar + 256;          // float w_cache of the tile's 128 rows
-constexpr int kAttnSmem = kOffW + 4096 + 1024; // per-query constants, stats exchange, column partial + slack
+constexpr int kAttnSmem = kOffW + 6656 + 1024; // per-query constants, stats exchange, column partial + slack
 constexpr int kAttnThreads = 320;
 constexpr unsigned kSpin = 1u << 22;
 constexpr int kTmemCols = 512;
@@ -276,6 +276,20 @@ __device__ __forceinline__ uint64_t desc_mn_major(uint32_t saddr, uint32_t n_ato
     d |= (uint64_t)2 << 61;
     return d;
 }
+// The issuing thread's instruction stream is on the kernel's critical path, so descriptors are
+// assembled from a precomputed low word (start address >> 4 | leading offset << 16) plus a
+// compile-time offset, and a constant high word (stride offset, version, swizzle mode).
+constexpr uint32_t kDescHi = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t desc_lo_k(uint32_t saddr) { return ((saddr & 0x3FFFFu) >> 4) | (1u << 16); }
+__device__ __forceinline__ uint32_t desc_lo_mn(uint32_t saddr) {
+    return ((saddr & 0x3FFFFu) >> 4) | ((uint32_t)(kSubBytes >> 4) << 16);
+}
+__device__ __forceinline__ uint64_t desc_from(uint32_t lo) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(kDescHi));
+    return d;
+}
+
 template <typename T> struct P2;
 template <> struct P2<__nv_bfloat16> {
     static __device__ __forceinline__ uint32_t pack(float a, float b) {
@@ -357,6 +371,12 @@ template <typename T> __device__ __forceinline__ uint32_t idesc(bool a_mn, bool 
            ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
 }
 
+// One CTA serves TWO query heads of the same KV head (a GQA pair) for one 128-query tile, so that
+// every K / V tile fetched from L2 feeds two heads: the kernel is bound by L2 -> SM bandwidth when
+// each head streams the keys alone.  While the softmax warps work on one head's logits the tensor
+// core computes the other head's, so a single accumulator per head suffices.
+// Tensor memory (512 columns): S[0], S[1] at 0 / 128; out^T[0], out^T[1] at 256 / 384; during phase A the
+// out^T columns hold the two Q tiles as MMA A-operands instead.
 template <typename T, bool kEma>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -367,18 +387,22 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     uint64_t *q_full = bars + 0, *r_full = bars + 1, *r_empty = bars + 1 + kRing;
     uint64_t *s_full = bars + 9, *s_free = bars + 11, *p_full = bars + 13, *p_free = bars + 14, *o_full = bars + 15;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 16);
-    uint64_t *qt_ready = bars + 17;                             // Q copied into tensor memory
-    float *c_q = reinterpret_cast<float *>(smem + kOffW);       // [128] softmax shift of each query of the tile
-    float *w_q = c_q + 128;                                     // [128] EMA weight of each query
-    float *x_m = w_q + 128;                                     // [2][128] stats exchange between column halves
-    float *x_l = x_m + 256;
-    float *colsum = x_l + 256;                                  // [2][128] second half's column partial
+    uint64_t *qt_ready = bars + 17;                             // both Q tiles copied into tensor memory
+    float *c_q = reinterpret_cast<float *>(smem + kOffW);       // [2 heads][128] softmax shift of each query
+    float *w_q = c_q + 256;                                     // [128] EMA weight of each query
+    float *x_m = w_q + 128;                                     // [2 halves][2 heads][128] stats exchange
+    float *x_l = x_m + 512;
+    float *colsum = x_l + 512;                                  // [2][128] second half's column partial
 
     const int warp = threadIdx.x >> 5, lane_id = threadIdx.x & 31;
     const int qt = blockIdx.x;
-    const int bh = blockIdx.y;
-    const int b = bh / p.H, h = bh % p.H;
-    const long long lane = (long long)b * p.KVH + h / p.G;
+    const int pairs = (p.G + 1) / 2;                            // head pairs per KV head
+    const int lane_i = blockIdx.y / pairs, pair = blockIdx.y % pairs;
+    const int b = lane_i / p.KVH, kvh = lane_i % p.KVH;
+    const long long lane = lane_i;
+    const int head[2] = {kvh * p.G + 2 * pair, kvh * p.G + 2 * pair + 1};
+    const bool head_ok[2] = {true, 2 * pair + 1 < p.G};        // an odd group leaves its last pair half empty
+    const int bh[2] = {b * p.H + head[0], b * p.H + (head_ok[1] ? head[1] : head[0])};
     const Extents e = make_extents(p);
     const int q_hi = min(p.K, kBM * (qt + 1));
     const int n_keys = e.n_cached + q_hi;
@@ -398,7 +422,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         bar_init(p_full, 8);
         bar_init(p_free, 1);
         bar_init(o_full, 1);
-        bar_init(qt_ready, 4);
+        bar_init(qt_ready, 8);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -410,18 +434,21 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     const uint32_t tm_s[2] = {tmem, tmem + 128u};
-    const uint32_t tm_o = tmem + 256u;
-    const uint32_t tm_q = tmem + 384u;   // Q as an A operand: 128 lanes x 64 columns of packed pairs
+    const uint32_t tm_o[2] = {tmem + 256u, tmem + 384u};
+    const uint32_t tm_q[2] = {tmem + 256u, tmem + 320u};   // phase A only: 128 lanes x 64 columns of packed pairs
 
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
         if (lane_id == 0) {
-            bar_expect_tx(q_full, kTileBytes);
-            const int yq = bh * p.Kpad + qt * kBM;
-            tma_2d(smem + kOffQ, &tmQ, 0, yq, q_full);
-            tma_2d(smem + kOffQ + kSubBytes, &tmQ, 64, yq, q_full);
-            // tiles are loaded in exactly the order the MMA warp consumes them:
-            //   phase A: K_0 .. K_{n-1};   phase B: K_0, K_1, V_0, K_2, V_1, ..., K_{n-1}, V_{n-2}, V_{n-1}
+            bar_expect_tx(q_full, 2 * kTileBytes);
+#pragma unroll
+            for (int hd = 0; hd < 2; ++hd) {
+                const int yq = bh[hd] * p.Kpad + qt * kBM;
+                tma_2d(smem + kOffQ + hd * kTileBytes, &tmQ, 0, yq, q_full);
+                tma_2d(smem + kOffQ + hd * kTileBytes + kSubBytes, &tmQ, 64, yq, q_full);
+            }
+            // tiles are loaded in the order the MMA warp first touches them:
+            //   phase A: K_0 .. K_{n-1};   phase B: K_0, V_0, K_1, V_1, ...
             int n_load = 0;
             bool ok = true;
             auto load_tile = [&](const CUtensorMap *tm, int j) {
@@ -437,12 +464,11 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 tma_2d(dst + kSubBytes, tm, 64, y, &r_full[slot]);
                 ++n_load;
             };
-            for (int g = 0; ok && g < nTA; ++g) load_tile(&tmK, g);
+            for (int g = 0; ok && g < nTA && !(p.dbg & 128); ++g) load_tile(&tmK, g);
             for (int jb = 0; ok && jb < nTB; ++jb) {
                 load_tile(&tmK, jb);
-                if (ok && jb >= 1) load_tile(&tmV, jb - 1);
+                if (ok) load_tile(&tmV, jb);
             }
-            if (ok && nTB > 0) load_tile(&tmV, nTB - 1);
         }
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
@@ -451,56 +477,86 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             const uint32_t id_pv = idesc<T>(true, true);     // out^T = V^T P^T: both operands MN-major
             const uint32_t q_addr = s_u32(smem + kOffQ), p_addr = s_u32(smem + kOffP);
             bool ok = bar_wait(q_full, 0, p.status) && bar_wait(qt_ready, 0, p.status);
-            int n_use = 0;     // tiles consumed from the ring, same order as the producer's loads
-            auto ring_wait = [&](uint32_t &addr, int &slot) -> bool {
-                slot = n_use % kRing;
-                if (!bar_wait(&r_full[slot], (n_use / kRing) & 1, p.status)) return false;
-                addr = s_u32(smem + kOffRing + slot * kTileBytes);
-                ++n_use;
-                return true;
+            // low descriptor words of the fixed tiles and of the ring slots
+            const uint32_t q_lo[2] = {desc_lo_k(q_addr), desc_lo_k(q_addr + kTileBytes)};
+            const uint32_t p_lo = desc_lo_mn(p_addr);
+            uint32_t ring_lo_k[kRing], ring_lo_mn[kRing];
+#pragma unroll
+            for (int i = 0; i < kRing; ++i) {
+                const uint32_t a = s_u32(smem + kOffRing + i * kTileBytes);
+                ring_lo_k[i] = desc_lo_k(a);
+                ring_lo_mn[i] = desc_lo_mn(a);
+            }
+            auto ring_wait = [&](int load_idx) -> bool {
+                return bar_wait(&r_full[load_idx % kRing], (load_idx / kRing) & 1, p.status);
             };
-            auto do_qk = [&](int g, bool transposed) -> bool {
-                const int st = g & 1;
-                uint32_t k_addr;
-                int slot;
-                if (!ring_wait(k_addr, slot)) return false;
-                if (g >= 2 && !bar_wait(&s_free[st], ((g >> 1) - 1) & 1, p.status)) return false;
+            // u = running tile index over both phases: S[hd] completes once per u
+            auto do_qk = [&](int u, int load_idx, int hd, bool transposed, bool last_use) -> bool {
+                const int slot = load_idx % kRing;
+                if (hd == 0 && !(p.dbg & 128) && !ring_wait(load_idx)) return false;
+                if (u >= 1 && !(p.dbg & 64) && !bar_wait(&s_free[hd], (u - 1) & 1, p.status)) return false;
                 tc_fence_after();
+                const uint32_t k_lo = ring_lo_k[slot];
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {
-                    const uint32_t off = (ks >> 2) * kSubBytes + (ks & 3) * 32;
-                    const uint64_t dk = desc_k_major(k_addr + off);
-                    // phase A: S = Q K^T with Q read from tensor memory (halves the shared-memory reads);
-                    // phase B: S^T = K Q^T with both operands in shared memory
-                    if (transposed) tc_mma(tm_s[st], dk, desc_k_major(q_addr + off), id_kk, ks > 0 ? 1u : 0u);
-                    else tc_mma_ts(tm_s[st], tm_q + ks * 8, dk, id_kk, ks > 0 ? 1u : 0u);
+                    const uint32_t off = (uint32_t)(((ks >> 2) * kSubBytes + (ks & 3) * 32) >> 4);
+                    // phase A: S = Q K^T with Q read from tensor memory; phase B: S^T = K Q^T
+                    if (transposed) tc_mma(tm_s[hd], desc_from(k_lo + off), desc_from(q_lo[hd] + off), id_kk, ks > 0 ? 1u : 0u);
+                    else tc_mma_ts(tm_s[hd], tm_q[hd] + ks * 8, desc_from(k_lo + off), id_kk, ks > 0 ? 1u : 0u);
                 }
-                tc_commit(&r_empty[slot]);
-                tc_commit(&s_full[st]);
+                if (last_use) tc_commit(&r_empty[slot]);
+                tc_commit(&s_full[hd]);
                 return true;
             };
-            auto do_pv = [&](int j) -> bool {
-                uint32_t v_addr;
-                int slot;
-                if (!bar_wait(p_full, j & 1, p.status)) return false;
-                if (!ring_wait(v_addr, slot)) return false;
+            auto do_pv = [&](int jb, int hd) -> bool {
+                const int load_idx = nTA + 2 * jb + 1;
+                const int slot = load_idx % kRing;
+                if (!bar_wait(p_full, (2 * jb + hd) & 1, p.status)) return false;
+                if (hd == 0 && !ring_wait(load_idx)) return false;
                 tc_fence_after();
+                const uint32_t v_lo = ring_lo_mn[slot];
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {
-                    const uint64_t da = desc_mn_major(v_addr + ks * 2048, kSubBytes);   // V^T: dims x keys
-                    const uint64_t db = desc_mn_major(p_addr + ks * 2048, kSubBytes);   // P^T: keys x queries
-                    tc_mma(tm_o, da, db, id_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                    const uint32_t off = (uint32_t)((ks * 2048) >> 4);
+                    // out^T += V^T (dims x keys) * P^T (keys x queries)
+                    tc_mma(tm_o[hd], desc_from(v_lo + off), desc_from(p_lo + off), id_pv, (jb > 0 || ks > 0) ? 1u : 0u);
                 }
-                tc_commit(&r_empty[slot]);
+                if (hd == 1) tc_commit(&r_empty[slot]);
                 tc_commit(p_free);
                 return true;
             };
-            for (int g = 0; ok && g < nTA; ++g) ok = do_qk(g, false);
-            for (int jb = 0; ok && jb < nTB; ++jb) {
-                ok = do_qk(nTA + jb, true);          // phase B: S^T = K Q^T (rows = keys)
-                if (ok && jb >= 1) ok = do_pv(jb - 1);
+            // phase A: the two heads' MMAs are interleaved k-step by k-step, so that consecutive
+            // instructions accumulate into different tensor-memory tiles
+            for (int g = 0; ok && g < nTA; ++g) {
+                const int slot = g % kRing;
+                if (!(p.dbg & 128)) ok = ring_wait(g);
+                if (ok && g >= 1 && !(p.dbg & 64))
+                    ok = bar_wait(&s_free[0], (g - 1) & 1, p.status) && bar_wait(&s_free[1], (g - 1) & 1, p.status);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t k_lo = ring_lo_k[slot];
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint32_t off = (uint32_t)(((ks >> 2) * kSubBytes + (ks & 3) * 32) >> 4);
+                    const uint64_t dk = desc_from(k_lo + off);
+                    tc_mma_ts(tm_s[0], tm_q[0] + ks * 8, dk, id_kk, ks > 0 ? 1u : 0u);
+                    tc_mma_ts(tm_s[1], tm_q[1] + ks * 8, dk, id_kk, ks > 0 ? 1u : 0u);
+                }
+                tc_commit(&r_empty[slot]);
+                tc_commit(&s_full[0]);
+                tc_commit(&s_full[1]);
             }
-            if (ok && nTB > 0) ok = do_pv(nTB - 1);
+            if (ok && nTB > 0) {
+                ok = do_qk(nTA, nTA, 0, true, false);
+                if (ok) ok = do_qk(nTA, nTA, 1, true, true);
+            }
+            for (int jb = 0; ok && jb < nTB; ++jb) {
+                const bool more = jb + 1 < nTB;
+                ok = do_pv(jb, 0);
+                if (ok && more) ok = do_qk(nTA + jb + 1, nTA + 2 * (jb + 1), 0, true, false);
+                if (ok) ok = do_pv(jb, 1);
+                if (ok && more) ok = do_qk(nTA + jb + 1, nTA + 2 * (jb + 1), 1, true, true);
+            }
             if (ok) tc_commit(o_full);
         }
     } else {
@@ -512,21 +568,22 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const uint32_t lane_base = (uint32_t)(32 * quarter) << 16;
         bool ok = true;
 
-        // ---- Q tile -> tensor memory (rows = lanes, the row's 64 words in order)
+        // ---- Q tiles -> tensor memory (rows = lanes, the row's 64 words in order): half h copies head h
         ok = bar_wait(q_full, 0, p.status);
-        if (half == 0) {
+        {
             uint32_t qw[2][32];
+            const uint8_t *qsm = smem + kOffQ + half * kTileBytes;
 #pragma unroll
             for (int c = 0; c < 16; ++c) {
-                const uint4 w4 = *reinterpret_cast<const uint4 *>(smem + kOffQ + (c >> 3) * kSubBytes + row * 128 +
+                const uint4 w4 = *reinterpret_cast<const uint4 *>(qsm + (c >> 3) * kSubBytes + row * 128 +
                                                                   (((c & 7) ^ (row & 7)) << 4));
                 qw[c >> 3][4 * (c & 7)] = w4.x;
                 qw[c >> 3][4 * (c & 7) + 1] = w4.y;
                 qw[c >> 3][4 * (c & 7) + 2] = w4.z;
                 qw[c >> 3][4 * (c & 7) + 3] = w4.w;
             }
-            tc_st32(tm_q + lane_base, qw[0]);
-            tc_st32(tm_q + lane_base + 32, qw[1]);
+            tc_st32(tm_q[half] + lane_base, qw[0]);
+            tc_st32(tm_q[half] + lane_base + 32, qw[1]);
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             tc_fence_before();
             __syncwarp();
@@ -538,198 +595,210 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             const int qg = qt * kBM + row;
             const bool row_ok = qg < p.K;
             const int row_limit = e.n_cached + (row_ok ? qg + 1 : 0);     // visible columns: [0, row_limit)
-            float m_run = -INFINITY, l_run = 0.f;
+            float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
             for (int g = 0; g < nTA; ++g) {
-                const int st = g & 1;
-                // after a failed (timed-out) wait the warp keeps walking the loop without waiting, so
-                // that the block-wide barriers below are still reached by everyone
-                if (ok) ok = bar_wait(&s_full[st], (g >> 1) & 1, p.status);
-                tc_fence_after();
                 const bool full_tile = (g + 1) * kBN <= e.n_cached + qt * kBM + 1 && (qt + 1) * kBM <= p.K;
-                uint32_t va[2][32];
-                tc_ld32(tm_s[st] + lane_base + 64 * half, va[0]);
-                tc_ld32(tm_s[st] + lane_base + 64 * half + 32, va[1]);
-                tc_ld_wait();
-                // the accumulator can be overwritten as soon as it is in registers
-                tc_fence_before();
-                __syncwarp();
-                if (lane_id == 0) bar_arrive(&s_free[st]);
-                if (p.dbg & 4) continue;
-                // the statistics must be those of the logits ROUNDED to T: in a peaked row a single
-                // logit carries the sum, and its rounding (up to 2^-9 of its value) moves every
-                // probability of the row by far more than T's resolution
-                uint64_t r2[2][16];
-                float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-                for (int ch = 0; ch < 2; ++ch) {
-                    const int col0 = g * kBN + 64 * half + 32 * ch;
-#pragma unroll
-                    for (int c = 0; c < 32; c += 2) {
-                        uint64_t r = pk2(__uint_as_float(va[ch][c]), __uint_as_float(va[ch][c + 1]));
-                        if (!(p.dbg & 16)) r = round2_to_t<T>(r);
-                        float s0, s1;
-                        upk2(r, s0, s1);
-                        if (!full_tile) {
-                            if ((col0 + c) >= row_limit) s0 = -INFINITY;
-                            if ((col0 + c + 1) >= row_limit) s1 = -INFINITY;
-                            r = pk2(s0, s1);
-                        }
-                        r2[ch][c >> 1] = r;
-                        mx[(c >> 1) & 1] = max3(mx[(c >> 1) & 1], s0, s1);
+                for (int hd = 0; hd < 2; ++hd) {
+                    // after a failed (timed-out) wait the warp keeps walking the loops without waiting, so
+                    // that the block-wide barriers below are still reached by everyone
+                    if (ok) ok = bar_wait(&s_full[hd], g & 1, p.status);
+                    tc_fence_after();
+                    uint32_t va[2][32];
+                    if (!(p.dbg & 32)) {
+                    tc_ld32(tm_s[hd] + lane_base + 64 * half, va[0]);
+                    tc_ld32(tm_s[hd] + lane_base + 64 * half + 32, va[1]);
+                    tc_ld_wait();
                     }
-                }
-                const float m_new = max3(mx[0], mx[1], m_run);
-                if (m_new != -INFINITY) {
-                    const float mneg = -m_new * kLog2e;
-                    const uint64_t mneg2 = pk2(mneg, mneg), l2e2 = pk2(kLog2e, kLog2e);
-                    uint64_t sum2[2] = {0ull, 0ull};
+                    // the accumulator can be overwritten as soon as it is in registers
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane_id == 0) bar_arrive(&s_free[hd]);
+                    if ((p.dbg & 4) || ((p.dbg & 256) && quarter == 1)) continue;
+                    // the statistics must be those of the logits ROUNDED to T: in a peaked row a single
+                    // logit carries the sum, and its rounding (up to 2^-9 of its value) moves every
+                    // probability of the row by far more than T's resolution
+                    uint64_t r2[2][16];
+                    float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-                    for (int ch = 0; ch < 2; ++ch)
+                    for (int ch = 0; ch < 2; ++ch) {
+                        const int col0 = g * kBN + 64 * half + 32 * ch;
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            float a0, a1;
-                            upk2(fma2(r2[ch][i], l2e2, mneg2), a0, a1);
-                            if (p.dbg & 8) sum2[i & 1] = add2(sum2[i & 1], pk2(a0, a1));
-                            else sum2[i & 1] = add2(sum2[i & 1], pk2(ex2f(a0), ex2f(a1)));
+                        for (int c = 0; c < 32; c += 2) {
+                            uint64_t r = round2_to_t<T>(pk2(__uint_as_float(va[ch][c]), __uint_as_float(va[ch][c + 1])));
+                            float s0, s1;
+                            upk2(r, s0, s1);
+                            if (!full_tile) {
+                                if ((col0 + c) >= row_limit) s0 = -INFINITY;
+                                if ((col0 + c + 1) >= row_limit) s1 = -INFINITY;
+                                r = pk2(s0, s1);
+                            }
+                            r2[ch][c >> 1] = r;
+                            mx[(c >> 1) & 1] = max3(mx[(c >> 1) & 1], s0, s1);
                         }
-                    float t0, t1;
-                    upk2(add2(sum2[0], sum2[1]), t0, t1);
-                    l_run = l_run * ex2f(fmaf(m_run, kLog2e, mneg)) + (t0 + t1);
-                    m_run = m_new;
+                    }
+                    const float m_new = max3(mx[0], mx[1], m_run[hd]);
+                    if (m_new != -INFINITY) {
+                        const float mneg = -m_new * kLog2e;
+                        const uint64_t mneg2 = pk2(mneg, mneg), l2e2 = pk2(kLog2e, kLog2e);
+                        uint64_t sum2[2] = {0ull, 0ull};
+#pragma unroll
+                        for (int ch = 0; ch < 2; ++ch)
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                float a0, a1;
+                                upk2(fma2(r2[ch][i], l2e2, mneg2), a0, a1);
+                                sum2[i & 1] = add2(sum2[i & 1], pk2(ex2f(a0), ex2f(a1)));
+                            }
+                        float t0, t1;
+                        upk2(add2(sum2[0], sum2[1]), t0, t1);
+                        l_run[hd] = l_run[hd] * ex2f(fmaf(m_run[hd], kLog2e, mneg)) + (t0 + t1);
+                        m_run[hd] = m_new;
+                    }
                 }
             }
             // combine the two column halves of each row; publish shift and EMA weight per query
-            x_m[half * 128 + row] = m_run;
-            x_l[half * 128 + row] = l_run;
+#pragma unroll
+            for (int hd = 0; hd < 2; ++hd) {
+                x_m[(half * 2 + hd) * 128 + row] = m_run[hd];
+                x_l[(half * 2 + hd) * 128 + row] = l_run[hd];
+            }
             softmax_sync();
-            if (half == 0) {
-                const float m0 = x_m[row], m1 = x_m[128 + row];
+            {
+                const int hd = half;   // the two halves each finish one head
+                const float m0 = x_m[hd * 128 + row], m1 = x_m[(2 + hd) * 128 + row];
                 const float mm = fmaxf(m0, m1);
                 float cq = -INFINITY;
                 if (row_ok && mm != -INFINITY) {
-                    const float l = x_l[row] * (m0 == -INFINITY ? 0.f : ex2f((m0 - mm) * kLog2e)) +
-                                    x_l[128 + row] * (m1 == -INFINITY ? 0.f : ex2f((m1 - mm) * kLog2e));
+                    const float l = x_l[hd * 128 + row] * (m0 == -INFINITY ? 0.f : ex2f((m0 - mm) * kLog2e)) +
+                                    x_l[(2 + hd) * 128 + row] * (m1 == -INFINITY ? 0.f : ex2f((m1 - mm) * kLog2e));
                     cq = -mm * kLog2e - __log2f(l);
                 }
-                c_q[row] = cq;
-                w_q[row] = (kEma && row_ok) ? p.ema_w_cache[qg] : 0.f;
+                c_q[hd * 128 + row] = cq;
+                if (hd == 0) w_q[row] = (kEma && row_ok) ? p.ema_w_cache[qg] : 0.f;
             }
             softmax_sync();
         }
 
         // ---- phase B: rows are keys (S^T); this thread owns key `key`, queries [64 half, 64 half + 64)
         const T *w_new = reinterpret_cast<const T *>(p.ema_w_new);
-        float *part = p.colpart + ((long long)bh * p.nQT + qt) * p.Rpad;
         uint8_t *pt_row = smem + kOffP + half * kSubBytes + row * 128;
         for (int jb = 0; jb < nTB; ++jb) {
-            const int g = nTA + jb, st = g & 1;
-            if (ok) ok = bar_wait(&s_full[st], (g >> 1) & 1, p.status);
-            tc_fence_after();
+            const int u = nTA + jb;
             const int key = jb * kBN + row;                      // row of the compacted key matrix
             const bool key_ok = key < n_keys;
             const bool is_new = key >= e.n_cached;
             // query q of the tile sees this key iff  qt*128 + q >= key - n_cached
             const int q_min = key_ok ? key - e.n_cached - qt * kBM : kBM;
             const bool full_tile = (jb + 1) * kBN <= e.n_cached + qt * kBM + 1 && (qt + 1) * kBM <= p.K;
-            float acc = 0.f;
-            uint32_t va[2][32];
-            tc_ld32(tm_s[st] + lane_base + 64 * half, va[0]);
-            tc_ld32(tm_s[st] + lane_base + 64 * half + 32, va[1]);
-            tc_ld_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane_id == 0) bar_arrive(&s_free[st]);
-            uint32_t pk[2][16];
             // every key of the tile is a cached one and every (key, query) pair is visible: the common
             // case, kept free of per-element control flow so that the exponentials overlap
             const bool fast_tile = full_tile && (jb + 1) * kBN <= e.n_cached;
-            if (p.dbg & 4) {
 #pragma unroll
-                for (int i = 0; i < 16; ++i) pk[0][i] = pk[1][i] = va[0][i];
-            } else if (fast_tile) {
-                uint64_t acc2[2] = {0ull, 0ull};
-                const uint64_t l2e2 = pk2(kLog2e, kLog2e);
+            for (int hd = 0; hd < 2; ++hd) {
+                const int v_idx = 2 * jb + hd;                   // sequence number of this (tile, head)
+                const float *cq_h = c_q + hd * 128;
+                if (ok) ok = bar_wait(&s_full[hd], u & 1, p.status);
+                tc_fence_after();
+                float acc = 0.f;
+                uint32_t va[2][32];
+                tc_ld32(tm_s[hd] + lane_base + 64 * half, va[0]);
+                tc_ld32(tm_s[hd] + lane_base + 64 * half + 32, va[1]);
+                tc_ld_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane_id == 0) bar_arrive(&s_free[hd]);
+                uint32_t pk[2][16];
+                if (p.dbg & 4) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) pk[0][i] = pk[1][i] = va[0][i];
+                } else if (fast_tile) {
+                    uint64_t acc2[2] = {0ull, 0ull};
+                    const uint64_t l2e2 = pk2(kLog2e, kLog2e);
+#pragma unroll
+                    for (int ch = 0; ch < 2; ++ch) {
+                        uint32_t (&v)[32] = va[ch];
+                        const int qbase = 64 * half + 32 * ch;
+#pragma unroll
+                        for (int c4 = 0; c4 < 32; c4 += 4) {
+                            // per-query constants arrive as two packed pairs per 16-byte load
+                            const ulonglong2 cq = *reinterpret_cast<const ulonglong2 *>(cq_h + qbase + c4);
+                            const uint64_t sa = round2_to_t<T>(pk2(__uint_as_float(v[c4]), __uint_as_float(v[c4 + 1])));
+                            const uint64_t sb = round2_to_t<T>(pk2(__uint_as_float(v[c4 + 2]), __uint_as_float(v[c4 + 3])));
+                            float a0, a1, b0, b1;
+                            upk2(fma2(sa, l2e2, cq.x), a0, a1);
+                            upk2(fma2(sb, l2e2, cq.y), b0, b1);
+                            const uint64_t pa = round2_to_t<T>(pk2(ex2f(a0), ex2f(a1)));
+                            const uint64_t pb = round2_to_t<T>(pk2(ex2f(b0), ex2f(b1)));
+                            if (kEma) {
+                                const ulonglong2 wq = *reinterpret_cast<const ulonglong2 *>(w_q + qbase + c4);
+                                acc2[0] = fma2(pa, wq.x, acc2[0]);
+                                acc2[1] = fma2(pb, wq.y, acc2[1]);
+                            }
+                            float p0, p1, p2, p3;
+                            upk2(pa, p0, p1);
+                            upk2(pb, p2, p3);
+                            pk[ch][(c4 >> 1)] = P2<T>::pack_rounded(p0, p1);
+                            pk[ch][(c4 >> 1) + 1] = P2<T>::pack_rounded(p2, p3);
+                        }
+                    }
+                    float t0, t1;
+                    upk2(add2(acc2[0], acc2[1]), t0, t1);
+                    acc = t0 + t1;
+                } else {
+#pragma unroll
+                    for (int ch = 0; ch < 2; ++ch) {
+                        uint32_t (&v)[32] = va[ch];
+                        const int qbase = 64 * half + 32 * ch;
+#pragma unroll
+                        for (int c4 = 0; c4 < 32; c4 += 4) {
+                            const float4 cq4 = *reinterpret_cast<const float4 *>(cq_h + qbase + c4);
+                            const float4 wq4 = *reinterpret_cast<const float4 *>(w_q + qbase + c4);
+                            const float cqv[4] = {cq4.x, cq4.y, cq4.z, cq4.w};
+                            const float wqv[4] = {wq4.x, wq4.y, wq4.z, wq4.w};
+                            float pr[4];
+#pragma unroll
+                            for (int uu = 0; uu < 4; ++uu) {
+                                const float sv = round_to_t<T>(__uint_as_float(v[c4 + uu]));
+                                float pv = ex2f(fmaf(sv, kLog2e, cqv[uu]));
+                                if (!full_tile && (qbase + c4 + uu) < q_min) pv = 0.f;
+                                pr[uu] = round_to_t<T>(pv);
+                                if (kEma) {
+                                    if (!is_new) {
+                                        acc = fmaf(pr[uu], wqv[uu], acc);
+                                    } else if (pr[uu] != 0.f) {
+                                        const int d = qt * kBM + qbase + c4 + uu - (key - e.n_cached);
+                                        acc += round_to_t<T>(__fmul_rn(pr[uu], Elem<T>::to_f(w_new[d])));
+                                    }
+                                }
+                            }
+                            pk[ch][(c4 >> 1)] = P2<T>::pack_rounded(pr[0], pr[1]);
+                            pk[ch][(c4 >> 1) + 1] = P2<T>::pack_rounded(pr[2], pr[3]);
+                        }
+                    }
+                }
+                // P^T of the previous (tile, head) must have been consumed before this one overwrites it
+                if (ok && v_idx >= 1) ok = bar_wait(p_free, (v_idx - 1) & 1, p.status);
 #pragma unroll
                 for (int ch = 0; ch < 2; ++ch) {
-                    uint32_t (&v)[32] = va[ch];
-                    const int qbase = 64 * half + 32 * ch;
 #pragma unroll
-                    for (int c4 = 0; c4 < 32; c4 += 4) {
-                        // per-query constants arrive as two packed pairs per 16-byte load
-                        const ulonglong2 cq = *reinterpret_cast<const ulonglong2 *>(c_q + qbase + c4);
-                        const uint64_t sa = round2_to_t<T>(pk2(__uint_as_float(v[c4]), __uint_as_float(v[c4 + 1])));
-                        const uint64_t sb = round2_to_t<T>(pk2(__uint_as_float(v[c4 + 2]), __uint_as_float(v[c4 + 3])));
-                        float a0, a1, b0, b1;
-                        upk2(fma2(sa, l2e2, cq.x), a0, a1);
-                        upk2(fma2(sb, l2e2, cq.y), b0, b1);
-                        const uint64_t pa = round2_to_t<T>(pk2(ex2f(a0), ex2f(a1)));
-                        const uint64_t pb = round2_to_t<T>(pk2(ex2f(b0), ex2f(b1)));
-                        if (kEma) {
-                            const ulonglong2 wq = *reinterpret_cast<const ulonglong2 *>(w_q + qbase + c4);
-                            acc2[0] = fma2(pa, wq.x, acc2[0]);
-                            acc2[1] = fma2(pb, wq.y, acc2[1]);
-                        }
-                        float p0, p1, p2, p3;
-                        upk2(pa, p0, p1);
-                        upk2(pb, p2, p3);
-                        pk[ch][(c4 >> 1)] = P2<T>::pack_rounded(p0, p1);
-                        pk[ch][(c4 >> 1) + 1] = P2<T>::pack_rounded(p2, p3);
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        const int chunk = ch * 4 + q4;
+                        *reinterpret_cast<uint4 *>(pt_row + ((chunk ^ (row & 7)) << 4)) =
+                            make_uint4(pk[ch][4 * q4], pk[ch][4 * q4 + 1], pk[ch][4 * q4 + 2], pk[ch][4 * q4 + 3]);
                     }
                 }
-                float t0, t1;
-                upk2(add2(acc2[0], acc2[1]), t0, t1);
-                acc = t0 + t1;
-            } else
-#pragma unroll
-            for (int ch = 0; ch < 2; ++ch) {
-                uint32_t (&v)[32] = va[ch];
-                const int qbase = 64 * half + 32 * ch;
-#pragma unroll
-                for (int c4 = 0; c4 < 32; c4 += 4) {
-                    const float4 cq4 = *reinterpret_cast<const float4 *>(c_q + qbase + c4);
-                    const float4 wq4 = *reinterpret_cast<const float4 *>(w_q + qbase + c4);
-                    const float cqv[4] = {cq4.x, cq4.y, cq4.z, cq4.w};
-                    const float wqv[4] = {wq4.x, wq4.y, wq4.z, wq4.w};
-                    float pr[4];
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        const float s = round_to_t<T>(__uint_as_float(v[c4 + u]));
-                        float pv = ex2f(fmaf(s, kLog2e, cqv[u]));
-                        if (!full_tile && (qbase + c4 + u) < q_min) pv = 0.f;
-                        pr[u] = round_to_t<T>(pv);
-                        if (kEma) {
-                            if (!is_new) {
-                                acc = fmaf(pr[u], wqv[u], acc);
-                            } else if (pr[u] != 0.f) {
-                                const int d = qt * kBM + qbase + c4 + u - (key - e.n_cached);
-                                acc += round_to_t<T>(__fmul_rn(pr[u], Elem<T>::to_f(w_new[d])));
-                            }
-                        }
-                    }
-                    pk[ch][(c4 >> 1)] = P2<T>::pack_rounded(pr[0], pr[1]);
-                    pk[ch][(c4 >> 1) + 1] = P2<T>::pack_rounded(pr[2], pr[3]);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane_id == 0) bar_arrive(p_full);
+                if (kEma) {
+                    // column EMA partial of this query tile = row sum of P^T over both query halves;
+                    // double-buffered by sequence parity: the next barrier orders the reuse
+                    if (half == 1) colsum[(v_idx & 1) * 128 + row] = acc;
+                    softmax_sync();
+                    if (half == 0 && key_ok && key >= (int)e.sinks && head_ok[hd])
+                        p.colpart[((long long)bh[hd] * p.nQT + qt) * p.Rpad + key] = acc + colsum[(v_idx & 1) * 128 + row];
                 }
-            }
-            // P^T of the previous tile must have been consumed before this one overwrites it
-            if (ok && jb >= 1) ok = bar_wait(p_free, (jb - 1) & 1, p.status);
-#pragma unroll
-            for (int ch = 0; ch < 2; ++ch) {
-#pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    const int chunk = ch * 4 + q4;
-                    *reinterpret_cast<uint4 *>(pt_row + ((chunk ^ (row & 7)) << 4)) =
-                        make_uint4(pk[ch][4 * q4], pk[ch][4 * q4 + 1], pk[ch][4 * q4 + 2], pk[ch][4 * q4 + 3]);
-                }
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            if (lane_id == 0) bar_arrive(p_full);
-            if (kEma) {
-                // column EMA partial of this query tile = row sum of P^T over both query halves
-                // double-buffered by tile parity: the barrier of the next tile orders the reuse
-                if (half == 1) colsum[(jb & 1) * 128 + row] = acc;
-                softmax_sync();
-                if (half == 0 && key_ok && key >= (int)e.sinks) part[key] = acc + colsum[(jb & 1) * 128 + row];
             }
         }
 
@@ -738,17 +807,21 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             tc_fence_after();
             const int d = row;
 #pragma unroll 1
-            for (int ch = 0; ch < 2; ++ch) {
-                uint32_t v[32];
-                const int qbase = 64 * half + 32 * ch;
-                tc_ld32(tm_o + lane_base + qbase, v);
-                tc_ld_wait();
+            for (int hd = 0; hd < 2; ++hd) {
+                if (!head_ok[hd]) continue;
+#pragma unroll 1
+                for (int ch = 0; ch < 2; ++ch) {
+                    uint32_t v[32];
+                    const int qbase = 64 * half + 32 * ch;
+                    tc_ld32(tm_o[hd] + lane_base + qbase, v);
+                    tc_ld_wait();
 #pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    const int qg = qt * kBM + qbase + c;
-                    if (qg < p.K) {
-                        T *orow = reinterpret_cast<T *>(p.out) + b * p.osb + h * p.osh + (long long)qg * p.ost;
-                        orow[d] = Elem<T>::from_f(__uint_as_float(v[c]));
+                    for (int c = 0; c < 32; ++c) {
+                        const int qg = qt * kBM + qbase + c;
+                        if (qg < p.K) {
+                            T *orow = reinterpret_cast<T *>(p.out) + b * p.osb + head[hd] * p.osh + (long long)qg * p.ost;
+                            orow[d] = Elem<T>::from_f(__uint_as_float(v[c]));
+                        }
                     }
                 }
             }
@@ -957,7 +1030,7 @@ int launch_prefill_tuned(const Dims &d, const ckv_layer_state *st, const void *q
     const long long prep_work = ((long long)d.B * d.KVH * s.Rpad + (long long)d.B * d.H * s.Kpad) * 8;
     int prep_blocks = (int)((prep_work + 255) / 256);
     if (prep_blocks > 148 * 16) prep_blocks = 148 * 16;
-    const dim3 grid(s.nQT, d.B * d.H);
+    const dim3 grid(s.nQT, d.B * d.KVH * ((d.G + 1) / 2));   // one CTA per (query tile, KV head, head pair)
     if (d.dtype == CKV_BF16) {
         prefill_prep_kernel<__nv_bfloat16><<<prep_blocks, 256, 0, stream>>>(p);
         if (hook) hook->before(stream, "prefill_attn_kernel");
