@@ -23,8 +23,6 @@
 // Every mbarrier wait is bounded; on a time-out the status word is raised and all roles leave.
 #include <cuda.h>
 
-#include <stdlib.h>
-
 #include <type_traits>
 
 #include "ckv_common.cuh"
@@ -37,13 +35,13 @@ constexpr int kBM = 128, kBN = 128;
 constexpr int kSubBytes = 128 * 128;          // [128 rows x 64 elements] 16-bit, 128-byte swizzled
 constexpr int kTileBytes = 2 * kSubBytes;     // [128 x 128]
 constexpr int kOffQ = 0;                      // two Q tiles (the head pair)
-constexpr int kRing = 3;                      // K and V tiles share one ring, in the order they are consumed
-constexpr int kOffRing = 2 * kTileBytes;
-constexpr int kOffP = (2 + kRing) * kTileBytes;
-constexpr int kOffBar = (3 + kRing) * kTileBytes;
-constexpr int kOffW = kOffBar + 256;          // float w_cache of the tile's 128 rows
-constexpr int kAttnSmem = kOffW + 6656 + 1024; // per-query constants, stats exchange, column partial + slack
-constexpr int kAttnThreads = 320;
+constexpr int kOffRing = 2 * kTileBytes;      // two K / V slots
+constexpr int kOffP = 4 * kTileBytes;         // two P^T tiles (one per head); contiguous with the ring
+constexpr int kRingA = 4;                     // phase A cycles K tiles through ring + P^T space
+constexpr int kOffBar = 6 * kTileBytes;
+constexpr int kOffW = kOffBar + 256;          // per-query constants and the statistics exchange
+constexpr int kAttnSmem = kOffW + 6144 + 1024; // + alignment slack
+constexpr int kAttnThreads = 576;             // TMA warp, MMA warp, 2 x 8 softmax warps
 constexpr unsigned kSpin = 1u << 22;
 constexpr int kTmemCols = 512;
 constexpr float kLog2e = 1.4426950408889634f;
@@ -67,11 +65,10 @@ struct PrefillParams {
     void *qs;          // [B*H][Kpad][128]
     void *kcat;        // [B*KVH][Rpad][128]
     void *vcat;        // [B*KVH][Rpad][128]
-    float *colpart;    // [B*H][nQT][Rpad]
+    float *colpart;    // [B*H][nQT][2 query halves][Rpad]
     void *new_scores;  // [B*KVH][K]
     int B, KVH, H, G, NS, S, C, K, Kpad, Rpad, nQT;
     int ema, head_reduction;
-    int dbg;           // timing experiments only: 1 = skip phase A, 2 = skip phase B, 4 = skip softmax math
     float rs, beta_pow;
 };
 
@@ -362,7 +359,11 @@ template <typename T> __device__ __forceinline__ uint64_t round2_to_t(uint64_t x
     return sub2(c2, sub2(c2, x2));
 }
 
-__device__ __forceinline__ void softmax_sync() { asm volatile("bar.sync 2, 256;" ::: "memory"); }
+// barrier among the 256 threads (8 warps) that serve one head of the pair
+__device__ __forceinline__ void group_sync(int grp) {
+    if (grp == 0) asm volatile("bar.sync 2, 256;" ::: "memory");
+    else asm volatile("bar.sync 3, 256;" ::: "memory");
+}
 
 // Instruction descriptor: fp32 accumulate, operand format, A / B major-ness, N, M.
 template <typename T> __device__ __forceinline__ uint32_t idesc(bool a_mn, bool b_mn) {
@@ -371,12 +372,19 @@ template <typename T> __device__ __forceinline__ uint32_t idesc(bool a_mn, bool 
            ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
 }
 
+// Logits that the causal mask hides are replaced by this finite value: it survives the rounding
+// arithmetic (an infinity would turn into NaN there), its exponential is exactly 0, and a running
+// maximum still at or below kMaskedBelow means "nothing visible yet".
+constexpr float kMasked = -1.0e30f, kMaskedBelow = -1.0e29f;
+
 // One CTA serves TWO query heads of the same KV head (a GQA pair) for one 128-query tile, so that
-// every K / V tile fetched from L2 feeds two heads: the kernel is bound by L2 -> SM bandwidth when
-// each head streams the keys alone.  While the softmax warps work on one head's logits the tensor
-// core computes the other head's, so a single accumulator per head suffices.
+// every K / V tile fetched from L2 feeds two heads.  Each head has its own group of 8 softmax warps,
+// its own logit accumulator and its own P^T buffer: the two groups never wait for each other, and
+// while one group's warps stall on a barrier the other group's keep the SM's pipes busy.
 // Tensor memory (512 columns): S[0], S[1] at 0 / 128; out^T[0], out^T[1] at 256 / 384; during phase A the
 // out^T columns hold the two Q tiles as MMA A-operands instead.
+// Shared memory: Q[2] | ring[2] | P^T[2] (32 KB each).  Phase A streams K through ring AND P^T space
+// (4 slots); phase B keeps K in ring[0], V in ring[1].
 template <typename T, bool kEma>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -384,15 +392,14 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kOffBar);
-    uint64_t *q_full = bars + 0, *r_full = bars + 1, *r_empty = bars + 1 + kRing;
-    uint64_t *s_full = bars + 9, *s_free = bars + 11, *p_full = bars + 13, *p_free = bars + 14, *o_full = bars + 15;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 16);
-    uint64_t *qt_ready = bars + 17;                             // both Q tiles copied into tensor memory
+    uint64_t *q_full = bars + 0, *ra_full = bars + 1, *ra_empty = bars + 5, *rb_full = bars + 9, *rb_empty = bars + 11;
+    uint64_t *s_full = bars + 13, *s_free = bars + 15, *p_full = bars + 17, *p_free = bars + 19;
+    uint64_t *o_full = bars + 21, *qt_ready = bars + 22, *a_done = bars + 23;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 24);
     float *c_q = reinterpret_cast<float *>(smem + kOffW);       // [2 heads][128] softmax shift of each query
-    float *w_q = c_q + 256;                                     // [128] EMA weight of each query
-    float *x_m = w_q + 128;                                     // [2 halves][2 heads][128] stats exchange
+    float *w_q = c_q + 256;                                     // [2 heads][128] EMA weight of each query (one copy per group)
+    float *x_m = w_q + 256;                                     // [2 heads][2 halves][128] stats exchange
     float *x_l = x_m + 512;
-    float *colsum = x_l + 512;                                  // [2][128] second half's column partial
 
     const int warp = threadIdx.x >> 5, lane_id = threadIdx.x & 31;
     const int qt = blockIdx.x;
@@ -406,23 +413,25 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const Extents e = make_extents(p);
     const int q_hi = min(p.K, kBM * (qt + 1));
     const int n_keys = e.n_cached + q_hi;
-    const int nT = (n_keys + kBN - 1) / kBN;
-    const int nTA = (p.dbg & 1) ? 0 : nT, nTB = (p.dbg & 2) ? 0 : nT;
+    const int nT = (n_keys + kBN - 1) / kBN;                    // key tiles of either phase
 
     if (threadIdx.x == 0) {
         bar_init(q_full, 1);
-        for (int i = 0; i < kRing; ++i) {
-            bar_init(&r_full[i], 1);
-            bar_init(&r_empty[i], 1);
+        for (int i = 0; i < kRingA; ++i) {
+            bar_init(&ra_full[i], 1);
+            bar_init(&ra_empty[i], 1);
         }
         for (int i = 0; i < 2; ++i) {
+            bar_init(&rb_full[i], 1);
+            bar_init(&rb_empty[i], 1);
             bar_init(&s_full[i], 1);
             bar_init(&s_free[i], 8);
+            bar_init(&p_full[i], 8);
+            bar_init(&p_free[i], 1);
         }
-        bar_init(p_full, 8);
-        bar_init(p_free, 1);
         bar_init(o_full, 1);
-        bar_init(qt_ready, 8);
+        bar_init(qt_ready, 16);
+        bar_init(a_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -447,27 +456,27 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 tma_2d(smem + kOffQ + hd * kTileBytes, &tmQ, 0, yq, q_full);
                 tma_2d(smem + kOffQ + hd * kTileBytes + kSubBytes, &tmQ, 64, yq, q_full);
             }
-            // tiles are loaded in the order the MMA warp first touches them:
-            //   phase A: K_0 .. K_{n-1};   phase B: K_0, V_0, K_1, V_1, ...
-            int n_load = 0;
             bool ok = true;
-            auto load_tile = [&](const CUtensorMap *tm, int j) {
-                const int slot = n_load % kRing;
-                if (n_load >= kRing && !bar_wait(&r_empty[slot], ((n_load / kRing) - 1) & 1, p.status)) {
-                    ok = false;
-                    return;
-                }
+            auto load_tile = [&](const CUtensorMap *tm, int j, int slot, uint64_t *full) {
                 const int y = (int)(lane * p.Rpad) + j * kBN;
                 uint8_t *dst = smem + kOffRing + slot * kTileBytes;
-                bar_expect_tx(&r_full[slot], kTileBytes);
-                tma_2d(dst, tm, 0, y, &r_full[slot]);
-                tma_2d(dst + kSubBytes, tm, 64, y, &r_full[slot]);
-                ++n_load;
+                bar_expect_tx(full, kTileBytes);
+                tma_2d(dst, tm, 0, y, full);
+                tma_2d(dst + kSubBytes, tm, 64, y, full);
             };
-            for (int g = 0; ok && g < nTA && !(p.dbg & 128); ++g) load_tile(&tmK, g);
-            for (int jb = 0; ok && jb < nTB; ++jb) {
-                load_tile(&tmK, jb);
-                if (ok) load_tile(&tmV, jb);
+            // phase A: K_0 .. K_{n-1} through four slots
+            for (int g = 0; ok && g < nT; ++g) {
+                const int slot = g % kRingA;
+                if (g >= kRingA) ok = bar_wait(&ra_empty[slot], ((g / kRingA) - 1) & 1, p.status);
+                if (ok) load_tile(&tmK, g, slot, &ra_full[slot]);
+            }
+            // every phase A MMA has read its tile before phase B reuses the slots
+            if (ok) ok = bar_wait(a_done, 0, p.status);
+            // phase B: K_j into slot 0, V_j into slot 1
+            for (int n = 0; ok && n < 2 * nT; ++n) {
+                const int slot = n & 1, j = n >> 1;
+                if (j >= 1) ok = bar_wait(&rb_empty[slot], (j - 1) & 1, p.status);
+                if (ok) load_tile(slot ? &tmV : &tmK, j, slot, &rb_full[slot]);
             }
         }
     } else if (warp == 1) {
@@ -475,216 +484,201 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (lane_id == 0) {
             const uint32_t id_kk = idesc<T>(false, false);   // both operands K-major (Q K^T and K Q^T)
             const uint32_t id_pv = idesc<T>(true, true);     // out^T = V^T P^T: both operands MN-major
-            const uint32_t q_addr = s_u32(smem + kOffQ), p_addr = s_u32(smem + kOffP);
+            const uint32_t q_addr = s_u32(smem + kOffQ), p_addr = s_u32(smem + kOffP), r_addr = s_u32(smem + kOffRing);
             bool ok = bar_wait(q_full, 0, p.status) && bar_wait(qt_ready, 0, p.status);
             // low descriptor words of the fixed tiles and of the ring slots
             const uint32_t q_lo[2] = {desc_lo_k(q_addr), desc_lo_k(q_addr + kTileBytes)};
-            const uint32_t p_lo = desc_lo_mn(p_addr);
-            uint32_t ring_lo_k[kRing], ring_lo_mn[kRing];
+            const uint32_t p_lo[2] = {desc_lo_mn(p_addr), desc_lo_mn(p_addr + kTileBytes)};
+            uint32_t ra_lo[kRingA];
 #pragma unroll
-            for (int i = 0; i < kRing; ++i) {
-                const uint32_t a = s_u32(smem + kOffRing + i * kTileBytes);
-                ring_lo_k[i] = desc_lo_k(a);
-                ring_lo_mn[i] = desc_lo_mn(a);
+            for (int i = 0; i < kRingA; ++i) ra_lo[i] = desc_lo_k(r_addr + i * kTileBytes);
+            const uint32_t kb_lo = desc_lo_k(r_addr), vb_lo = desc_lo_mn(r_addr + kTileBytes);
+
+            // ---- phase A: S[hd] = Q[hd] K^T with Q read from tensor memory; u = g
+            for (int g = 0; ok && g < nT; ++g) {
+                const int slot = g % kRingA;
+                ok = bar_wait(&ra_full[slot], (g / kRingA) & 1, p.status);
+#pragma unroll
+                for (int hd = 0; hd < 2; ++hd) {
+                    if (ok && g >= 1) ok = bar_wait(&s_free[hd], (g - 1) & 1, p.status);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t k_lo = ra_lo[slot];
+#pragma unroll
+                    for (int ks = 0; ks < 8; ++ks) {
+                        const uint32_t off = (uint32_t)(((ks >> 2) * kSubBytes + (ks & 3) * 32) >> 4);
+                        tc_mma_ts(tm_s[hd], tm_q[hd] + ks * 8, desc_from(k_lo + off), id_kk, ks > 0 ? 1u : 0u);
+                    }
+                    if (hd == 1) tc_commit(&ra_empty[slot]);
+                    tc_commit(&s_full[hd]);
+                }
             }
-            auto ring_wait = [&](int load_idx) -> bool {
-                return bar_wait(&r_full[load_idx % kRing], (load_idx / kRing) & 1, p.status);
-            };
-            // u = running tile index over both phases: S[hd] completes once per u
-            auto do_qk = [&](int u, int load_idx, int hd, bool transposed, bool last_use) -> bool {
-                const int slot = load_idx % kRing;
-                if (hd == 0 && !(p.dbg & 128) && !ring_wait(load_idx)) return false;
-                if (u >= 1 && !(p.dbg & 64) && !bar_wait(&s_free[hd], (u - 1) & 1, p.status)) return false;
+            if (ok) tc_commit(a_done);
+
+            // ---- phase B: S^T[hd] = K Q[hd]^T, out^T[hd] += V^T P^T[hd]; S[hd] completes once per u = nT + jb
+            auto qk_b = [&](int jb, int hd) -> bool {
+                const int u = nT + jb;
+                if (hd == 0 && !bar_wait(&rb_full[0], jb & 1, p.status)) return false;
+                if (!bar_wait(&s_free[hd], (u - 1) & 1, p.status)) return false;
                 tc_fence_after();
-                const uint32_t k_lo = ring_lo_k[slot];
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {
                     const uint32_t off = (uint32_t)(((ks >> 2) * kSubBytes + (ks & 3) * 32) >> 4);
-                    // phase A: S = Q K^T with Q read from tensor memory; phase B: S^T = K Q^T
-                    if (transposed) tc_mma(tm_s[hd], desc_from(k_lo + off), desc_from(q_lo[hd] + off), id_kk, ks > 0 ? 1u : 0u);
-                    else tc_mma_ts(tm_s[hd], tm_q[hd] + ks * 8, desc_from(k_lo + off), id_kk, ks > 0 ? 1u : 0u);
+                    tc_mma(tm_s[hd], desc_from(kb_lo + off), desc_from(q_lo[hd] + off), id_kk, ks > 0 ? 1u : 0u);
                 }
-                if (last_use) tc_commit(&r_empty[slot]);
+                if (hd == 1) tc_commit(&rb_empty[0]);
                 tc_commit(&s_full[hd]);
                 return true;
             };
-            auto do_pv = [&](int jb, int hd) -> bool {
-                const int load_idx = nTA + 2 * jb + 1;
-                const int slot = load_idx % kRing;
-                if (!bar_wait(p_full, (2 * jb + hd) & 1, p.status)) return false;
-                if (hd == 0 && !ring_wait(load_idx)) return false;
+            auto pv_b = [&](int jb, int hd) -> bool {
+                if (!bar_wait(&p_full[hd], jb & 1, p.status)) return false;
+                if (hd == 0 && !bar_wait(&rb_full[1], jb & 1, p.status)) return false;
                 tc_fence_after();
-                const uint32_t v_lo = ring_lo_mn[slot];
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {
                     const uint32_t off = (uint32_t)((ks * 2048) >> 4);
                     // out^T += V^T (dims x keys) * P^T (keys x queries)
-                    tc_mma(tm_o[hd], desc_from(v_lo + off), desc_from(p_lo + off), id_pv, (jb > 0 || ks > 0) ? 1u : 0u);
+                    tc_mma(tm_o[hd], desc_from(vb_lo + off), desc_from(p_lo[hd] + off), id_pv, (jb > 0 || ks > 0) ? 1u : 0u);
                 }
-                if (hd == 1) tc_commit(&r_empty[slot]);
-                tc_commit(p_free);
+                if (hd == 1) tc_commit(&rb_empty[1]);
+                tc_commit(&p_free[hd]);
                 return true;
             };
-            // phase A: the two heads' MMAs are interleaved k-step by k-step, so that consecutive
-            // instructions accumulate into different tensor-memory tiles
-            for (int g = 0; ok && g < nTA; ++g) {
-                const int slot = g % kRing;
-                if (!(p.dbg & 128)) ok = ring_wait(g);
-                if (ok && g >= 1 && !(p.dbg & 64))
-                    ok = bar_wait(&s_free[0], (g - 1) & 1, p.status) && bar_wait(&s_free[1], (g - 1) & 1, p.status);
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t k_lo = ring_lo_k[slot];
-#pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {
-                    const uint32_t off = (uint32_t)(((ks >> 2) * kSubBytes + (ks & 3) * 32) >> 4);
-                    const uint64_t dk = desc_from(k_lo + off);
-                    tc_mma_ts(tm_s[0], tm_q[0] + ks * 8, dk, id_kk, ks > 0 ? 1u : 0u);
-                    tc_mma_ts(tm_s[1], tm_q[1] + ks * 8, dk, id_kk, ks > 0 ? 1u : 0u);
-                }
-                tc_commit(&r_empty[slot]);
-                tc_commit(&s_full[0]);
-                tc_commit(&s_full[1]);
-            }
-            if (ok && nTB > 0) {
-                ok = do_qk(nTA, nTA, 0, true, false);
-                if (ok) ok = do_qk(nTA, nTA, 1, true, true);
-            }
-            for (int jb = 0; ok && jb < nTB; ++jb) {
-                const bool more = jb + 1 < nTB;
-                ok = do_pv(jb, 0);
-                if (ok && more) ok = do_qk(nTA + jb + 1, nTA + 2 * (jb + 1), 0, true, false);
-                if (ok) ok = do_pv(jb, 1);
-                if (ok && more) ok = do_qk(nTA + jb + 1, nTA + 2 * (jb + 1), 1, true, true);
+            if (ok) ok = qk_b(0, 0);
+            if (ok) ok = qk_b(0, 1);
+            for (int jb = 0; ok && jb < nT; ++jb) {
+                const bool more = jb + 1 < nT;
+                ok = pv_b(jb, 0);
+                if (ok && more) ok = qk_b(jb + 1, 0);
+                if (ok) ok = pv_b(jb, 1);
+                if (ok && more) ok = qk_b(jb + 1, 1);
             }
             if (ok) tc_commit(o_full);
         }
     } else {
-        // ---------------------------------------------------------------- softmax warps (8)
-        // tensor-memory lane = 32*quarter + lane_id; the two warps of a quarter split the 128 columns
+        // ---------------------------------------------------------------- softmax warps (2 groups of 8)
+        // group = head of the pair; tensor-memory lane = 32*quarter + lane_id; the two warps of a quarter
+        // split the tile's 128 columns
+        const int grp = (warp - 2) >> 3;
+        const int half = ((warp - 2) >> 2) & 1;
         const int quarter = warp & 3;
-        const int half = (warp - 2) >> 2;
         const int row = 32 * quarter + lane_id;
         const uint32_t lane_base = (uint32_t)(32 * quarter) << 16;
+        const uint32_t tms = tm_s[grp] + lane_base + 64 * half;
+        const uint64_t l2e2 = pk2(kLog2e, kLog2e);
         bool ok = true;
 
-        // ---- Q tiles -> tensor memory (rows = lanes, the row's 64 words in order): half h copies head h
+        // ---- Q tile of this group's head -> tensor memory (rows = lanes, the row's 64 words in order)
         ok = bar_wait(q_full, 0, p.status);
         {
-            uint32_t qw[2][32];
-            const uint8_t *qsm = smem + kOffQ + half * kTileBytes;
+            uint32_t qw[32];
+            const uint8_t *qsm = smem + kOffQ + grp * kTileBytes + half * kSubBytes + row * 128;
 #pragma unroll
-            for (int c = 0; c < 16; ++c) {
-                const uint4 w4 = *reinterpret_cast<const uint4 *>(qsm + (c >> 3) * kSubBytes + row * 128 +
-                                                                  (((c & 7) ^ (row & 7)) << 4));
-                qw[c >> 3][4 * (c & 7)] = w4.x;
-                qw[c >> 3][4 * (c & 7) + 1] = w4.y;
-                qw[c >> 3][4 * (c & 7) + 2] = w4.z;
-                qw[c >> 3][4 * (c & 7) + 3] = w4.w;
+            for (int c = 0; c < 8; ++c) {
+                const uint4 w4 = *reinterpret_cast<const uint4 *>(qsm + ((c ^ (row & 7)) << 4));
+                qw[4 * c] = w4.x;
+                qw[4 * c + 1] = w4.y;
+                qw[4 * c + 2] = w4.z;
+                qw[4 * c + 3] = w4.w;
             }
-            tc_st32(tm_q[half] + lane_base, qw[0]);
-            tc_st32(tm_q[half] + lane_base + 32, qw[1]);
+            tc_st32(tm_q[grp] + lane_base + 32 * half, qw);
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             tc_fence_before();
             __syncwarp();
             if (lane_id == 0) bar_arrive(qt_ready);
         }
 
-        // ---- phase A: rows are queries; running max and sum of exp over the logits rounded to T
+        // ---- phase A: rows are queries; running max and sum of exp over the logits rounded to T,
+        //      renormalised per 32-column chunk
         {
             const int qg = qt * kBM + row;
             const bool row_ok = qg < p.K;
             const int row_limit = e.n_cached + (row_ok ? qg + 1 : 0);     // visible columns: [0, row_limit)
-            float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
-            for (int g = 0; g < nTA; ++g) {
+            float m_run = kMasked, l_run = 0.f;
+            for (int g = 0; g < nT; ++g) {
                 const bool full_tile = (g + 1) * kBN <= e.n_cached + qt * kBM + 1 && (qt + 1) * kBM <= p.K;
+                // after a failed (timed-out) wait the warp keeps walking the loops without waiting, so
+                // that the group barriers below are still reached by everyone
+                if (ok) ok = bar_wait(&s_full[grp], g & 1, p.status);
+                tc_fence_after();
+                uint32_t va[2][32];
+                tc_ld32(tms, va[0]);
+                tc_ld32(tms + 32, va[1]);
+                tc_ld_wait();
+                // the accumulator can be overwritten as soon as it is in registers
+                tc_fence_before();
+                __syncwarp();
+                if (lane_id == 0) bar_arrive(&s_free[grp]);
 #pragma unroll
-                for (int hd = 0; hd < 2; ++hd) {
-                    // after a failed (timed-out) wait the warp keeps walking the loops without waiting, so
-                    // that the block-wide barriers below are still reached by everyone
-                    if (ok) ok = bar_wait(&s_full[hd], g & 1, p.status);
-                    tc_fence_after();
-                    uint32_t va[2][32];
-                    if (!(p.dbg & 32)) {
-                    tc_ld32(tm_s[hd] + lane_base + 64 * half, va[0]);
-                    tc_ld32(tm_s[hd] + lane_base + 64 * half + 32, va[1]);
-                    tc_ld_wait();
-                    }
-                    // the accumulator can be overwritten as soon as it is in registers
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane_id == 0) bar_arrive(&s_free[hd]);
-                    if ((p.dbg & 4) || ((p.dbg & 256) && quarter == 1)) continue;
-                    // the statistics must be those of the logits ROUNDED to T: in a peaked row a single
-                    // logit carries the sum, and its rounding (up to 2^-9 of its value) moves every
-                    // probability of the row by far more than T's resolution
-                    uint64_t r2[2][16];
-                    float mx[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-                    for (int ch = 0; ch < 2; ++ch) {
+                for (int ch = 0; ch < 2; ++ch) {
+                    uint32_t (&v)[32] = va[ch];
+                    if (!full_tile) {
                         const int col0 = g * kBN + 64 * half + 32 * ch;
 #pragma unroll
-                        for (int c = 0; c < 32; c += 2) {
-                            uint64_t r = round2_to_t<T>(pk2(__uint_as_float(va[ch][c]), __uint_as_float(va[ch][c + 1])));
-                            float s0, s1;
-                            upk2(r, s0, s1);
-                            if (!full_tile) {
-                                if ((col0 + c) >= row_limit) s0 = -INFINITY;
-                                if ((col0 + c + 1) >= row_limit) s1 = -INFINITY;
-                                r = pk2(s0, s1);
-                            }
-                            r2[ch][c >> 1] = r;
-                            mx[(c >> 1) & 1] = max3(mx[(c >> 1) & 1], s0, s1);
-                        }
+                        for (int c = 0; c < 32; ++c)
+                            if (col0 + c >= row_limit) v[c] = __float_as_uint(kMasked);
                     }
-                    const float m_new = max3(mx[0], mx[1], m_run[hd]);
-                    if (m_new != -INFINITY) {
+                    // rounding is monotonic: the maximum of the rounded logits is the rounded maximum
+                    float mx0 = kMasked, mx1 = kMasked;
+#pragma unroll
+                    for (int c = 0; c < 32; c += 4) {
+                        mx0 = max3(mx0, __uint_as_float(v[c]), __uint_as_float(v[c + 1]));
+                        mx1 = max3(mx1, __uint_as_float(v[c + 2]), __uint_as_float(v[c + 3]));
+                    }
+                    const float mt = fmaxf(mx0, mx1);
+                    if (mt > kMaskedBelow) {
+                        float mr, unused;
+                        upk2(round2_to_t<T>(pk2(mt, mt)), mr, unused);
+                        // the statistics must be those of the logits ROUNDED to T: in a peaked row a single
+                        // logit carries the sum, and its rounding (up to 2^-9 of its value) moves every
+                        // probability of the row by far more than T's resolution
+                        const float m_new = fmaxf(m_run, mr);
                         const float mneg = -m_new * kLog2e;
-                        const uint64_t mneg2 = pk2(mneg, mneg), l2e2 = pk2(kLog2e, kLog2e);
+                        const uint64_t mneg2 = pk2(mneg, mneg);
                         uint64_t sum2[2] = {0ull, 0ull};
 #pragma unroll
-                        for (int ch = 0; ch < 2; ++ch)
-#pragma unroll
-                            for (int i = 0; i < 16; ++i) {
-                                float a0, a1;
-                                upk2(fma2(r2[ch][i], l2e2, mneg2), a0, a1);
-                                sum2[i & 1] = add2(sum2[i & 1], pk2(ex2f(a0), ex2f(a1)));
-                            }
+                        for (int i = 0; i < 16; ++i) {
+                            const uint64_t r = round2_to_t<T>(pk2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])));
+                            float a0, a1;
+                            upk2(fma2(r, l2e2, mneg2), a0, a1);
+                            sum2[i & 1] = add2(sum2[i & 1], pk2(ex2f(a0), ex2f(a1)));
+                        }
                         float t0, t1;
                         upk2(add2(sum2[0], sum2[1]), t0, t1);
-                        l_run[hd] = l_run[hd] * ex2f(fmaf(m_run[hd], kLog2e, mneg)) + (t0 + t1);
-                        m_run[hd] = m_new;
+                        // m_run == kMasked (nothing seen yet) gives ex2 of a huge negative number: 0
+                        l_run = l_run * ex2f(fmaf(m_run, kLog2e, mneg)) + (t0 + t1);
+                        m_run = m_new;
                     }
                 }
             }
             // combine the two column halves of each row; publish shift and EMA weight per query
-#pragma unroll
-            for (int hd = 0; hd < 2; ++hd) {
-                x_m[(half * 2 + hd) * 128 + row] = m_run[hd];
-                x_l[(half * 2 + hd) * 128 + row] = l_run[hd];
-            }
-            softmax_sync();
-            {
-                const int hd = half;   // the two halves each finish one head
-                const float m0 = x_m[hd * 128 + row], m1 = x_m[(2 + hd) * 128 + row];
+            x_m[(grp * 2 + half) * 128 + row] = m_run;
+            x_l[(grp * 2 + half) * 128 + row] = l_run;
+            group_sync(grp);
+            if (half == 0) {
+                const float m0 = x_m[(grp * 2) * 128 + row], m1 = x_m[(grp * 2 + 1) * 128 + row];
                 const float mm = fmaxf(m0, m1);
                 float cq = -INFINITY;
-                if (row_ok && mm != -INFINITY) {
-                    const float l = x_l[hd * 128 + row] * (m0 == -INFINITY ? 0.f : ex2f((m0 - mm) * kLog2e)) +
-                                    x_l[(2 + hd) * 128 + row] * (m1 == -INFINITY ? 0.f : ex2f((m1 - mm) * kLog2e));
+                if (row_ok && mm > kMaskedBelow) {
+                    const float l = x_l[(grp * 2) * 128 + row] * ex2f((m0 - mm) * kLog2e) +
+                                    x_l[(grp * 2 + 1) * 128 + row] * ex2f((m1 - mm) * kLog2e);
                     cq = -mm * kLog2e - __log2f(l);
                 }
-                c_q[hd * 128 + row] = cq;
-                if (hd == 0) w_q[row] = (kEma && row_ok) ? p.ema_w_cache[qg] : 0.f;
+                c_q[grp * 128 + row] = cq;
+            } else {
+                w_q[grp * 128 + row] = (kEma && row_ok) ? p.ema_w_cache[qg] : 0.f;
             }
-            softmax_sync();
+            group_sync(grp);
         }
 
         // ---- phase B: rows are keys (S^T); this thread owns key `key`, queries [64 half, 64 half + 64)
         const T *w_new = reinterpret_cast<const T *>(p.ema_w_new);
-        uint8_t *pt_row = smem + kOffP + half * kSubBytes + row * 128;
-        for (int jb = 0; jb < nTB; ++jb) {
-            const int u = nTA + jb;
+        uint8_t *pt_row = smem + kOffP + grp * kTileBytes + half * kSubBytes + row * 128;
+        const float *cq_h = c_q + grp * 128, *wq_h = w_q + grp * 128;
+        // EMA partial of (head, query tile, query half): summed over tiles and halves by prefill_scores_kernel
+        float *part = (kEma && head_ok[grp]) ? p.colpart + (((long long)bh[grp] * p.nQT + qt) * 2 + half) * p.Rpad : nullptr;
+        for (int jb = 0; jb < nT; ++jb) {
+            const int u = nT + jb;
             const int key = jb * kBN + row;                      // row of the compacted key matrix
             const bool key_ok = key < n_keys;
             const bool is_new = key >= e.n_cached;
@@ -694,134 +688,115 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             // every key of the tile is a cached one and every (key, query) pair is visible: the common
             // case, kept free of per-element control flow so that the exponentials overlap
             const bool fast_tile = full_tile && (jb + 1) * kBN <= e.n_cached;
-#pragma unroll
-            for (int hd = 0; hd < 2; ++hd) {
-                const int v_idx = 2 * jb + hd;                   // sequence number of this (tile, head)
-                const float *cq_h = c_q + hd * 128;
-                if (ok) ok = bar_wait(&s_full[hd], u & 1, p.status);
-                tc_fence_after();
-                float acc = 0.f;
-                uint32_t va[2][32];
-                tc_ld32(tm_s[hd] + lane_base + 64 * half, va[0]);
-                tc_ld32(tm_s[hd] + lane_base + 64 * half + 32, va[1]);
-                tc_ld_wait();
-                tc_fence_before();
-                __syncwarp();
-                if (lane_id == 0) bar_arrive(&s_free[hd]);
-                uint32_t pk[2][16];
-                if (p.dbg & 4) {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) pk[0][i] = pk[1][i] = va[0][i];
-                } else if (fast_tile) {
-                    uint64_t acc2[2] = {0ull, 0ull};
-                    const uint64_t l2e2 = pk2(kLog2e, kLog2e);
-#pragma unroll
-                    for (int ch = 0; ch < 2; ++ch) {
-                        uint32_t (&v)[32] = va[ch];
-                        const int qbase = 64 * half + 32 * ch;
-#pragma unroll
-                        for (int c4 = 0; c4 < 32; c4 += 4) {
-                            // per-query constants arrive as two packed pairs per 16-byte load
-                            const ulonglong2 cq = *reinterpret_cast<const ulonglong2 *>(cq_h + qbase + c4);
-                            const uint64_t sa = round2_to_t<T>(pk2(__uint_as_float(v[c4]), __uint_as_float(v[c4 + 1])));
-                            const uint64_t sb = round2_to_t<T>(pk2(__uint_as_float(v[c4 + 2]), __uint_as_float(v[c4 + 3])));
-                            float a0, a1, b0, b1;
-                            upk2(fma2(sa, l2e2, cq.x), a0, a1);
-                            upk2(fma2(sb, l2e2, cq.y), b0, b1);
-                            const uint64_t pa = round2_to_t<T>(pk2(ex2f(a0), ex2f(a1)));
-                            const uint64_t pb = round2_to_t<T>(pk2(ex2f(b0), ex2f(b1)));
-                            if (kEma) {
-                                const ulonglong2 wq = *reinterpret_cast<const ulonglong2 *>(w_q + qbase + c4);
-                                acc2[0] = fma2(pa, wq.x, acc2[0]);
-                                acc2[1] = fma2(pb, wq.y, acc2[1]);
-                            }
-                            float p0, p1, p2, p3;
-                            upk2(pa, p0, p1);
-                            upk2(pb, p2, p3);
-                            pk[ch][(c4 >> 1)] = P2<T>::pack_rounded(p0, p1);
-                            pk[ch][(c4 >> 1) + 1] = P2<T>::pack_rounded(p2, p3);
-                        }
-                    }
-                    float t0, t1;
-                    upk2(add2(acc2[0], acc2[1]), t0, t1);
-                    acc = t0 + t1;
-                } else {
-#pragma unroll
-                    for (int ch = 0; ch < 2; ++ch) {
-                        uint32_t (&v)[32] = va[ch];
-                        const int qbase = 64 * half + 32 * ch;
-#pragma unroll
-                        for (int c4 = 0; c4 < 32; c4 += 4) {
-                            const float4 cq4 = *reinterpret_cast<const float4 *>(cq_h + qbase + c4);
-                            const float4 wq4 = *reinterpret_cast<const float4 *>(w_q + qbase + c4);
-                            const float cqv[4] = {cq4.x, cq4.y, cq4.z, cq4.w};
-                            const float wqv[4] = {wq4.x, wq4.y, wq4.z, wq4.w};
-                            float pr[4];
-#pragma unroll
-                            for (int uu = 0; uu < 4; ++uu) {
-                                const float sv = round_to_t<T>(__uint_as_float(v[c4 + uu]));
-                                float pv = ex2f(fmaf(sv, kLog2e, cqv[uu]));
-                                if (!full_tile && (qbase + c4 + uu) < q_min) pv = 0.f;
-                                pr[uu] = round_to_t<T>(pv);
-                                if (kEma) {
-                                    if (!is_new) {
-                                        acc = fmaf(pr[uu], wqv[uu], acc);
-                                    } else if (pr[uu] != 0.f) {
-                                        const int d = qt * kBM + qbase + c4 + uu - (key - e.n_cached);
-                                        acc += round_to_t<T>(__fmul_rn(pr[uu], Elem<T>::to_f(w_new[d])));
-                                    }
-                                }
-                            }
-                            pk[ch][(c4 >> 1)] = P2<T>::pack_rounded(pr[0], pr[1]);
-                            pk[ch][(c4 >> 1) + 1] = P2<T>::pack_rounded(pr[2], pr[3]);
-                        }
-                    }
-                }
-                // P^T of the previous (tile, head) must have been consumed before this one overwrites it
-                if (ok && v_idx >= 1) ok = bar_wait(p_free, (v_idx - 1) & 1, p.status);
+            if (ok) ok = bar_wait(&s_full[grp], u & 1, p.status);
+            tc_fence_after();
+            float acc = 0.f;
+            uint32_t va[2][32];
+            tc_ld32(tms, va[0]);
+            tc_ld32(tms + 32, va[1]);
+            tc_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane_id == 0) bar_arrive(&s_free[grp]);
+            uint32_t pk[2][16];
+            if (fast_tile) {
+                uint64_t acc2[2] = {0ull, 0ull};
 #pragma unroll
                 for (int ch = 0; ch < 2; ++ch) {
+                    uint32_t (&v)[32] = va[ch];
+                    const int qbase = 64 * half + 32 * ch;
 #pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) {
-                        const int chunk = ch * 4 + q4;
-                        *reinterpret_cast<uint4 *>(pt_row + ((chunk ^ (row & 7)) << 4)) =
-                            make_uint4(pk[ch][4 * q4], pk[ch][4 * q4 + 1], pk[ch][4 * q4 + 2], pk[ch][4 * q4 + 3]);
+                    for (int c4 = 0; c4 < 32; c4 += 4) {
+                        // per-query constants arrive as two packed pairs per 16-byte load
+                        const ulonglong2 cq = *reinterpret_cast<const ulonglong2 *>(cq_h + qbase + c4);
+                        const uint64_t sa = round2_to_t<T>(pk2(__uint_as_float(v[c4]), __uint_as_float(v[c4 + 1])));
+                        const uint64_t sb = round2_to_t<T>(pk2(__uint_as_float(v[c4 + 2]), __uint_as_float(v[c4 + 3])));
+                        float a0, a1, b0, b1;
+                        upk2(fma2(sa, l2e2, cq.x), a0, a1);
+                        upk2(fma2(sb, l2e2, cq.y), b0, b1);
+                        const uint64_t pa = round2_to_t<T>(pk2(ex2f(a0), ex2f(a1)));
+                        const uint64_t pb = round2_to_t<T>(pk2(ex2f(b0), ex2f(b1)));
+                        if (kEma) {
+                            const ulonglong2 wq = *reinterpret_cast<const ulonglong2 *>(wq_h + qbase + c4);
+                            acc2[0] = fma2(pa, wq.x, acc2[0]);
+                            acc2[1] = fma2(pb, wq.y, acc2[1]);
+                        }
+                        float p0, p1, p2, p3;
+                        upk2(pa, p0, p1);
+                        upk2(pb, p2, p3);
+                        pk[ch][(c4 >> 1)] = P2<T>::pack_rounded(p0, p1);
+                        pk[ch][(c4 >> 1) + 1] = P2<T>::pack_rounded(p2, p3);
                     }
                 }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                __syncwarp();
-                if (lane_id == 0) bar_arrive(p_full);
-                if (kEma) {
-                    // column EMA partial of this query tile = row sum of P^T over both query halves;
-                    // double-buffered by sequence parity: the next barrier orders the reuse
-                    if (half == 1) colsum[(v_idx & 1) * 128 + row] = acc;
-                    softmax_sync();
-                    if (half == 0 && key_ok && key >= (int)e.sinks && head_ok[hd])
-                        p.colpart[((long long)bh[hd] * p.nQT + qt) * p.Rpad + key] = acc + colsum[(v_idx & 1) * 128 + row];
+                float t0, t1;
+                upk2(add2(acc2[0], acc2[1]), t0, t1);
+                acc = t0 + t1;
+            } else {
+#pragma unroll
+                for (int ch = 0; ch < 2; ++ch) {
+                    uint32_t (&v)[32] = va[ch];
+                    const int qbase = 64 * half + 32 * ch;
+#pragma unroll
+                    for (int c4 = 0; c4 < 32; c4 += 4) {
+                        const float4 cq4 = *reinterpret_cast<const float4 *>(cq_h + qbase + c4);
+                        const float4 wq4 = *reinterpret_cast<const float4 *>(wq_h + qbase + c4);
+                        const float cqv[4] = {cq4.x, cq4.y, cq4.z, cq4.w};
+                        const float wqv[4] = {wq4.x, wq4.y, wq4.z, wq4.w};
+                        float pr[4];
+#pragma unroll
+                        for (int uu = 0; uu < 4; ++uu) {
+                            const float sv = round_to_t<T>(__uint_as_float(v[c4 + uu]));
+                            float pv = ex2f(fmaf(sv, kLog2e, cqv[uu]));
+                            if (!full_tile && (qbase + c4 + uu) < q_min) pv = 0.f;
+                            pr[uu] = round_to_t<T>(pv);
+                            if (kEma) {
+                                if (!is_new) {
+                                    acc = fmaf(pr[uu], wqv[uu], acc);
+                                } else if (pr[uu] != 0.f) {
+                                    const int d = qt * kBM + qbase + c4 + uu - (key - e.n_cached);
+                                    acc += round_to_t<T>(__fmul_rn(pr[uu], Elem<T>::to_f(w_new[d])));
+                                }
+                            }
+                        }
+                        pk[ch][(c4 >> 1)] = P2<T>::pack_rounded(pr[0], pr[1]);
+                        pk[ch][(c4 >> 1) + 1] = P2<T>::pack_rounded(pr[2], pr[3]);
+                    }
                 }
             }
+            // P^T of the previous tile must have been consumed before this one overwrites it
+            if (ok && jb >= 1) ok = bar_wait(&p_free[grp], (jb - 1) & 1, p.status);
+#pragma unroll
+            for (int ch = 0; ch < 2; ++ch) {
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const int chunk = ch * 4 + q4;
+                    *reinterpret_cast<uint4 *>(pt_row + ((chunk ^ (row & 7)) << 4)) =
+                        make_uint4(pk[ch][4 * q4], pk[ch][4 * q4 + 1], pk[ch][4 * q4 + 2], pk[ch][4 * q4 + 3]);
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane_id == 0) bar_arrive(&p_full[grp]);
+            // column EMA partial of this query half = row sum of P^T over the thread's 64 queries
+            if (kEma && part && key_ok && key >= (int)e.sinks) part[key] = acc;
         }
 
         // ---- epilogue: out^T lives in tensor memory, lane = dim, column = query
-        if (ok && bar_wait(o_full, 0, p.status)) {
+        if (ok && bar_wait(o_full, 0, p.status) && head_ok[grp]) {
             tc_fence_after();
             const int d = row;
 #pragma unroll 1
-            for (int hd = 0; hd < 2; ++hd) {
-                if (!head_ok[hd]) continue;
-#pragma unroll 1
-                for (int ch = 0; ch < 2; ++ch) {
-                    uint32_t v[32];
-                    const int qbase = 64 * half + 32 * ch;
-                    tc_ld32(tm_o[hd] + lane_base + qbase, v);
-                    tc_ld_wait();
+            for (int ch = 0; ch < 2; ++ch) {
+                uint32_t v[32];
+                const int qbase = 64 * half + 32 * ch;
+                tc_ld32(tm_o[grp] + lane_base + qbase, v);
+                tc_ld_wait();
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) {
-                        const int qg = qt * kBM + qbase + c;
-                        if (qg < p.K) {
-                            T *orow = reinterpret_cast<T *>(p.out) + b * p.osb + head[hd] * p.osh + (long long)qg * p.ost;
-                            orow[d] = Elem<T>::from_f(__uint_as_float(v[c]));
-                        }
+                for (int c = 0; c < 32; ++c) {
+                    const int qg = qt * kBM + qbase + c;
+                    if (qg < p.K) {
+                        T *orow = reinterpret_cast<T *>(p.out) + b * p.osb + head[grp] * p.osh + (long long)qg * p.ost;
+                        orow[d] = Elem<T>::from_f(__uint_as_float(v[c]));
                     }
                 }
             }
@@ -878,9 +853,9 @@ __global__ void __launch_bounds__(256) prefill_scores_kernel(PrefillParams p) {
         const int r = is_new ? e.n_cached + (col - p.S) : (int)e.sinks + col;      // row of the compacted key matrix
         const int qt0 = is_new ? (col - p.S) / kBM : 0;                            // first query tile that sees it
         for (int gh = 0; gh < p.G; ++gh) {
-            const float *part = p.colpart + ((long long)(b * p.H + kvh * p.G + gh) * p.nQT) * p.Rpad + r;
+            const float *part = p.colpart + ((long long)(b * p.H + kvh * p.G + gh) * p.nQT) * 2 * p.Rpad + r;
             float s = 0.f;
-            for (int qt = qt0; qt < p.nQT; ++qt) s += part[(long long)qt * p.Rpad];
+            for (int i = 2 * qt0; i < 2 * p.nQT; ++i) s += part[(long long)i * p.Rpad];
             v[gh] = rnd<T>(s);
         }
         red = rnd<T>(reduce_heads_pf(v, p.G, p.head_reduction));
@@ -944,7 +919,7 @@ PrefillScratch prefill_scratch(const Dims &d, int K) {
     s.qs = off; off += a256((size_t)d.B * d.H * s.Kpad * 256);
     s.kcat = off; off += a256((size_t)d.B * d.KVH * s.Rpad * 256);
     s.vcat = off; off += a256((size_t)d.B * d.KVH * s.Rpad * 256);
-    s.colpart = off; off += a256((size_t)d.B * d.H * s.nQT * s.Rpad * 4);
+    s.colpart = off; off += a256((size_t)d.B * d.H * s.nQT * 2 * s.Rpad * 4);
     s.new_scores = off; off += a256((size_t)d.B * d.KVH * K * 2);
     s.upd_bytes = update_chunk_workspace_bytes(d, K);
     s.upd = off; off += s.upd_bytes;
@@ -1015,10 +990,6 @@ int launch_prefill_tuned(const Dims &d, const ckv_layer_state *st, const void *q
     p.ema = ema; p.head_reduction = d.head_reduction;
     p.rs = (float)sqrt(1.0 / sqrt((double)d.D));
     p.beta_pow = (float)pow(d.beta, (double)n_tokens);
-    {
-        const char *dbg = getenv("CKV_PREFILL_DEBUG");
-        p.dbg = dbg ? atoi(dbg) : 0;
-    }
 
     CUtensorMap tmQ, tmK, tmV;
     int rc;
