@@ -35,12 +35,13 @@ constexpr int kBM = 128, kBN = 128;
 constexpr int kSubBytes = 128 * 128;          // [128 rows x 64 elements] 16-bit, 128-byte swizzled
 constexpr int kTileBytes = 2 * kSubBytes;     // [128 x 128]
 constexpr int kOffQ = 0;                      // two Q tiles (the head pair)
-constexpr int kOffRing = 2 * kTileBytes;      // two K / V slots
-constexpr int kOffP = 4 * kTileBytes;         // two P^T tiles (one per head); contiguous with the ring
-constexpr int kRingA = 4;                     // phase A cycles K tiles through ring + P^T space
-constexpr int kOffBar = 6 * kTileBytes;
-constexpr int kOffW = kOffBar + 256;          // per-query constants and the statistics exchange
-constexpr int kAttnSmem = kOffW + 6144 + 1024; // + alignment slack
+constexpr int kRingB = 4;                     // phase B: K and V tiles share one ring, in the order they are consumed
+constexpr int kOffRing = 2 * kTileBytes;
+constexpr int kOffP = (2 + kRingB) * kTileBytes;   // the P^T tile, contiguous with the ring
+constexpr int kRingA = kRingB + 1;            // phase A cycles K tiles through ring + P^T space
+constexpr int kOffBar = (3 + kRingB) * kTileBytes;
+constexpr int kOffW = kOffBar + 256;          // per-query constants (also the statistics exchange)
+constexpr int kAttnSmem = kOffW + 2048;       // 231680 of the 232448 bytes a block may have
 constexpr int kAttnThreads = 576;             // TMA warp, MMA warp, 2 x 8 softmax warps
 constexpr unsigned kSpin = 1u << 22;
 constexpr int kTmemCols = 512;
@@ -191,15 +192,18 @@ __device__ __forceinline__ bool bar_try(uint64_t *bar, unsigned parity) {
         : "=r"(ok) : "r"(s_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
-__device__ __forceinline__ bool bar_wait(uint64_t *bar, unsigned parity, int *status) {
+// Bounded wait.  On a time-out the status word becomes 2 | (source line of the wait << 8) -- the first
+// wait to give up wins -- and every other wait of the grid returns false soon after.
+__device__ __forceinline__ bool bar_wait_at(uint64_t *bar, unsigned parity, int *status, int line) {
     for (unsigned n = 0; n < kSpin; ++n) {
         if (bar_try(bar, parity)) return true;
         if (n > 4096) __nanosleep(64);
         if ((n & 1023) == 1023 && *((volatile int *)status) != 0) return false;
     }
-    atomicExch(status, 2);
+    atomicCAS(status, 0, 2 | (line << 8));
     return false;
 }
+#define bar_wait(bar, parity, status) bar_wait_at(bar, parity, status, __LINE__)
 __device__ __forceinline__ void tma_2d(void *dst, const CUtensorMap *tm, int x, int y, uint64_t *bar) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -378,28 +382,33 @@ template <typename T> __device__ __forceinline__ uint32_t idesc(bool a_mn, bool 
 constexpr float kMasked = -1.0e30f, kMaskedBelow = -1.0e29f;
 
 // One CTA serves TWO query heads of the same KV head (a GQA pair) for one 128-query tile, so that
-// every K / V tile fetched from L2 feeds two heads.  Each head has its own group of 8 softmax warps,
-// its own logit accumulator and its own P^T buffer: the two groups never wait for each other, and
-// while one group's warps stall on a barrier the other group's keep the SM's pipes busy.
+// every K / V tile fetched from L2 feeds two heads.  Each head has its own group of 8 softmax warps and
+// its own logit accumulator; while one group's warps stall on a barrier the other group's keep the
+// SM's pipes busy.  The groups take turns on the single P^T buffer, which staggers them by the time
+// of one P V product.
 // Tensor memory (512 columns): S[0], S[1] at 0 / 128; out^T[0], out^T[1] at 256 / 384; during phase A the
 // out^T columns hold the two Q tiles as MMA A-operands instead.
-// Shared memory: Q[2] | ring[2] | P^T[2] (32 KB each).  Phase A streams K through ring AND P^T space
-// (4 slots); phase B keeps K in ring[0], V in ring[1].
+// Shared memory: Q[2] | ring[4] | P^T (32 KB each).  Phase A streams K through ring AND P^T space
+// (5 slots); phase B streams K_0 V_0 K_1 V_1 ... through the ring, each tile fetched about one tile
+// period ahead of its use (a tile takes 2000-3500 cycles to arrive from L2 under this load).
 template <typename T, bool kEma>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, PrefillParams p) {
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    // the tiles need 1024-byte alignment (128-byte swizzle atoms); there is no room for slack, so the
+    // window itself must be aligned -- it is when the kernel has no static shared memory
+    extern __shared__ __align__(1024) uint8_t smem[];
+    if ((s_u32(smem) & 1023u) != 0) {
+        if (threadIdx.x == 0) atomicExch(p.status, 3);
+        return;
+    }
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kOffBar);
-    uint64_t *q_full = bars + 0, *ra_full = bars + 1, *ra_empty = bars + 5, *rb_full = bars + 9, *rb_empty = bars + 11;
-    uint64_t *s_full = bars + 13, *s_free = bars + 15, *p_full = bars + 17, *p_free = bars + 19;
-    uint64_t *o_full = bars + 21, *qt_ready = bars + 22, *a_done = bars + 23;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 24);
+    uint64_t *q_full = bars + 0, *ra_full = bars + 1, *ra_empty = bars + 6, *rb_full = bars + 11, *rb_empty = bars + 15;
+    uint64_t *s_full = bars + 19, *s_free = bars + 21, *p_full = bars + 23, *p_free = bars + 25;
+    uint64_t *o_full = bars + 27, *qt_ready = bars + 28, *a_done = bars + 29;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 30);
     float *c_q = reinterpret_cast<float *>(smem + kOffW);       // [2 heads][128] softmax shift of each query
     float *w_q = c_q + 256;                                     // [2 heads][128] EMA weight of each query (one copy per group)
-    float *x_m = w_q + 256;                                     // [2 heads][2 halves][128] stats exchange
-    float *x_l = x_m + 512;
 
     const int warp = threadIdx.x >> 5, lane_id = threadIdx.x & 31;
     const int qt = blockIdx.x;
@@ -421,9 +430,11 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             bar_init(&ra_full[i], 1);
             bar_init(&ra_empty[i], 1);
         }
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < kRingB; ++i) {
             bar_init(&rb_full[i], 1);
             bar_init(&rb_empty[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
             bar_init(&s_full[i], 1);
             bar_init(&s_free[i], 8);
             bar_init(&p_full[i], 8);
@@ -472,11 +483,11 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             }
             // every phase A MMA has read its tile before phase B reuses the slots
             if (ok) ok = bar_wait(a_done, 0, p.status);
-            // phase B: K_j into slot 0, V_j into slot 1
+            // phase B: K_0, V_0, K_1, V_1, ... in the order the MMA warp first touches them
             for (int n = 0; ok && n < 2 * nT; ++n) {
-                const int slot = n & 1, j = n >> 1;
-                if (j >= 1) ok = bar_wait(&rb_empty[slot], (j - 1) & 1, p.status);
-                if (ok) load_tile(slot ? &tmV : &tmK, j, slot, &rb_full[slot]);
+                const int slot = n % kRingB;
+                if (n >= kRingB) ok = bar_wait(&rb_empty[slot], ((n / kRingB) - 1) & 1, p.status);
+                if (ok) load_tile((n & 1) ? &tmV : &tmK, n >> 1, slot, &rb_full[slot]);
             }
         }
     } else if (warp == 1) {
@@ -488,11 +499,10 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             bool ok = bar_wait(q_full, 0, p.status) && bar_wait(qt_ready, 0, p.status);
             // low descriptor words of the fixed tiles and of the ring slots
             const uint32_t q_lo[2] = {desc_lo_k(q_addr), desc_lo_k(q_addr + kTileBytes)};
-            const uint32_t p_lo[2] = {desc_lo_mn(p_addr), desc_lo_mn(p_addr + kTileBytes)};
-            uint32_t ra_lo[kRingA];
-#pragma unroll
-            for (int i = 0; i < kRingA; ++i) ra_lo[i] = desc_lo_k(r_addr + i * kTileBytes);
-            const uint32_t kb_lo = desc_lo_k(r_addr), vb_lo = desc_lo_mn(r_addr + kTileBytes);
+            const uint32_t p_lo = desc_lo_mn(p_addr);
+            // slot i of the ring: shared-memory addresses stay below 2^18, so the address field is linear in i
+            const uint32_t r_lo_k = desc_lo_k(r_addr), r_lo_mn = desc_lo_mn(r_addr);
+            constexpr uint32_t kSlotStep = (uint32_t)(kTileBytes >> 4);
 
             // ---- phase A: S[hd] = Q[hd] K^T with Q read from tensor memory; u = g
             for (int g = 0; ok && g < nT; ++g) {
@@ -503,7 +513,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     if (ok && g >= 1) ok = bar_wait(&s_free[hd], (g - 1) & 1, p.status);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t k_lo = ra_lo[slot];
+                    const uint32_t k_lo = r_lo_k + slot * kSlotStep;
 #pragma unroll
                     for (int ks = 0; ks < 8; ++ks) {
                         const uint32_t off = (uint32_t)(((ks >> 2) * kSubBytes + (ks & 3) * 32) >> 4);
@@ -517,30 +527,33 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
             // ---- phase B: S^T[hd] = K Q[hd]^T, out^T[hd] += V^T P^T[hd]; S[hd] completes once per u = nT + jb
             auto qk_b = [&](int jb, int hd) -> bool {
-                const int u = nT + jb;
-                if (hd == 0 && !bar_wait(&rb_full[0], jb & 1, p.status)) return false;
+                const int u = nT + jb, n = 2 * jb, slot = n % kRingB;
+                if (hd == 0 && !bar_wait(&rb_full[slot], (n / kRingB) & 1, p.status)) return false;
                 if (!bar_wait(&s_free[hd], (u - 1) & 1, p.status)) return false;
                 tc_fence_after();
+                const uint32_t kb_lo = r_lo_k + slot * kSlotStep;
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {
                     const uint32_t off = (uint32_t)(((ks >> 2) * kSubBytes + (ks & 3) * 32) >> 4);
                     tc_mma(tm_s[hd], desc_from(kb_lo + off), desc_from(q_lo[hd] + off), id_kk, ks > 0 ? 1u : 0u);
                 }
-                if (hd == 1) tc_commit(&rb_empty[0]);
+                if (hd == 1) tc_commit(&rb_empty[slot]);
                 tc_commit(&s_full[hd]);
                 return true;
             };
             auto pv_b = [&](int jb, int hd) -> bool {
+                const int n = 2 * jb + 1, slot = n % kRingB;
                 if (!bar_wait(&p_full[hd], jb & 1, p.status)) return false;
-                if (hd == 0 && !bar_wait(&rb_full[1], jb & 1, p.status)) return false;
+                if (hd == 0 && !bar_wait(&rb_full[slot], (n / kRingB) & 1, p.status)) return false;
                 tc_fence_after();
+                const uint32_t vb_lo = r_lo_mn + slot * kSlotStep;
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {
                     const uint32_t off = (uint32_t)((ks * 2048) >> 4);
                     // out^T += V^T (dims x keys) * P^T (keys x queries)
-                    tc_mma(tm_o[hd], desc_from(vb_lo + off), desc_from(p_lo[hd] + off), id_pv, (jb > 0 || ks > 0) ? 1u : 0u);
+                    tc_mma(tm_o[hd], desc_from(vb_lo + off), desc_from(p_lo + off), id_pv, (jb > 0 || ks > 0) ? 1u : 0u);
                 }
-                if (hd == 1) tc_commit(&rb_empty[1]);
+                if (hd == 1) tc_commit(&rb_empty[slot]);
                 tc_commit(&p_free[hd]);
                 return true;
             };
@@ -548,10 +561,12 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             if (ok) ok = qk_b(0, 1);
             for (int jb = 0; ok && jb < nT; ++jb) {
                 const bool more = jb + 1 < nT;
-                ok = pv_b(jb, 0);
-                if (ok && more) ok = qk_b(jb + 1, 0);
-                if (ok) ok = pv_b(jb, 1);
+                // the next tile's logits are started as soon as the group has read this tile's out of
+                // tensor memory, long before its P^T is ready
+                if (more) ok = qk_b(jb + 1, 0);
+                if (ok) ok = pv_b(jb, 0);
                 if (ok && more) ok = qk_b(jb + 1, 1);
+                if (ok) ok = pv_b(jb, 1);
             }
             if (ok) tc_commit(o_full);
         }
@@ -564,7 +579,11 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const int quarter = warp & 3;
         const int row = 32 * quarter + lane_id;
         const uint32_t lane_base = (uint32_t)(32 * quarter) << 16;
-        const uint32_t tms = tm_s[grp] + lane_base + 64 * half;
+        const uint32_t tms = tmem + 128u * grp + lane_base + 64 * half;
+        const uint32_t tmo = tmem + 256u + 128u * grp, tmq = tmem + 256u + 64u * grp;
+        const int head_g = kvh * p.G + 2 * pair + grp;
+        const bool head_ok_g = grp == 0 || 2 * pair + 1 < p.G;
+        const int bh_g = b * p.H + (head_ok_g ? head_g : head_g - 1);
         const uint64_t l2e2 = pk2(kLog2e, kLog2e);
         bool ok = true;
 
@@ -581,7 +600,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 qw[4 * c + 2] = w4.z;
                 qw[4 * c + 3] = w4.w;
             }
-            tc_st32(tm_q[grp] + lane_base + 32 * half, qw);
+            tc_st32(tmq + lane_base + 32 * half, qw);
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             tc_fence_before();
             __syncwarp();
@@ -651,32 +670,34 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     }
                 }
             }
-            // combine the two column halves of each row; publish shift and EMA weight per query
-            x_m[(grp * 2 + half) * 128 + row] = m_run;
-            x_l[(grp * 2 + half) * 128 + row] = l_run;
+            // combine the two column halves of each row; publish shift and EMA weight per query.  The
+            // second half hands its statistics over through the arrays that then receive the results.
+            if (half == 1) {
+                c_q[grp * 128 + row] = m_run;
+                w_q[grp * 128 + row] = l_run;
+            }
             group_sync(grp);
+            float cq = -INFINITY;
             if (half == 0) {
-                const float m0 = x_m[(grp * 2) * 128 + row], m1 = x_m[(grp * 2 + 1) * 128 + row];
-                const float mm = fmaxf(m0, m1);
-                float cq = -INFINITY;
+                const float m1 = c_q[grp * 128 + row], l1 = w_q[grp * 128 + row];
+                const float mm = fmaxf(m_run, m1);
                 if (row_ok && mm > kMaskedBelow) {
-                    const float l = x_l[(grp * 2) * 128 + row] * ex2f((m0 - mm) * kLog2e) +
-                                    x_l[(grp * 2 + 1) * 128 + row] * ex2f((m1 - mm) * kLog2e);
+                    const float l = l_run * ex2f((m_run - mm) * kLog2e) + l1 * ex2f((m1 - mm) * kLog2e);
                     cq = -mm * kLog2e - __log2f(l);
                 }
-                c_q[grp * 128 + row] = cq;
-            } else {
-                w_q[grp * 128 + row] = (kEma && row_ok) ? p.ema_w_cache[qg] : 0.f;
             }
+            group_sync(grp);
+            if (half == 0) c_q[grp * 128 + row] = cq;
+            else w_q[grp * 128 + row] = (kEma && row_ok) ? p.ema_w_cache[qg] : 0.f;
             group_sync(grp);
         }
 
         // ---- phase B: rows are keys (S^T); this thread owns key `key`, queries [64 half, 64 half + 64)
         const T *w_new = reinterpret_cast<const T *>(p.ema_w_new);
-        uint8_t *pt_row = smem + kOffP + grp * kTileBytes + half * kSubBytes + row * 128;
+        uint8_t *pt_row = smem + kOffP + half * kSubBytes + row * 128;
         const float *cq_h = c_q + grp * 128, *wq_h = w_q + grp * 128;
         // EMA partial of (head, query tile, query half): summed over tiles and halves by prefill_scores_kernel
-        float *part = (kEma && head_ok[grp]) ? p.colpart + (((long long)bh[grp] * p.nQT + qt) * 2 + half) * p.Rpad : nullptr;
+        float *part = (kEma && head_ok_g) ? p.colpart + (((long long)bh_g * p.nQT + qt) * 2 + half) * p.Rpad : nullptr;
         for (int jb = 0; jb < nT; ++jb) {
             const int u = nT + jb;
             const int key = jb * kBN + row;                      // row of the compacted key matrix
@@ -763,8 +784,10 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     }
                 }
             }
-            // P^T of the previous tile must have been consumed before this one overwrites it
-            if (ok && jb >= 1) ok = bar_wait(&p_free[grp], (jb - 1) & 1, p.status);
+            // the groups alternate on the P^T buffer: head 0 writes tile jb once the other head's P V
+            // product of tile jb - 1 has read it, head 1 once head 0's of tile jb has.  Each head has its
+            // own barrier pair: on a shared one a group could be two phases ahead of the parity it tests.
+            if (ok && (grp == 1 || jb >= 1)) ok = bar_wait(&p_free[grp ^ 1], (grp ? jb : jb - 1) & 1, p.status);
 #pragma unroll
             for (int ch = 0; ch < 2; ++ch) {
 #pragma unroll
@@ -782,20 +805,20 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
 
         // ---- epilogue: out^T lives in tensor memory, lane = dim, column = query
-        if (ok && bar_wait(o_full, 0, p.status) && head_ok[grp]) {
+        if (ok && bar_wait(o_full, 0, p.status) && head_ok_g) {
             tc_fence_after();
             const int d = row;
 #pragma unroll 1
             for (int ch = 0; ch < 2; ++ch) {
                 uint32_t v[32];
                 const int qbase = 64 * half + 32 * ch;
-                tc_ld32(tm_o[grp] + lane_base + qbase, v);
+                tc_ld32(tmo + lane_base + qbase, v);
                 tc_ld_wait();
 #pragma unroll
                 for (int c = 0; c < 32; ++c) {
                     const int qg = qt * kBM + qbase + c;
                     if (qg < p.K) {
-                        T *orow = reinterpret_cast<T *>(p.out) + b * p.osb + head[grp] * p.osh + (long long)qg * p.ost;
+                        T *orow = reinterpret_cast<T *>(p.out) + b * p.osb + head_g * p.osh + (long long)qg * p.ost;
                         orow[d] = Elem<T>::from_f(__uint_as_float(v[c]));
                     }
                 }
