@@ -5,7 +5,8 @@
 //                            slots, the chunk itself) at its cache position into scratch, compacted
 //                            so that key row r of a lane is [sinks | cached | new][r]; copy the
 //                            values alongside.  (reference: cascade_attention.py:141-166, :284-291)
-//   2. prefill_attn_kernel   one CTA per (batch, head, 128-query tile), two phases over the key tiles:
+//   2. prefill_attn_kernel   one CTA per (batch, KV head, pair of query heads, 128-query tile), two
+//                            phases over the key tiles:
 //                            A: S = Q K^T (tcgen05), running row max / sum;
 //                            B: S^T = K Q^T, P^T = T(exp(S^T - max) / sum) exactly normalised,
 //                               out^T += V^T P^T (tcgen05, out^T in tensor memory), and the EMA
@@ -15,12 +16,14 @@
 //                            GQA group, applies score = T(T(beta^K score) + ema) (:231-248, :329-330).
 //   4. the cache update of the chunk (ckv_update.cu).
 //
-// Warp roles in prefill_attn_kernel (320 threads): warp 0 TMA producer, warp 1 MMA issuer and
-// tensor-memory owner, warps 2-9 softmax (two warps per 32-lane quarter of tensor memory, each taking
-// 64 of a tile's 128 columns).  Phase B runs TRANSPOSED (S^T = K Q^T, out^T = V^T P^T): a thread
-// then owns one key row, so the EMA score of that key is simply its row sum of P^T -- no
-// cross-thread column reduction and no extra warps.
+// Warp roles in prefill_attn_kernel (608 threads): warp 0 TMA producer, warp 1 Q K^T issuer and
+// tensor-memory owner, warps 2-9 softmax of the pair's first head, warps 10-17 of its second head (two
+// warps per 32-lane quarter of tensor memory, each taking 64 of a tile's 128 columns), warp 18 P V
+// issuer.  Phase B runs TRANSPOSED (S^T = K Q^T, out^T = V^T P^T): a thread then owns one key row,
+// so the EMA score of that key is simply its row sum of P^T -- no cross-thread column reduction.
 // Every mbarrier wait is bounded; on a time-out the status word is raised and all roles leave.
+// A waiter tests one parity bit, so no barrier here is ever waited on by a role that could be two
+// completions behind it.
 #include <cuda.h>
 
 #include <type_traits>
@@ -35,14 +38,15 @@ constexpr int kBM = 128, kBN = 128;
 constexpr int kSubBytes = 128 * 128;          // [128 rows x 64 elements] 16-bit, 128-byte swizzled
 constexpr int kTileBytes = 2 * kSubBytes;     // [128 x 128]
 constexpr int kOffQ = 0;                      // two Q tiles (the head pair)
-constexpr int kRingB = 4;                     // phase B: K and V tiles share one ring, in the order they are consumed
+constexpr int kRingB = 3;                     // phase B: K and V tiles share one ring, in the order they are consumed
 constexpr int kOffRing = 2 * kTileBytes;
-constexpr int kOffP = (2 + kRingB) * kTileBytes;   // the P^T tile, contiguous with the ring
-constexpr int kRingA = kRingB + 1;            // phase A cycles K tiles through ring + P^T space
-constexpr int kOffBar = (3 + kRingB) * kTileBytes;
+constexpr int kOffP = (2 + kRingB) * kTileBytes;   // two P^T tiles (one per head), contiguous with the ring
+constexpr int kRingA = kRingB + 2;            // phase A cycles K tiles through ring + P^T space
+constexpr int kOffBar = (4 + kRingB) * kTileBytes;
 constexpr int kOffW = kOffBar + 256;          // per-query constants (also the statistics exchange)
 constexpr int kAttnSmem = kOffW + 2048;       // 231680 of the 232448 bytes a block may have
-constexpr int kAttnThreads = 576;             // TMA warp, MMA warp, 2 x 8 softmax warps
+constexpr int kAttnThreads = 608;             // TMA warp, Q K^T warp, 2 x 8 softmax warps, P V warp
+constexpr int kPvWarp = 18;
 constexpr unsigned kSpin = 1u << 22;
 constexpr int kTmemCols = 512;
 constexpr float kLog2e = 1.4426950408889634f;
@@ -382,15 +386,14 @@ template <typename T> __device__ __forceinline__ uint32_t idesc(bool a_mn, bool 
 constexpr float kMasked = -1.0e30f, kMaskedBelow = -1.0e29f;
 
 // One CTA serves TWO query heads of the same KV head (a GQA pair) for one 128-query tile, so that
-// every K / V tile fetched from L2 feeds two heads.  Each head has its own group of 8 softmax warps and
-// its own logit accumulator; while one group's warps stall on a barrier the other group's keep the
-// SM's pipes busy.  The groups take turns on the single P^T buffer, which staggers them by the time
-// of one P V product.
+// every K / V tile fetched from L2 feeds two heads.  Each head has its own group of 8 softmax warps,
+// its own logit accumulator and its own P^T buffer: the groups meet only in the K / V ring, and while
+// one group's warps stall on a barrier the other group's keep the SM's pipes busy.
 // Tensor memory (512 columns): S[0], S[1] at 0 / 128; out^T[0], out^T[1] at 256 / 384; during phase A the
 // out^T columns hold the two Q tiles as MMA A-operands instead.
-// Shared memory: Q[2] | ring[4] | P^T (32 KB each).  Phase A streams K through ring AND P^T space
-// (5 slots); phase B streams K_0 V_0 K_1 V_1 ... through the ring, each tile fetched about one tile
-// period ahead of its use (a tile takes 2000-3500 cycles to arrive from L2 under this load).
+// Shared memory: Q[2] | ring[3] | P^T[2] (32 KB each).  Phase A streams K through ring AND P^T space
+// (5 slots); phase B streams K_0 V_0 K_1 V_1 ... through the ring: while K_j and V_j are in use the
+// third slot receives the next tile (a tile arrives 500-800 cycles after it is requested).
 template <typename T, bool kEma>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -404,6 +407,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kOffBar);
     uint64_t *q_full = bars + 0, *ra_full = bars + 1, *ra_empty = bars + 6, *rb_full = bars + 11, *rb_empty = bars + 15;
+    static_assert(kRingA <= 5 && kRingB <= 4, "barrier table layout");
     uint64_t *s_full = bars + 19, *s_free = bars + 21, *p_full = bars + 23, *p_free = bars + 25;
     uint64_t *o_full = bars + 27, *qt_ready = bars + 28, *a_done = bars + 29;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 30);
@@ -491,17 +495,15 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             }
         }
     } else if (warp == 1) {
-        // ---------------------------------------------------------------- MMA issuer
+        // ---------------------------------------------------------------- Q K^T issuer (owns tensor memory)
         if (lane_id == 0) {
             const uint32_t id_kk = idesc<T>(false, false);   // both operands K-major (Q K^T and K Q^T)
-            const uint32_t id_pv = idesc<T>(true, true);     // out^T = V^T P^T: both operands MN-major
-            const uint32_t q_addr = s_u32(smem + kOffQ), p_addr = s_u32(smem + kOffP), r_addr = s_u32(smem + kOffRing);
+            const uint32_t q_addr = s_u32(smem + kOffQ), r_addr = s_u32(smem + kOffRing);
             bool ok = bar_wait(q_full, 0, p.status) && bar_wait(qt_ready, 0, p.status);
             // low descriptor words of the fixed tiles and of the ring slots
             const uint32_t q_lo[2] = {desc_lo_k(q_addr), desc_lo_k(q_addr + kTileBytes)};
-            const uint32_t p_lo = desc_lo_mn(p_addr);
             // slot i of the ring: shared-memory addresses stay below 2^18, so the address field is linear in i
-            const uint32_t r_lo_k = desc_lo_k(r_addr), r_lo_mn = desc_lo_mn(r_addr);
+            const uint32_t r_lo_k = desc_lo_k(r_addr);
             constexpr uint32_t kSlotStep = (uint32_t)(kTileBytes >> 4);
 
             // ---- phase A: S[hd] = Q[hd] K^T with Q read from tensor memory; u = g
@@ -525,48 +527,56 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             }
             if (ok) tc_commit(a_done);
 
-            // ---- phase B: S^T[hd] = K Q[hd]^T, out^T[hd] += V^T P^T[hd]; S[hd] completes once per u = nT + jb
-            auto qk_b = [&](int jb, int hd) -> bool {
+            // ---- phase B: S^T[hd] = K Q[hd]^T; S[hd] completes once per u = nT + jb.  A tile's logits are
+            //      started as soon as the group has read the previous tile's out of tensor memory.
+            for (int jb = 0; ok && jb < nT; ++jb) {
                 const int u = nT + jb, n = 2 * jb, slot = n % kRingB;
-                if (hd == 0 && !bar_wait(&rb_full[slot], (n / kRingB) & 1, p.status)) return false;
-                if (!bar_wait(&s_free[hd], (u - 1) & 1, p.status)) return false;
-                tc_fence_after();
+                ok = bar_wait(&rb_full[slot], (n / kRingB) & 1, p.status);
                 const uint32_t kb_lo = r_lo_k + slot * kSlotStep;
 #pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {
-                    const uint32_t off = (uint32_t)(((ks >> 2) * kSubBytes + (ks & 3) * 32) >> 4);
-                    tc_mma(tm_s[hd], desc_from(kb_lo + off), desc_from(q_lo[hd] + off), id_kk, ks > 0 ? 1u : 0u);
+                for (int hd = 0; hd < 2; ++hd) {
+                    if (ok) ok = bar_wait(&s_free[hd], (u - 1) & 1, p.status);
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int ks = 0; ks < 8; ++ks) {
+                        const uint32_t off = (uint32_t)(((ks >> 2) * kSubBytes + (ks & 3) * 32) >> 4);
+                        tc_mma(tm_s[hd], desc_from(kb_lo + off), desc_from(q_lo[hd] + off), id_kk, ks > 0 ? 1u : 0u);
+                    }
+                    if (hd == 1) tc_commit(&rb_empty[slot]);
+                    tc_commit(&s_full[hd]);
                 }
-                if (hd == 1) tc_commit(&rb_empty[slot]);
-                tc_commit(&s_full[hd]);
-                return true;
-            };
-            auto pv_b = [&](int jb, int hd) -> bool {
+            }
+        }
+    } else if (warp == kPvWarp) {
+        // ---------------------------------------------------------------- P V issuer
+        // A thread of its own: an issuing thread is held while the tensor pipe's queue is full, and
+        // one thread issuing both products would react late to whichever operand arrives meanwhile.
+        if (lane_id == 0) {
+            const uint32_t id_pv = idesc<T>(true, true);     // out^T = V^T P^T: both operands MN-major
+            const uint32_t p_lo[2] = {desc_lo_mn(s_u32(smem + kOffP)), desc_lo_mn(s_u32(smem + kOffP + kTileBytes))};
+            const uint32_t r_lo_mn = desc_lo_mn(s_u32(smem + kOffRing));
+            constexpr uint32_t kSlotStep = (uint32_t)(kTileBytes >> 4);
+            // out^T overlays the Q tiles that phase A reads from tensor memory
+            bool ok = bar_wait(a_done, 0, p.status);
+            for (int jb = 0; ok && jb < nT; ++jb) {
                 const int n = 2 * jb + 1, slot = n % kRingB;
-                if (!bar_wait(&p_full[hd], jb & 1, p.status)) return false;
-                if (hd == 0 && !bar_wait(&rb_full[slot], (n / kRingB) & 1, p.status)) return false;
-                tc_fence_after();
                 const uint32_t vb_lo = r_lo_mn + slot * kSlotStep;
 #pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {
-                    const uint32_t off = (uint32_t)((ks * 2048) >> 4);
-                    // out^T += V^T (dims x keys) * P^T (keys x queries)
-                    tc_mma(tm_o[hd], desc_from(vb_lo + off), desc_from(p_lo + off), id_pv, (jb > 0 || ks > 0) ? 1u : 0u);
+                for (int hd = 0; hd < 2; ++hd) {
+                    if (ok) ok = bar_wait(&p_full[hd], jb & 1, p.status);
+                    if (ok && hd == 0) ok = bar_wait(&rb_full[slot], (n / kRingB) & 1, p.status);
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int ks = 0; ks < 8; ++ks) {
+                        const uint32_t off = (uint32_t)((ks * 2048) >> 4);
+                        // out^T += V^T (dims x keys) * P^T (keys x queries)
+                        tc_mma(tm_o[hd], desc_from(vb_lo + off), desc_from(p_lo[hd] + off), id_pv, (jb > 0 || ks > 0) ? 1u : 0u);
+                    }
+                    if (hd == 1) tc_commit(&rb_empty[slot]);
+                    tc_commit(&p_free[hd]);
                 }
-                if (hd == 1) tc_commit(&rb_empty[slot]);
-                tc_commit(&p_free[hd]);
-                return true;
-            };
-            if (ok) ok = qk_b(0, 0);
-            if (ok) ok = qk_b(0, 1);
-            for (int jb = 0; ok && jb < nT; ++jb) {
-                const bool more = jb + 1 < nT;
-                // the next tile's logits are started as soon as the group has read this tile's out of
-                // tensor memory, long before its P^T is ready
-                if (more) ok = qk_b(jb + 1, 0);
-                if (ok) ok = pv_b(jb, 0);
-                if (ok && more) ok = qk_b(jb + 1, 1);
-                if (ok) ok = pv_b(jb, 1);
             }
             if (ok) tc_commit(o_full);
         }
@@ -694,7 +704,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
         // ---- phase B: rows are keys (S^T); this thread owns key `key`, queries [64 half, 64 half + 64)
         const T *w_new = reinterpret_cast<const T *>(p.ema_w_new);
-        uint8_t *pt_row = smem + kOffP + half * kSubBytes + row * 128;
+        uint8_t *pt_row = smem + kOffP + grp * kTileBytes + half * kSubBytes + row * 128;
         const float *cq_h = c_q + grp * 128, *wq_h = w_q + grp * 128;
         // EMA partial of (head, query tile, query half): summed over tiles and halves by prefill_scores_kernel
         float *part = (kEma && head_ok_g) ? p.colpart + (((long long)bh_g * p.nQT + qt) * 2 + half) * p.Rpad : nullptr;
@@ -784,10 +794,8 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     }
                 }
             }
-            // the groups alternate on the P^T buffer: head 0 writes tile jb once the other head's P V
-            // product of tile jb - 1 has read it, head 1 once head 0's of tile jb has.  Each head has its
-            // own barrier pair: on a shared one a group could be two phases ahead of the parity it tests.
-            if (ok && (grp == 1 || jb >= 1)) ok = bar_wait(&p_free[grp ^ 1], (grp ? jb : jb - 1) & 1, p.status);
+            // the head's P^T buffer may be rewritten once the P V product of its previous tile has read it
+            if (ok && jb >= 1) ok = bar_wait(&p_free[grp], (jb - 1) & 1, p.status);
 #pragma unroll
             for (int ch = 0; ch < 2; ++ch) {
 #pragma unroll
