@@ -38,7 +38,7 @@ constexpr int kBM = 128, kBN = 128;
 constexpr int kSubBytes = 128 * 128;          // [128 rows x 64 elements] 16-bit, 128-byte swizzled
 constexpr int kTileBytes = 2 * kSubBytes;     // [128 x 128]
 constexpr int kOffQ = 0;                      // two Q tiles (the head pair)
-constexpr int kRingB = 3;                     // phase B: K and V tiles share one ring, in the order they are consumed
+constexpr int kRingB = 3;                     // phase B: slot 0 holds the K tile, slots 1 and 2 alternate for V
 constexpr int kOffRing = 2 * kTileBytes;
 constexpr int kOffP = (2 + kRingB) * kTileBytes;   // two P^T tiles (one per head), contiguous with the ring
 constexpr int kRingA = kRingB + 2;            // phase A cycles K tiles through ring + P^T space
@@ -208,6 +208,19 @@ __device__ __forceinline__ bool bar_wait_at(uint64_t *bar, unsigned parity, int 
     return false;
 }
 #define bar_wait(bar, parity, status) bar_wait_at(bar, parity, status, __LINE__)
+// Non-blocking test of a phase.  Barrier operations share the SM's memory-I/O queue with the special
+// function unit, so while the softmax warps keep that unit saturated a test takes hundreds of cycles
+// to answer: the softmax warps therefore ask early, compute meanwhile, and fall back to the bounded
+// wait only on "not yet".
+__device__ __forceinline__ bool bar_probe(uint64_t *bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(s_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ void tma_2d(void *dst, const CUtensorMap *tm, int x, int y, uint64_t *bar) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -392,8 +405,10 @@ constexpr float kMasked = -1.0e30f, kMaskedBelow = -1.0e29f;
 // Tensor memory (512 columns): S[0], S[1] at 0 / 128; out^T[0], out^T[1] at 256 / 384; during phase A the
 // out^T columns hold the two Q tiles as MMA A-operands instead.
 // Shared memory: Q[2] | ring[3] | P^T[2] (32 KB each).  Phase A streams K through ring AND P^T space
-// (5 slots); phase B streams K_0 V_0 K_1 V_1 ... through the ring: while K_j and V_j are in use the
-// third slot receives the next tile (a tile arrives 500-800 cycles after it is requested).
+// (5 slots).  In phase B a K tile is consumed at the START of a tile period (the next tile's logits
+// are issued as soon as the softmax warps have read the current ones) and its slot refilled at once,
+// so one K slot suffices; a V tile is consumed at the END of its period, so V is double-buffered.
+// A tile arrives 500-800 cycles after it is requested.
 template <typename T, bool kEma>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -487,11 +502,13 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             }
             // every phase A MMA has read its tile before phase B reuses the slots
             if (ok) ok = bar_wait(a_done, 0, p.status);
-            // phase B: K_0, V_0, K_1, V_1, ... in the order the MMA warp first touches them
-            for (int n = 0; ok && n < 2 * nT; ++n) {
-                const int slot = n % kRingB;
-                if (n >= kRingB) ok = bar_wait(&rb_empty[slot], ((n / kRingB) - 1) & 1, p.status);
-                if (ok) load_tile((n & 1) ? &tmV : &tmK, n >> 1, slot, &rb_full[slot]);
+            // phase B: K_j into slot 0, V_j into slot 1 + (j & 1)
+            for (int j = 0; ok && j < nT; ++j) {
+                const int vs = 1 + (j & 1);
+                if (j >= 1) ok = bar_wait(&rb_empty[0], (j - 1) & 1, p.status);
+                if (ok) load_tile(&tmK, j, 0, &rb_full[0]);
+                if (ok && j >= 2) ok = bar_wait(&rb_empty[vs], ((j >> 1) - 1) & 1, p.status);
+                if (ok) load_tile(&tmV, j, vs, &rb_full[vs]);
             }
         }
     } else if (warp == 1) {
@@ -530,9 +547,9 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             // ---- phase B: S^T[hd] = K Q[hd]^T; S[hd] completes once per u = nT + jb.  A tile's logits are
             //      started as soon as the group has read the previous tile's out of tensor memory.
             for (int jb = 0; ok && jb < nT; ++jb) {
-                const int u = nT + jb, n = 2 * jb, slot = n % kRingB;
-                ok = bar_wait(&rb_full[slot], (n / kRingB) & 1, p.status);
-                const uint32_t kb_lo = r_lo_k + slot * kSlotStep;
+                const int u = nT + jb;
+                ok = bar_wait(&rb_full[0], jb & 1, p.status);
+                const uint32_t kb_lo = r_lo_k;
 #pragma unroll
                 for (int hd = 0; hd < 2; ++hd) {
                     if (ok) ok = bar_wait(&s_free[hd], (u - 1) & 1, p.status);
@@ -543,7 +560,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                         const uint32_t off = (uint32_t)(((ks >> 2) * kSubBytes + (ks & 3) * 32) >> 4);
                         tc_mma(tm_s[hd], desc_from(kb_lo + off), desc_from(q_lo[hd] + off), id_kk, ks > 0 ? 1u : 0u);
                     }
-                    if (hd == 1) tc_commit(&rb_empty[slot]);
+                    if (hd == 1) tc_commit(&rb_empty[0]);
                     tc_commit(&s_full[hd]);
                 }
             }
@@ -560,12 +577,12 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             // out^T overlays the Q tiles that phase A reads from tensor memory
             bool ok = bar_wait(a_done, 0, p.status);
             for (int jb = 0; ok && jb < nT; ++jb) {
-                const int n = 2 * jb + 1, slot = n % kRingB;
+                const int slot = 1 + (jb & 1);
                 const uint32_t vb_lo = r_lo_mn + slot * kSlotStep;
 #pragma unroll
                 for (int hd = 0; hd < 2; ++hd) {
                     if (ok) ok = bar_wait(&p_full[hd], jb & 1, p.status);
-                    if (ok && hd == 0) ok = bar_wait(&rb_full[slot], (n / kRingB) & 1, p.status);
+                    if (ok && hd == 0) ok = bar_wait(&rb_full[slot], (jb >> 1) & 1, p.status);
                     if (!ok) break;
                     tc_fence_after();
 #pragma unroll
@@ -624,11 +641,12 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             const bool row_ok = qg < p.K;
             const int row_limit = e.n_cached + (row_ok ? qg + 1 : 0);     // visible columns: [0, row_limit)
             float m_run = kMasked, l_run = 0.f;
+            bool s_rdy = false;                                           // the tile's logits are known to be complete
             for (int g = 0; g < nT; ++g) {
                 const bool full_tile = (g + 1) * kBN <= e.n_cached + qt * kBM + 1 && (qt + 1) * kBM <= p.K;
                 // after a failed (timed-out) wait the warp keeps walking the loops without waiting, so
                 // that the group barriers below are still reached by everyone
-                if (ok) ok = bar_wait(&s_full[grp], g & 1, p.status);
+                if (ok && !s_rdy) ok = bar_wait(&s_full[grp], g & 1, p.status);
                 tc_fence_after();
                 uint32_t va[2][32];
                 tc_ld32(tms, va[0]);
@@ -678,6 +696,8 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                         l_run = l_run * ex2f(fmaf(m_run, kLog2e, mneg)) + (t0 + t1);
                         m_run = m_new;
                     }
+                    // the next tile's logits were started when this warp group released the accumulator
+                    if (ch == 0) s_rdy = bar_probe(&s_full[grp], (g + 1) & 1);
                 }
             }
             // combine the two column halves of each row; publish shift and EMA weight per query.  The
@@ -708,6 +728,11 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const float *cq_h = c_q + grp * 128, *wq_h = w_q + grp * 128;
         // EMA partial of (head, query tile, query half): summed over tiles and halves by prefill_scores_kernel
         float *part = (kEma && head_ok_g) ? p.colpart + (((long long)bh_g * p.nQT + qt) * 2 + half) * p.Rpad : nullptr;
+        // The second head starts half a tile late (once the first head's first P^T is written) and stays
+        // there: one group's exponentials then overlap the other group's waits and stores, instead of
+        // all sixteen warps contending for the same pipes at the same time.
+        if (grp == 1 && ok && nT > 1) ok = bar_wait(&p_full[0], 0, p.status);
+        bool s_rdy = false;
         for (int jb = 0; jb < nT; ++jb) {
             const int u = nT + jb;
             const int key = jb * kBN + row;                      // row of the compacted key matrix
@@ -719,7 +744,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             // every key of the tile is a cached one and every (key, query) pair is visible: the common
             // case, kept free of per-element control flow so that the exponentials overlap
             const bool fast_tile = full_tile && (jb + 1) * kBN <= e.n_cached;
-            if (ok) ok = bar_wait(&s_full[grp], u & 1, p.status);
+            if (ok && !s_rdy) ok = bar_wait(&s_full[grp], u & 1, p.status);
             tc_fence_after();
             float acc = 0.f;
             uint32_t va[2][32];
@@ -729,6 +754,8 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             tc_fence_before();
             __syncwarp();
             if (lane_id == 0) bar_arrive(&s_free[grp]);
+            // asked now, needed after the arithmetic: has the P V product of the previous tile read P^T?
+            const bool p_rdy = jb == 0 || bar_probe(&p_free[grp], (jb - 1) & 1);
             uint32_t pk[2][16];
             if (fast_tile) {
                 uint64_t acc2[2] = {0ull, 0ull};
@@ -794,8 +821,10 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     }
                 }
             }
+            // the next tile's logits were started when this group released the accumulator
+            s_rdy = bar_probe(&s_full[grp], (u + 1) & 1);
             // the head's P^T buffer may be rewritten once the P V product of its previous tile has read it
-            if (ok && jb >= 1) ok = bar_wait(&p_free[grp], (jb - 1) & 1, p.status);
+            if (ok && !p_rdy) ok = bar_wait(&p_free[grp], (jb - 1) & 1, p.status);
 #pragma unroll
             for (int ch = 0; ch < 2; ++ch) {
 #pragma unroll
