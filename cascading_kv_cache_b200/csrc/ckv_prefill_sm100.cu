@@ -648,17 +648,17 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 // that the group barriers below are still reached by everyone
                 if (ok && !s_rdy) ok = bar_wait(&s_full[grp], g & 1, p.status);
                 tc_fence_after();
-                uint32_t va[2][32];
-                tc_ld32(tms, va[0]);
-                tc_ld32(tms + 32, va[1]);
-                tc_ld_wait();
-                // the accumulator can be overwritten as soon as it is in registers
-                tc_fence_before();
-                __syncwarp();
-                if (lane_id == 0) bar_arrive(&s_free[grp]);
 #pragma unroll
                 for (int ch = 0; ch < 2; ++ch) {
-                    uint32_t (&v)[32] = va[ch];
+                    uint32_t v[32];
+                    tc_ld32(tms + 32 * ch, v);
+                    tc_ld_wait();
+                    if (ch == 1) {
+                        // the accumulator can be overwritten as soon as it is in registers
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane_id == 0) bar_arrive(&s_free[grp]);
+                    }
                     if (!full_tile) {
                         const int col0 = g * kBN + 64 * half + 32 * ch;
 #pragma unroll
@@ -697,7 +697,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                         m_run = m_new;
                     }
                     // the next tile's logits were started when this warp group released the accumulator
-                    if (ch == 0) s_rdy = bar_probe(&s_full[grp], (g + 1) & 1);
+                    if (ch == 1) s_rdy = bar_probe(&s_full[grp], (g + 1) & 1);
                 }
             }
             // combine the two column halves of each row; publish shift and EMA weight per query.  The
@@ -747,22 +747,27 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             if (ok && !s_rdy) ok = bar_wait(&s_full[grp], u & 1, p.status);
             tc_fence_after();
             float acc = 0.f;
-            uint32_t va[2][32];
-            tc_ld32(tms, va[0]);
-            tc_ld32(tms + 32, va[1]);
-            tc_ld_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane_id == 0) bar_arrive(&s_free[grp]);
-            // asked now, needed after the arithmetic: has the P V product of the previous tile read P^T?
-            const bool p_rdy = jb == 0 || bar_probe(&p_free[grp], (jb - 1) & 1);
-            uint32_t pk[2][16];
-            if (fast_tile) {
-                uint64_t acc2[2] = {0ull, 0ull};
+            uint64_t acc2[2] = {0ull, 0ull};
+            bool p_rdy = jb == 0;
+            // The tile is taken in two chunks of 32 queries: load, compute, store.  Few values are live at
+            // a time, which leaves the compiler registers to overlap the dependent chains of many elements.
 #pragma unroll
-                for (int ch = 0; ch < 2; ++ch) {
-                    uint32_t (&v)[32] = va[ch];
-                    const int qbase = 64 * half + 32 * ch;
+            for (int ch = 0; ch < 2; ++ch) {
+                uint32_t v[32];
+                tc_ld32(tms + 32 * ch, v);
+                tc_ld_wait();
+                if (ch == 1) {
+                    // the accumulator can be overwritten as soon as it is in registers
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane_id == 0) bar_arrive(&s_free[grp]);
+                } else if (!p_rdy) {
+                    // asked now, needed after the arithmetic: has the P V product of the previous tile read P^T?
+                    p_rdy = bar_probe(&p_free[grp], (jb - 1) & 1);
+                }
+                uint32_t pk[16];
+                const int qbase = 64 * half + 32 * ch;
+                if (fast_tile) {
 #pragma unroll
                     for (int c4 = 0; c4 < 32; c4 += 4) {
                         // per-query constants arrive as two packed pairs per 16-byte load
@@ -782,18 +787,10 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                         float p0, p1, p2, p3;
                         upk2(pa, p0, p1);
                         upk2(pb, p2, p3);
-                        pk[ch][(c4 >> 1)] = P2<T>::pack_rounded(p0, p1);
-                        pk[ch][(c4 >> 1) + 1] = P2<T>::pack_rounded(p2, p3);
+                        pk[(c4 >> 1)] = P2<T>::pack_rounded(p0, p1);
+                        pk[(c4 >> 1) + 1] = P2<T>::pack_rounded(p2, p3);
                     }
-                }
-                float t0, t1;
-                upk2(add2(acc2[0], acc2[1]), t0, t1);
-                acc = t0 + t1;
-            } else {
-#pragma unroll
-                for (int ch = 0; ch < 2; ++ch) {
-                    uint32_t (&v)[32] = va[ch];
-                    const int qbase = 64 * half + 32 * ch;
+                } else {
 #pragma unroll
                     for (int c4 = 0; c4 < 32; c4 += 4) {
                         const float4 cq4 = *reinterpret_cast<const float4 *>(cq_h + qbase + c4);
@@ -816,23 +813,28 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                                 }
                             }
                         }
-                        pk[ch][(c4 >> 1)] = P2<T>::pack_rounded(pr[0], pr[1]);
-                        pk[ch][(c4 >> 1) + 1] = P2<T>::pack_rounded(pr[2], pr[3]);
+                        pk[(c4 >> 1)] = P2<T>::pack_rounded(pr[0], pr[1]);
+                        pk[(c4 >> 1) + 1] = P2<T>::pack_rounded(pr[2], pr[3]);
                     }
                 }
-            }
-            // the next tile's logits were started when this group released the accumulator
-            s_rdy = bar_probe(&s_full[grp], (u + 1) & 1);
-            // the head's P^T buffer may be rewritten once the P V product of its previous tile has read it
-            if (ok && !p_rdy) ok = bar_wait(&p_free[grp], (jb - 1) & 1, p.status);
-#pragma unroll
-            for (int ch = 0; ch < 2; ++ch) {
+                if (ch == 0) {
+                    // the head's P^T buffer may be rewritten once the P V product of its previous tile has read it
+                    if (ok && !p_rdy) ok = bar_wait(&p_free[grp], (jb - 1) & 1, p.status);
+                } else {
+                    // the next tile's logits were started when this group released the accumulator
+                    s_rdy = bar_probe(&s_full[grp], (u + 1) & 1);
+                }
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
                     const int chunk = ch * 4 + q4;
                     *reinterpret_cast<uint4 *>(pt_row + ((chunk ^ (row & 7)) << 4)) =
-                        make_uint4(pk[ch][4 * q4], pk[ch][4 * q4 + 1], pk[ch][4 * q4 + 2], pk[ch][4 * q4 + 3]);
+                        make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
                 }
+            }
+            if (fast_tile) {
+                float t0, t1;
+                upk2(add2(acc2[0], acc2[1]), t0, t1);
+                acc = t0 + t1;
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
