@@ -329,15 +329,18 @@ template <> struct P2<__half> {
 };
 
 // ------------------------------------------------------------------------------ attention kernel
-// Round an fp32 value to the precision of T with two integer operations on its bits (add half an
-// ulp of T, clear the low mantissa bits): round-half-up, which differs from the reference's
-// round-to-nearest-even only on exact ties.  Used on the masked / diagonal tiles.
+// Round an fp32 value to the precision of T, nearest-even, with integer operations on its bits (add
+// half an ulp of T minus one plus the bit that will become the last one, clear the low mantissa
+// bits).  Used on the masked / diagonal tiles; must agree bit for bit with round2_to_t, because the
+// two phases have to see the same rounded logit.
 template <typename T> __device__ __forceinline__ float round_to_t(float x);
 template <> __device__ __forceinline__ float round_to_t<__nv_bfloat16>(float x) {
-    return __uint_as_float((__float_as_uint(x) + 0x8000u) & 0xFFFF0000u);
+    const uint32_t u = __float_as_uint(x);
+    return __uint_as_float((u + 0x7FFFu + ((u >> 16) & 1u)) & 0xFFFF0000u);
 }
 template <> __device__ __forceinline__ float round_to_t<__half>(float x) {
-    return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
+    const uint32_t u = __float_as_uint(x);
+    return __uint_as_float((u + 0xFFFu + ((u >> 13) & 1u)) & 0xFFFFE000u);
 }
 
 // Packed fp32 pairs (one instruction for two elements on this architecture).
@@ -372,11 +375,13 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
     return r;
 }
-// Veltkamp split on the FMA pipe: c = x * (2^s + 1); hi = c - (c - x) is x rounded to nearest with
-// 24 - s significant bits, i.e. to the precision of T (s = 16 for bf16, 13 for fp16).
+// Veltkamp split on the FMA pipe: c = x * (2^s + 1); hi = c - (c - x) is x rounded to nearest-even with
+// 24 - s significant bits, i.e. to the precision of T (s = 16 for bf16, 13 for fp16).  c is formed by
+// ONE fma, x * 2^s + x: a separate multiply is contracted with the subtraction that follows it (the
+// .rn of the packed multiply does not stop that), and then nothing is rounded at all.
 template <typename T> __device__ __forceinline__ uint64_t round2_to_t(uint64_t x2) {
-    const float cst = std::is_same<T, __nv_bfloat16>::value ? 65537.0f : 8193.0f;
-    const uint64_t c2 = mul2(x2, pk2(cst, cst));
+    const float cst = std::is_same<T, __nv_bfloat16>::value ? 65536.0f : 8192.0f;
+    const uint64_t c2 = fma2(x2, pk2(cst, cst), x2);
     return sub2(c2, sub2(c2, x2));
 }
 

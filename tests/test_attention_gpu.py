@@ -69,6 +69,11 @@ STREAMS = [
     (1, 14, 2, 128, 4, 32, 8, 40, 9, 6, torch.bfloat16, "stride", "mean", False, False, 0.9999, 1e6),
     (1, 8, 8, 64, 2, 16, 4, 16, 10, 4, torch.float16, "ema", "mean", True, False, 0.99, 1e4),
     (1, 4, 2, 128, 64, 128, 2, 128, 4, 4, torch.bfloat16, "ema", "median", False, True, 0.9999, 5e5),
+    # several query tiles, a dozen key tiles (every ring slot and barrier phase wraps), ragged chunk
+    # lengths; G = 1 and G = 3 leave a head pair half empty
+    (1, 4, 4, 128, 4, 256, 4, 300, 6, 3, torch.float16, "ema", "mean", False, True, 0.999, 5e5),
+    (1, 6, 2, 128, 8, 512, 2, 333, 5, 2, torch.bfloat16, "ema", "mean", False, False, 0.9999, 1e6),
+    (1, 8, 2, 128, 4, 128, 8, 257, 6, 2, torch.bfloat16, "stride", "mean", False, True, 0.9999, 5e5),
 ]
 
 
