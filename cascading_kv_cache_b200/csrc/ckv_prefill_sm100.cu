@@ -385,6 +385,23 @@ template <typename T> __device__ __forceinline__ uint64_t round2_to_t(uint64_t x
     return sub2(c2, sub2(c2, x2));
 }
 
+// Probabilities: below 2^-14 fp16 is subnormal -- multiples of 2^-24 -- which (p + 0.5) - 0.5 rounds to,
+// nearest-even, in the [0.5, 1) binade where fp32's last bit is 2^-24.  bf16 has fp32's exponent range.
+constexpr float kHalfMinNormal = 6.103515625e-05f;
+template <typename T> __device__ __forceinline__ float round_prob_to_t(float x) { return round_to_t<T>(x); }
+template <> __device__ __forceinline__ float round_prob_to_t<__half>(float x) {
+    return x < kHalfMinNormal ? __fsub_rn(__fadd_rn(x, 0.5f), 0.5f) : round_to_t<__half>(x);
+}
+template <typename T> __device__ __forceinline__ uint64_t round2_prob_to_t(uint64_t x2) { return round2_to_t<T>(x2); }
+template <> __device__ __forceinline__ uint64_t round2_prob_to_t<__half>(uint64_t x2) {
+    const uint64_t half2 = pk2(0.5f, 0.5f);
+    float x0, x1, n0, n1, s0, s1;
+    upk2(x2, x0, x1);
+    upk2(round2_to_t<__half>(x2), n0, n1);
+    upk2(sub2(add2(x2, half2), half2), s0, s1);
+    return pk2(x0 < kHalfMinNormal ? s0 : n0, x1 < kHalfMinNormal ? s1 : n1);
+}
+
 // barrier among the 256 threads (8 warps) that serve one head of the pair
 __device__ __forceinline__ void group_sync(int grp) {
     if (grp == 0) asm volatile("bar.sync 2, 256;" ::: "memory");
@@ -782,8 +799,8 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                         float a0, a1, b0, b1;
                         upk2(fma2(sa, l2e2, cq.x), a0, a1);
                         upk2(fma2(sb, l2e2, cq.y), b0, b1);
-                        const uint64_t pa = round2_to_t<T>(pk2(ex2f(a0), ex2f(a1)));
-                        const uint64_t pb = round2_to_t<T>(pk2(ex2f(b0), ex2f(b1)));
+                        const uint64_t pa = round2_prob_to_t<T>(pk2(ex2f(a0), ex2f(a1)));
+                        const uint64_t pb = round2_prob_to_t<T>(pk2(ex2f(b0), ex2f(b1)));
                         if (kEma) {
                             const ulonglong2 wq = *reinterpret_cast<const ulonglong2 *>(wq_h + qbase + c4);
                             acc2[0] = fma2(pa, wq.x, acc2[0]);
@@ -808,13 +825,13 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                             const float sv = round_to_t<T>(__uint_as_float(v[c4 + uu]));
                             float pv = ex2f(fmaf(sv, kLog2e, cqv[uu]));
                             if (!full_tile && (qbase + c4 + uu) < q_min) pv = 0.f;
-                            pr[uu] = round_to_t<T>(pv);
+                            pr[uu] = round_prob_to_t<T>(pv);
                             if (kEma) {
                                 if (!is_new) {
                                     acc = fmaf(pr[uu], wqv[uu], acc);
                                 } else if (pr[uu] != 0.f) {
                                     const int d = qt * kBM + qbase + c4 + uu - (key - e.n_cached);
-                                    acc += round_to_t<T>(__fmul_rn(pr[uu], Elem<T>::to_f(w_new[d])));
+                                    acc += round_prob_to_t<T>(__fmul_rn(pr[uu], Elem<T>::to_f(w_new[d])));
                                 }
                             }
                         }
