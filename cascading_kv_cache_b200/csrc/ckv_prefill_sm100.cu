@@ -309,7 +309,13 @@ __device__ __forceinline__ uint64_t desc_from(uint32_t lo) {
 }
 
 template <typename T> struct P2;
+// pack(a, b): two fp32 values rounded to T (nearest-even, fp16 subnormals included) in one conversion
+// instruction; unpack(): the rounded values back in fp32.
 template <> struct P2<__nv_bfloat16> {
+    static __device__ __forceinline__ void unpack(uint32_t v, float &a, float &b) {
+        a = __uint_as_float(v << 16);
+        b = __uint_as_float(v & 0xFFFF0000u);
+    }
     static __device__ __forceinline__ uint32_t pack(float a, float b) {
         __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
         return *reinterpret_cast<uint32_t *>(&v);
@@ -321,6 +327,11 @@ template <> struct P2<__nv_bfloat16> {
     }
 };
 template <> struct P2<__half> {
+    static __device__ __forceinline__ void unpack(uint32_t v, float &a, float &b) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&v));
+        a = f.x;
+        b = f.y;
+    }
     static __device__ __forceinline__ uint32_t pack(float a, float b) {
         __half2 v = __floats2half2_rn(a, b);
         return *reinterpret_cast<uint32_t *>(&v);
@@ -391,15 +402,6 @@ constexpr float kHalfMinNormal = 6.103515625e-05f;
 template <typename T> __device__ __forceinline__ float round_prob_to_t(float x) { return round_to_t<T>(x); }
 template <> __device__ __forceinline__ float round_prob_to_t<__half>(float x) {
     return x < kHalfMinNormal ? __fsub_rn(__fadd_rn(x, 0.5f), 0.5f) : round_to_t<__half>(x);
-}
-template <typename T> __device__ __forceinline__ uint64_t round2_prob_to_t(uint64_t x2) { return round2_to_t<T>(x2); }
-template <> __device__ __forceinline__ uint64_t round2_prob_to_t<__half>(uint64_t x2) {
-    const uint64_t half2 = pk2(0.5f, 0.5f);
-    float x0, x1, n0, n1, s0, s1;
-    upk2(x2, x0, x1);
-    upk2(round2_to_t<__half>(x2), n0, n1);
-    upk2(sub2(add2(x2, half2), half2), s0, s1);
-    return pk2(x0 < kHalfMinNormal ? s0 : n0, x1 < kHalfMinNormal ? s1 : n1);
 }
 
 // barrier among the 256 threads (8 warps) that serve one head of the pair
@@ -799,18 +801,20 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                         float a0, a1, b0, b1;
                         upk2(fma2(sa, l2e2, cq.x), a0, a1);
                         upk2(fma2(sb, l2e2, cq.y), b0, b1);
-                        const uint64_t pa = round2_prob_to_t<T>(pk2(ex2f(a0), ex2f(a1)));
-                        const uint64_t pb = round2_prob_to_t<T>(pk2(ex2f(b0), ex2f(b1)));
+                        // the conversion instruction rounds both probabilities to T and packs them for
+                        // P^T; the EMA sum needs the rounded values back in fp32
+                        const uint32_t qa = P2<T>::pack(ex2f(a0), ex2f(a1));
+                        const uint32_t qb = P2<T>::pack(ex2f(b0), ex2f(b1));
                         if (kEma) {
                             const ulonglong2 wq = *reinterpret_cast<const ulonglong2 *>(wq_h + qbase + c4);
-                            acc2[0] = fma2(pa, wq.x, acc2[0]);
-                            acc2[1] = fma2(pb, wq.y, acc2[1]);
+                            float p0, p1, p2, p3;
+                            P2<T>::unpack(qa, p0, p1);
+                            P2<T>::unpack(qb, p2, p3);
+                            acc2[0] = fma2(pk2(p0, p1), wq.x, acc2[0]);
+                            acc2[1] = fma2(pk2(p2, p3), wq.y, acc2[1]);
                         }
-                        float p0, p1, p2, p3;
-                        upk2(pa, p0, p1);
-                        upk2(pb, p2, p3);
-                        pk[(c4 >> 1)] = P2<T>::pack_rounded(p0, p1);
-                        pk[(c4 >> 1) + 1] = P2<T>::pack_rounded(p2, p3);
+                        pk[(c4 >> 1)] = qa;
+                        pk[(c4 >> 1) + 1] = qb;
                     }
                 } else {
 #pragma unroll
