@@ -53,28 +53,63 @@ def measured_peak_hbm():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons while the timed region runs: through NVML every 5 ms
+    (read-only queries), or with one nvidia-smi process per sample when NVML cannot be loaded."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    # NVML clocks-event-reason bits, in the order of `NAMES`
+    BITS = (0x8, 0x40, 0x20, 0x4)
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
 
     def __init__(self, gpu_index):
         self.gpu_index = gpu_index
-        self.samples = []
+        self.samples = []          # (sm_mhz, max_mhz, [bool] * 4)
+        self.source = "nvidia-smi"
         self._stop = threading.Event()
         self._thread = None
+        self._nvml = None
+        self._handle = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            try:
+                uuid = str(torch.cuda.get_device_properties(gpu_index).uuid)
+                self._handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid) if not uuid.startswith("GPU-") else uuid)
+            except Exception:
+                self._handle = pynvml.nvmlDeviceGetHandleByIndex(gpu_index)
+            self._nvml = pynvml
+            self.source = "nvml"
+        except Exception:
+            self._nvml = None
+
+    def _sample_nvml(self):
+        n = self._nvml
+        sm = n.nvmlDeviceGetClockInfo(self._handle, n.NVML_CLOCK_SM)
+        mx = n.nvmlDeviceGetMaxClockInfo(self._handle, n.NVML_CLOCK_SM)
+        try:
+            mask = n.nvmlDeviceGetCurrentClocksEventReasons(self._handle)
+        except Exception:
+            mask = n.nvmlDeviceGetCurrentClocksThrottleReasons(self._handle)
+        self.samples.append((float(sm), float(mx), [bool(mask & b) for b in self.BITS]))
+
+    def _sample_smi(self):
+        out = subprocess.run(["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.FIELDS}",
+                              "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5)
+        parts = [p.strip() for p in out.stdout.strip().split(",")]
+        if len(parts) >= 6:
+            self.samples.append((float(parts[0]), float(parts[1]), [x.lower().startswith("active") for x in parts[2:6]]))
 
     def _run(self):
         while not self._stop.is_set():
             try:
-                out = subprocess.run(["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.FIELDS}",
-                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5)
-                parts = [p.strip() for p in out.stdout.strip().split(",")]
-                if len(parts) >= 6:
-                    self.samples.append(parts)
+                if self._nvml is not None:
+                    self._sample_nvml()
+                else:
+                    self._sample_smi()
             except Exception:
                 pass
-            self._stop.wait(0.1)
+            self._stop.wait(0.005 if self._nvml is not None else 0.1)
 
     def __enter__(self):
         self._thread = threading.Thread(target=self._run, daemon=True)
@@ -88,11 +123,10 @@ class ClockSampler:
     def summary(self):
         if not self.samples:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        sm = sorted(float(s[0]) for s in self.samples)
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
-        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": float(self.samples[0][1]), "reasons": reasons,
-                "samples": len(sm)}
+        sm = sorted(s[0] for s in self.samples)
+        reasons = [n for i, n in enumerate(self.NAMES) if any(s[2][i] for s in self.samples)]
+        return {"sm_mhz": sm[len(sm) // 2], "sm_min_mhz": sm[0], "sm_max_mhz": self.samples[0][1], "reasons": reasons,
+                "samples": len(sm), "source": self.source}
 
 
 def algorithmic_bytes(w):
@@ -175,11 +209,12 @@ def run_prefill_leg(dev, chunks=6, warm=2):
         step(i)
     torch.cuda.synchronize()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record()
-    for i in range(chunks):
-        step(i)
-    ev1.record()
-    torch.cuda.synchronize()
+    with ClockSampler(dev.index or 0) as clocks:
+        ev0.record()
+        for i in range(chunks):
+            step(i)
+        ev1.record()
+        torch.cuda.synchronize()
     ms_chunk = ev0.elapsed_time(ev1) / chunks
     k_ms, _, k_name = profiling.time_dominant_kernel(step, n_steps=3)
     launches = profiling.last_launch_count()
@@ -191,7 +226,7 @@ def run_prefill_leg(dev, chunks=6, warm=2):
             "tflops": flops / (ms_chunk * 1e-3) / 1e12, "kernel": k_name, "kernel_ms": k_ms,
             "kernel_tflops": flops / (k_ms * 1e-3) / 1e12, "peak_tflops": burst, "peak_kind": kind,
             "kernel_frac_of_peak": flops / (k_ms * 1e-3) / 1e12 / burst, "launches_per_chunk": launches,
-            "status": cache.kernel_status()}
+            "clocks": clocks.summary(), "status": cache.kernel_status()}
 
 
 def run_reference(args, w, rank, world):

@@ -71,6 +71,9 @@ struct PrefillParams {
     void *kcat;        // [B*KVH][Rpad][128]
     void *vcat;        // [B*KVH][Rpad][128]
     float *colpart;    // [B*H][nQT][2 query halves][Rpad]
+    float2 *stats;     // [B*H][nSplit][Kpad]: running max and sum of exp of every query over one key split
+    float *opart;      // [nSplit][B*H][Kpad][128]: out partial of a key split (only when nSplit > 1)
+    int nSplit;
     void *new_scores;  // [B*KVH][K]
     int B, KVH, H, G, NS, S, C, K, Kpad, Rpad, nQT;
     int ema, head_reduction;
@@ -433,7 +436,10 @@ constexpr float kMasked = -1.0e30f, kMaskedBelow = -1.0e29f;
 // are issued as soon as the softmax warps have read the current ones) and its slot refilled at once,
 // so one K slot suffices; a V tile is consumed at the END of its period, so V is double-buffered.
 // A tile arrives 500-800 cycles after it is requested.
-template <typename T, bool kEma>
+// The two phases are two launches of this kernel (kPhaseB false, then true): phase A leaves (max, sum)
+// per query and key split in global memory.  Each launch also splits the key tiles of a query tile
+// over gridDim.z CTAs, chosen on the host so that the grid fills whole rounds of the SMs.
+template <typename T, bool kEma, bool kPhaseB>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, PrefillParams p) {
@@ -465,7 +471,10 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const Extents e = make_extents(p);
     const int q_hi = min(p.K, kBM * (qt + 1));
     const int n_keys = e.n_cached + q_hi;
-    const int nT = (n_keys + kBN - 1) / kBN;                    // key tiles of either phase
+    const int nT_all = (n_keys + kBN - 1) / kBN;                // key tiles this query tile sees
+    const int split = blockIdx.z;
+    const int t0 = (int)((long long)nT_all * split / p.nSplit);   // this CTA's tiles: [t0, t0 + nT)
+    const int nT = (int)((long long)nT_all * (split + 1) / p.nSplit) - t0;
 
     if (threadIdx.x == 0) {
         bar_init(q_full, 1);
@@ -518,21 +527,22 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 tma_2d(dst, tm, 0, y, full);
                 tma_2d(dst + kSubBytes, tm, 64, y, full);
             };
-            // phase A: K_0 .. K_{n-1} through four slots
-            for (int g = 0; ok && g < nT; ++g) {
-                const int slot = g % kRingA;
-                if (g >= kRingA) ok = bar_wait(&ra_empty[slot], ((g / kRingA) - 1) & 1, p.status);
-                if (ok) load_tile(&tmK, g, slot, &ra_full[slot]);
-            }
-            // every phase A MMA has read its tile before phase B reuses the slots
-            if (ok) ok = bar_wait(a_done, 0, p.status);
-            // phase B: K_j into slot 0, V_j into slot 1 + (j & 1)
-            for (int j = 0; ok && j < nT; ++j) {
-                const int vs = 1 + (j & 1);
-                if (j >= 1) ok = bar_wait(&rb_empty[0], (j - 1) & 1, p.status);
-                if (ok) load_tile(&tmK, j, 0, &rb_full[0]);
-                if (ok && j >= 2) ok = bar_wait(&rb_empty[vs], ((j >> 1) - 1) & 1, p.status);
-                if (ok) load_tile(&tmV, j, vs, &rb_full[vs]);
+            if (!kPhaseB) {
+                // phase A: the K tiles through five slots
+                for (int g = 0; ok && g < nT; ++g) {
+                    const int slot = g % kRingA;
+                    if (g >= kRingA) ok = bar_wait(&ra_empty[slot], ((g / kRingA) - 1) & 1, p.status);
+                    if (ok) load_tile(&tmK, t0 + g, slot, &ra_full[slot]);
+                }
+            } else {
+                // phase B: K_j into slot 0, V_j into slot 1 + (j & 1)
+                for (int j = 0; ok && j < nT; ++j) {
+                    const int vs = 1 + (j & 1);
+                    if (j >= 1) ok = bar_wait(&rb_empty[0], (j - 1) & 1, p.status);
+                    if (ok) load_tile(&tmK, t0 + j, 0, &rb_full[0]);
+                    if (ok && j >= 2) ok = bar_wait(&rb_empty[vs], ((j >> 1) - 1) & 1, p.status);
+                    if (ok) load_tile(&tmV, t0 + j, vs, &rb_full[vs]);
+                }
             }
         }
     } else if (warp == 1) {
@@ -540,15 +550,15 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (lane_id == 0) {
             const uint32_t id_kk = idesc<T>(false, false);   // both operands K-major (Q K^T and K Q^T)
             const uint32_t q_addr = s_u32(smem + kOffQ), r_addr = s_u32(smem + kOffRing);
-            bool ok = bar_wait(q_full, 0, p.status) && bar_wait(qt_ready, 0, p.status);
+            bool ok = bar_wait(q_full, 0, p.status) && (kPhaseB || bar_wait(qt_ready, 0, p.status));
             // low descriptor words of the fixed tiles and of the ring slots
             const uint32_t q_lo[2] = {desc_lo_k(q_addr), desc_lo_k(q_addr + kTileBytes)};
             // slot i of the ring: shared-memory addresses stay below 2^18, so the address field is linear in i
             const uint32_t r_lo_k = desc_lo_k(r_addr);
             constexpr uint32_t kSlotStep = (uint32_t)(kTileBytes >> 4);
 
-            // ---- phase A: S[hd] = Q[hd] K^T with Q read from tensor memory; u = g
-            for (int g = 0; ok && g < nT; ++g) {
+            // ---- phase A: S[hd] = Q[hd] K^T with Q read from tensor memory
+            for (int g = 0; !kPhaseB && ok && g < nT; ++g) {
                 const int slot = g % kRingA;
                 ok = bar_wait(&ra_full[slot], (g / kRingA) & 1, p.status);
 #pragma unroll
@@ -566,17 +576,15 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     tc_commit(&s_full[hd]);
                 }
             }
-            if (ok) tc_commit(a_done);
 
-            // ---- phase B: S^T[hd] = K Q[hd]^T; S[hd] completes once per u = nT + jb.  A tile's logits are
-            //      started as soon as the group has read the previous tile's out of tensor memory.
-            for (int jb = 0; ok && jb < nT; ++jb) {
-                const int u = nT + jb;
+            // ---- phase B: S^T[hd] = K Q[hd]^T.  A tile's logits are started as soon as the group has read
+            //      the previous tile's out of tensor memory.
+            for (int jb = 0; kPhaseB && ok && jb < nT; ++jb) {
                 ok = bar_wait(&rb_full[0], jb & 1, p.status);
                 const uint32_t kb_lo = r_lo_k;
 #pragma unroll
                 for (int hd = 0; hd < 2; ++hd) {
-                    if (ok) ok = bar_wait(&s_free[hd], (u - 1) & 1, p.status);
+                    if (ok && jb >= 1) ok = bar_wait(&s_free[hd], (jb - 1) & 1, p.status);
                     if (!ok) break;
                     tc_fence_after();
 #pragma unroll
@@ -593,13 +601,12 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         // ---------------------------------------------------------------- P V issuer
         // A thread of its own: an issuing thread is held while the tensor pipe's queue is full, and
         // one thread issuing both products would react late to whichever operand arrives meanwhile.
-        if (lane_id == 0) {
+        if (kPhaseB && lane_id == 0) {
             const uint32_t id_pv = idesc<T>(true, true);     // out^T = V^T P^T: both operands MN-major
             const uint32_t p_lo[2] = {desc_lo_mn(s_u32(smem + kOffP)), desc_lo_mn(s_u32(smem + kOffP + kTileBytes))};
             const uint32_t r_lo_mn = desc_lo_mn(s_u32(smem + kOffRing));
             constexpr uint32_t kSlotStep = (uint32_t)(kTileBytes >> 4);
-            // out^T overlays the Q tiles that phase A reads from tensor memory
-            bool ok = bar_wait(a_done, 0, p.status);
+            bool ok = true;
             for (int jb = 0; ok && jb < nT; ++jb) {
                 const int slot = 1 + (jb & 1);
                 const uint32_t vb_lo = r_lo_mn + slot * kSlotStep;
@@ -639,8 +646,8 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         bool ok = true;
 
         // ---- Q tile of this group's head -> tensor memory (rows = lanes, the row's 64 words in order)
-        ok = bar_wait(q_full, 0, p.status);
-        {
+        if (!kPhaseB) {
+            ok = bar_wait(q_full, 0, p.status);
             uint32_t qw[32];
             const uint8_t *qsm = smem + kOffQ + grp * kTileBytes + half * kSubBytes + row * 128;
 #pragma unroll
@@ -658,16 +665,17 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             if (lane_id == 0) bar_arrive(qt_ready);
         }
 
+        const int qg = qt * kBM + row;                                    // phase A and the prologue of B: row = query
+        const bool row_ok = qg < p.K;
         // ---- phase A: rows are queries; running max and sum of exp over the logits rounded to T,
         //      renormalised per 32-column chunk
-        {
-            const int qg = qt * kBM + row;
-            const bool row_ok = qg < p.K;
+        if (!kPhaseB) {
             const int row_limit = e.n_cached + (row_ok ? qg + 1 : 0);     // visible columns: [0, row_limit)
             float m_run = kMasked, l_run = 0.f;
             bool s_rdy = false;                                           // the tile's logits are known to be complete
             for (int g = 0; g < nT; ++g) {
-                const bool full_tile = (g + 1) * kBN <= e.n_cached + qt * kBM + 1 && (qt + 1) * kBM <= p.K;
+                const int gg = t0 + g;                                        // tile index among all the keys
+                const bool full_tile = (gg + 1) * kBN <= e.n_cached + qt * kBM + 1 && (qt + 1) * kBM <= p.K;
                 // after a failed (timed-out) wait the warp keeps walking the loops without waiting, so
                 // that the group barriers below are still reached by everyone
                 if (ok && !s_rdy) ok = bar_wait(&s_full[grp], g & 1, p.status);
@@ -684,7 +692,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                         if (lane_id == 0) bar_arrive(&s_free[grp]);
                     }
                     if (!full_tile) {
-                        const int col0 = g * kBN + 64 * half + 32 * ch;
+                        const int col0 = gg * kBN + 64 * half + 32 * ch;
 #pragma unroll
                         for (int c = 0; c < 32; ++c)
                             if (col0 + c >= row_limit) v[c] = __float_as_uint(kMasked);
@@ -724,27 +732,42 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     if (ch == 1) s_rdy = bar_probe(&s_full[grp], (g + 1) & 1);
                 }
             }
-            // combine the two column halves of each row; publish shift and EMA weight per query.  The
-            // second half hands its statistics over through the arrays that then receive the results.
+            // combine the two column halves of each row and leave (max, sum) of this key split in global memory
             if (half == 1) {
                 c_q[grp * 128 + row] = m_run;
                 w_q[grp * 128 + row] = l_run;
             }
             group_sync(grp);
-            float cq = -INFINITY;
-            if (half == 0) {
+            if (half == 0 && head_ok_g) {
                 const float m1 = c_q[grp * 128 + row], l1 = w_q[grp * 128 + row];
                 const float mm = fmaxf(m_run, m1);
+                float l = 0.f;
+                if (mm > kMaskedBelow) l = l_run * ex2f((m_run - mm) * kLog2e) + l1 * ex2f((m1 - mm) * kLog2e);
+                p.stats[((long long)bh_g * p.nSplit + split) * p.Kpad + qg] = make_float2(mm, l);
+            }
+        } else {
+            // ---- prologue of phase B: softmax shift c_q = -max log2e - log2(sum) of each query from the
+            //      statistics of all key splits; EMA weight of each query
+            if (half == 0) {
+                const float2 *st = p.stats + (long long)bh_g * p.nSplit * p.Kpad + qg;
+                float mm = kMasked;
+                for (int sp = 0; sp < p.nSplit; ++sp) mm = fmaxf(mm, st[(long long)sp * p.Kpad].x);
+                float cq = -INFINITY;
                 if (row_ok && mm > kMaskedBelow) {
-                    const float l = l_run * ex2f((m_run - mm) * kLog2e) + l1 * ex2f((m1 - mm) * kLog2e);
+                    float l = 0.f;
+                    for (int sp = 0; sp < p.nSplit; ++sp) {
+                        const float2 ml = st[(long long)sp * p.Kpad];
+                        l += ml.y * ex2f((ml.x - mm) * kLog2e);
+                    }
                     cq = -mm * kLog2e - __log2f(l);
                 }
+                c_q[grp * 128 + row] = cq;
+            } else {
+                w_q[grp * 128 + row] = (kEma && row_ok) ? p.ema_w_cache[qg] : 0.f;
             }
             group_sync(grp);
-            if (half == 0) c_q[grp * 128 + row] = cq;
-            else w_q[grp * 128 + row] = (kEma && row_ok) ? p.ema_w_cache[qg] : 0.f;
-            group_sync(grp);
         }
+        const int nTb = kPhaseB ? nT : 0;                                 // phase A launches skip what follows
 
         // ---- phase B: rows are keys (S^T); this thread owns key `key`, queries [64 half, 64 half + 64)
         const T *w_new = reinterpret_cast<const T *>(p.ema_w_new);
@@ -752,23 +775,19 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const float *cq_h = c_q + grp * 128, *wq_h = w_q + grp * 128;
         // EMA partial of (head, query tile, query half): summed over tiles and halves by prefill_scores_kernel
         float *part = (kEma && head_ok_g) ? p.colpart + (((long long)bh_g * p.nQT + qt) * 2 + half) * p.Rpad : nullptr;
-        // The second head starts half a tile late (once the first head's first P^T is written) and stays
-        // there: one group's exponentials then overlap the other group's waits and stores, instead of
-        // all sixteen warps contending for the same pipes at the same time.
-        if (grp == 1 && ok && nT > 1) ok = bar_wait(&p_full[0], 0, p.status);
         bool s_rdy = false;
-        for (int jb = 0; jb < nT; ++jb) {
-            const int u = nT + jb;
-            const int key = jb * kBN + row;                      // row of the compacted key matrix
+        for (int jb = 0; jb < nTb; ++jb) {
+            const int jg = t0 + jb;                              // tile index among all the keys
+            const int key = jg * kBN + row;                      // row of the compacted key matrix
             const bool key_ok = key < n_keys;
             const bool is_new = key >= e.n_cached;
             // query q of the tile sees this key iff  qt*128 + q >= key - n_cached
             const int q_min = key_ok ? key - e.n_cached - qt * kBM : kBM;
-            const bool full_tile = (jb + 1) * kBN <= e.n_cached + qt * kBM + 1 && (qt + 1) * kBM <= p.K;
+            const bool full_tile = (jg + 1) * kBN <= e.n_cached + qt * kBM + 1 && (qt + 1) * kBM <= p.K;
             // every key of the tile is a cached one and every (key, query) pair is visible: the common
             // case, kept free of per-element control flow so that the exponentials overlap
-            const bool fast_tile = full_tile && (jb + 1) * kBN <= e.n_cached;
-            if (ok && !s_rdy) ok = bar_wait(&s_full[grp], u & 1, p.status);
+            const bool fast_tile = full_tile && (jg + 1) * kBN <= e.n_cached;
+            if (ok && !s_rdy) ok = bar_wait(&s_full[grp], jb & 1, p.status);
             tc_fence_after();
             float acc = 0.f;
             uint64_t acc2[2] = {0ull, 0ull};
@@ -848,7 +867,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     if (ok && !p_rdy) ok = bar_wait(&p_free[grp], (jb - 1) & 1, p.status);
                 } else {
                     // the next tile's logits were started when this group released the accumulator
-                    s_rdy = bar_probe(&s_full[grp], (u + 1) & 1);
+                    s_rdy = bar_probe(&s_full[grp], (jb + 1) & 1);
                 }
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
@@ -869,23 +888,35 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             if (kEma && part && key_ok && key >= (int)e.sinks) part[key] = acc;
         }
 
-        // ---- epilogue: out^T lives in tensor memory, lane = dim, column = query
-        if (ok && bar_wait(o_full, 0, p.status) && head_ok_g) {
+        // ---- epilogue: out^T lives in tensor memory, lane = dim, column = query.  With one key split the
+        //      result is final; otherwise the split's fp32 partial goes to scratch for prefill_combine_kernel.
+        if (kPhaseB && ok && bar_wait(o_full, 0, p.status) && head_ok_g) {
             tc_fence_after();
             const int d = row;
+            float *opart = p.opart + (((long long)split * p.B * p.H + bh_g) * p.Kpad + qt * kBM) * 128;
 #pragma unroll 1
             for (int ch = 0; ch < 2; ++ch) {
                 uint32_t v[32];
                 const int qbase = 64 * half + 32 * ch;
-                tc_ld32(tmo + lane_base + qbase, v);
-                tc_ld_wait();
+                if (nT > 0) {
+                    tc_ld32(tmo + lane_base + qbase, v);
+                    tc_ld_wait();
+                } else {
 #pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    const int qg = qt * kBM + qbase + c;
-                    if (qg < p.K) {
-                        T *orow = reinterpret_cast<T *>(p.out) + b * p.osb + head_g * p.osh + (long long)qg * p.ost;
-                        orow[d] = Elem<T>::from_f(__uint_as_float(v[c]));
+                    for (int c = 0; c < 32; ++c) v[c] = 0u;      // an empty key split contributes nothing
+                }
+                if (p.nSplit == 1) {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        const int qo = qt * kBM + qbase + c;
+                        if (qo < p.K) {
+                            T *orow = reinterpret_cast<T *>(p.out) + b * p.osb + head_g * p.osh + (long long)qo * p.ost;
+                            orow[d] = Elem<T>::from_f(__uint_as_float(v[c]));
+                        }
                     }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) opart[(qbase + c) * 128 + d] = __uint_as_float(v[c]);
                 }
             }
         }
@@ -897,6 +928,31 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols));
     }
+}
+
+// Sum of the key splits' fp32 partials, in split order, rounded to T.  One thread per 4 dims.
+template <typename T>
+__global__ void __launch_bounds__(256) prefill_combine_kernel(PrefillParams p) {
+    const long long n4 = (long long)p.B * p.H * p.K * 32;
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n4) return;
+    const int d4 = (int)(idx & 31);
+    const long long row = idx >> 5;                 // (b, h, q)
+    const int q = (int)(row % p.K);
+    const int bh = (int)(row / p.K);
+    const long long split_stride = (long long)p.B * p.H * p.Kpad * 128;
+    const float *src = p.opart + ((long long)bh * p.Kpad + q) * 128 + 4 * d4;
+    float4 acc = *reinterpret_cast<const float4 *>(src);
+    for (int sp = 1; sp < p.nSplit; ++sp) {
+        const float4 x = *reinterpret_cast<const float4 *>(src + sp * split_stride);
+        acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+    }
+    const int b = bh / p.H, h = bh % p.H;
+    T *o = reinterpret_cast<T *>(p.out) + b * p.osb + h * p.osh + (long long)q * p.ost + 4 * d4;
+    o[0] = Elem<T>::from_f(acc.x);
+    o[1] = Elem<T>::from_f(acc.y);
+    o[2] = Elem<T>::from_f(acc.z);
+    o[3] = Elem<T>::from_f(acc.w);
 }
 
 // ----------------------------------------------------------------------------------- score reduce
@@ -992,10 +1048,39 @@ int rows_map_128(CUtensorMap *tm, const void *base, uint64_t rows, int dtype) {
 
 size_t a256(size_t x) { return (x + 255) & ~(size_t)255; }
 
+constexpr int kMaxSplit = 4;
+
+// Key splits per query tile: the smallest count that minimises the rounds of CTAs per unit of work,
+// rounds(s) / s with rounds(s) = ceil(items * s / SMs) -- provided every split keeps a few tiles.
+int choose_splits(long long items, int sms, int min_tiles) {
+    int best = 1;
+    double best_cost = (double)((items + sms - 1) / sms);
+    for (int sp = 2; sp <= kMaxSplit; ++sp) {
+        if (min_tiles < 4 * sp) break;
+        const double cost = (double)((items * sp + sms - 1) / sms) / sp;
+        if (cost < best_cost * 0.97) {
+            best = sp;
+            best_cost = cost;
+        }
+    }
+    return best;
+}
+
 struct PrefillScratch {
-    size_t status, qs, kcat, vcat, colpart, new_scores, upd, upd_bytes, total;
-    int Kpad, Rpad, nQT;
+    size_t status, qs, kcat, vcat, colpart, stats, opart, new_scores, upd, upd_bytes, total;
+    int Kpad, Rpad, nQT, nSplit;
 };
+
+// SM count of the current device (the B200's 148 where no device can be asked, e.g. when only sizes are wanted)
+int sm_count() {
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        sms <= 0) {
+        (void)cudaGetLastError();
+        return 148;
+    }
+    return sms;
+}
 
 PrefillScratch prefill_scratch(const Dims &d, int K) {
     PrefillScratch s;
@@ -1008,6 +1093,11 @@ PrefillScratch prefill_scratch(const Dims &d, int K) {
     s.kcat = off; off += a256((size_t)d.B * d.KVH * s.Rpad * 256);
     s.vcat = off; off += a256((size_t)d.B * d.KVH * s.Rpad * 256);
     s.colpart = off; off += a256((size_t)d.B * d.H * s.nQT * 2 * s.Rpad * 4);
+    // one CTA per (query tile, KV head, head pair, key split).  The number of key tiles is device state:
+    // the split count is chosen for a full cache, and a split that turns out empty costs one idle CTA.
+    s.nSplit = choose_splits((long long)s.nQT * d.B * d.KVH * ((d.G + 1) / 2), sm_count(), s.Rpad / kBN);
+    s.stats = off; off += a256((size_t)d.B * d.H * s.nSplit * s.Kpad * sizeof(float2));
+    s.opart = off; off += s.nSplit > 1 ? a256((size_t)s.nSplit * d.B * d.H * s.Kpad * 128 * 4) : 0;
     s.new_scores = off; off += a256((size_t)d.B * d.KVH * K * 2);
     s.upd_bytes = update_chunk_workspace_bytes(d, K);
     s.upd = off; off += s.upd_bytes;
@@ -1048,14 +1138,13 @@ int launch_prefill_tuned(const Dims &d, const ckv_layer_state *st, const void *q
 
     static bool attr_set = false;
     if (!attr_set) {
-        CKV_CUDA_CHECK(cudaFuncSetAttribute(prefill_attn_kernel<__nv_bfloat16, true>,
-                                            cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));
-        CKV_CUDA_CHECK(cudaFuncSetAttribute(prefill_attn_kernel<__nv_bfloat16, false>,
-                                            cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));
-        CKV_CUDA_CHECK(cudaFuncSetAttribute(prefill_attn_kernel<__half, true>,
-                                            cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));
-        CKV_CUDA_CHECK(cudaFuncSetAttribute(prefill_attn_kernel<__half, false>,
-                                            cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));
+        const void *kernels[] = {
+            (const void *)prefill_attn_kernel<__nv_bfloat16, true, false>, (const void *)prefill_attn_kernel<__nv_bfloat16, true, true>,
+            (const void *)prefill_attn_kernel<__nv_bfloat16, false, false>, (const void *)prefill_attn_kernel<__nv_bfloat16, false, true>,
+            (const void *)prefill_attn_kernel<__half, true, false>, (const void *)prefill_attn_kernel<__half, true, true>,
+            (const void *)prefill_attn_kernel<__half, false, false>, (const void *)prefill_attn_kernel<__half, false, true>};
+        for (const void *k : kernels)
+            CKV_CUDA_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));
         attr_set = true;
     }
     uint8_t *ws = (uint8_t *)workspace;
@@ -1073,6 +1162,7 @@ int launch_prefill_tuned(const Dims &d, const ckv_layer_state *st, const void *q
     p.status = (int *)(ws + s.status);
     p.qs = ws + s.qs; p.kcat = ws + s.kcat; p.vcat = ws + s.vcat;
     p.colpart = (float *)(ws + s.colpart); p.new_scores = ws + s.new_scores;
+    p.stats = (float2 *)(ws + s.stats); p.opart = (float *)(ws + s.opart);
     p.B = d.B; p.KVH = d.KVH; p.H = d.H; p.G = d.G; p.NS = d.NS; p.S = d.S; p.C = d.C;
     p.K = n_tokens; p.Kpad = s.Kpad; p.Rpad = s.Rpad; p.nQT = s.nQT;
     p.ema = ema; p.head_reduction = d.head_reduction;
@@ -1089,22 +1179,36 @@ int launch_prefill_tuned(const Dims &d, const ckv_layer_state *st, const void *q
     const long long prep_work = ((long long)d.B * d.KVH * s.Rpad + (long long)d.B * d.H * s.Kpad) * 8;
     int prep_blocks = (int)((prep_work + 255) / 256);
     if (prep_blocks > 148 * 16) prep_blocks = 148 * 16;
-    const dim3 grid(s.nQT, d.B * d.KVH * ((d.G + 1) / 2));   // one CTA per (query tile, KV head, head pair)
+    p.nSplit = s.nSplit;
+    const dim3 grid(s.nQT, d.B * d.KVH * ((d.G + 1) / 2), p.nSplit);
+    const long long comb = (long long)d.B * d.H * n_tokens * 32;
     if (d.dtype == CKV_BF16) {
         prefill_prep_kernel<__nv_bfloat16><<<prep_blocks, 256, 0, stream>>>(p);
         if (hook) hook->before(stream, "prefill_attn_kernel");
-        if (ema) prefill_attn_kernel<__nv_bfloat16, true><<<grid, kAttnThreads, kAttnSmem, stream>>>(tmQ, tmK, tmV, p);
-        else prefill_attn_kernel<__nv_bfloat16, false><<<grid, kAttnThreads, kAttnSmem, stream>>>(tmQ, tmK, tmV, p);
+        if (ema) {
+            prefill_attn_kernel<__nv_bfloat16, true, false><<<grid, kAttnThreads, kAttnSmem, stream>>>(tmQ, tmK, tmV, p);
+            prefill_attn_kernel<__nv_bfloat16, true, true><<<grid, kAttnThreads, kAttnSmem, stream>>>(tmQ, tmK, tmV, p);
+        } else {
+            prefill_attn_kernel<__nv_bfloat16, false, false><<<grid, kAttnThreads, kAttnSmem, stream>>>(tmQ, tmK, tmV, p);
+            prefill_attn_kernel<__nv_bfloat16, false, true><<<grid, kAttnThreads, kAttnSmem, stream>>>(tmQ, tmK, tmV, p);
+        }
+        if (p.nSplit > 1) prefill_combine_kernel<__nv_bfloat16><<<(unsigned)((comb + 255) / 256), 256, 0, stream>>>(p);
         if (hook) hook->after(stream);
     } else {
         prefill_prep_kernel<__half><<<prep_blocks, 256, 0, stream>>>(p);
         if (hook) hook->before(stream, "prefill_attn_kernel");
-        if (ema) prefill_attn_kernel<__half, true><<<grid, kAttnThreads, kAttnSmem, stream>>>(tmQ, tmK, tmV, p);
-        else prefill_attn_kernel<__half, false><<<grid, kAttnThreads, kAttnSmem, stream>>>(tmQ, tmK, tmV, p);
+        if (ema) {
+            prefill_attn_kernel<__half, true, false><<<grid, kAttnThreads, kAttnSmem, stream>>>(tmQ, tmK, tmV, p);
+            prefill_attn_kernel<__half, true, true><<<grid, kAttnThreads, kAttnSmem, stream>>>(tmQ, tmK, tmV, p);
+        } else {
+            prefill_attn_kernel<__half, false, false><<<grid, kAttnThreads, kAttnSmem, stream>>>(tmQ, tmK, tmV, p);
+            prefill_attn_kernel<__half, false, true><<<grid, kAttnThreads, kAttnSmem, stream>>>(tmQ, tmK, tmV, p);
+        }
+        if (p.nSplit > 1) prefill_combine_kernel<__half><<<(unsigned)((comb + 255) / 256), 256, 0, stream>>>(p);
         if (hook) hook->after(stream);
     }
     CKV_CUDA_CHECK(cudaGetLastError());
-    int launches = 2;
+    int launches = 3 + (p.nSplit > 1 ? 1 : 0);
     if (ema) {
         const long long n = (long long)d.B * d.KVH * (d.S + n_tokens);
         if (d.dtype == CKV_BF16) prefill_scores_kernel<__nv_bfloat16><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(p);

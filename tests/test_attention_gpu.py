@@ -232,7 +232,9 @@ def test_tuned_kernels_are_the_ones_that_run():
         cascade_attention(mk(8, 1), mk(2, 1), mk(2, 1), cache, 0, force_generic=True)
 
     assert profiling.time_dominant_kernel(chunk, 2)[2] == "prefill_attn_kernel"
-    assert profiling.last_launch_count() == 5       # prep, attention, scores, update walk, update finalize
+    # prep, attention phase A, attention phase B, scores, update walk, update finalize (this grid is too
+    # small for key splits, which would add the combine launch)
+    assert profiling.last_launch_count() == 6
     assert profiling.time_dominant_kernel(token, 2)[2] == "decode_stream_kernel"
     assert profiling.last_launch_count() == 3       # cos/sin image, stream, finish
     assert profiling.time_dominant_kernel(generic, 1)[2] == "attn_rows_kernel"
