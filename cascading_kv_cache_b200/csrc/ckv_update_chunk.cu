@@ -268,31 +268,55 @@ __global__ void __launch_bounds__(kThreads) update_chunk_kernel(ChunkParams p) {
     for (int i = n_stage - 1; i >= 0; --i) {
         const int *plan = plan_lane + 2 * sh.casc_off[i];
         const int n = sh.casc_cnt[i];
-        for (int idx = tid; idx < n * nchunk; idx += kThreads) {
-            const int e = idx / nchunk, c = idx % nchunk;
-            const int dst = plan[2 * e], id = plan[2 * e + 1];
-            const uint4 *sk, *sv;
-            if (id < u.K) {
-                sk = reinterpret_cast<const uint4 *>(u.key + b * u.ksb + h * u.ksh + (long long)id * u.kst);
-                sv = reinterpret_cast<const uint4 *>(u.val + b * u.ksb + h * u.ksh + (long long)id * u.kst);
-            } else {
-                sk = reinterpret_cast<const uint4 *>(ck + (long long)(id - u.K) * row);
-                sv = reinterpret_cast<const uint4 *>(cv + (long long)(id - u.K) * row);
-            }
-            reinterpret_cast<uint4 *>(ck + (long long)dst * row)[c] = sk[c];
-            reinterpret_cast<uint4 *>(cv + (long long)dst * row)[c] = sv[c];
-            if (c == 0) {
-                unsigned int bits;
-                long long o;
-                if (id < u.K) {
-                    bits = u.scr ? load_score_bits(u.scr + b * u.ssb + h * u.ssh + (long long)id * u.sst, u.esz) : 0u;
-                    o = seen + id + 1;
-                } else {
-                    bits = load_score_bits(cs + (long long)(id - u.K) * u.esz, u.esz);
-                    o = og[id - u.K];
+        // 16-byte pieces of the rows, kUnroll of them in flight per thread: with one CTA per lane the
+        // copy is bound by the latency of a dependent load-store pair, not by bandwidth
+        constexpr int kUnroll = 8;
+        const int total = n * nchunk;
+        for (int base = tid; base < total; base += kThreads * kUnroll) {
+            uint4 rk[kUnroll], rv[kUnroll];
+            int dsts[kUnroll], cs_[kUnroll];
+#pragma unroll
+            for (int r = 0; r < kUnroll; ++r) {
+                const int idx = base + r * kThreads;
+                dsts[r] = -1;
+                if (idx < total) {
+                    const int e = idx / nchunk, c = idx % nchunk;
+                    const int dst = plan[2 * e], id = plan[2 * e + 1];
+                    const uint4 *sk, *sv;
+                    if (id < u.K) {
+                        sk = reinterpret_cast<const uint4 *>(u.key + b * u.ksb + h * u.ksh + (long long)id * u.kst);
+                        sv = reinterpret_cast<const uint4 *>(u.val + b * u.ksb + h * u.ksh + (long long)id * u.kst);
+                    } else {
+                        sk = reinterpret_cast<const uint4 *>(ck + (long long)(id - u.K) * row);
+                        sv = reinterpret_cast<const uint4 *>(cv + (long long)(id - u.K) * row);
+                    }
+                    rk[r] = sk[c];
+                    rv[r] = sv[c];
+                    dsts[r] = dst;
+                    cs_[r] = c;
+                    if (c == 0) {
+                        unsigned int bits;
+                        long long o;
+                        if (id < u.K) {
+                            bits = u.scr ? load_score_bits(u.scr + b * u.ssb + h * u.ssh + (long long)id * u.sst, u.esz) : 0u;
+                            o = seen + id + 1;
+                        } else {
+                            bits = load_score_bits(cs + (long long)(id - u.K) * u.esz, u.esz);
+                            o = og[id - u.K];
+                        }
+                        // a slot is the destination of at most one move of a stage, and a stage's sources
+                        // lie in the chunk or in earlier cascades: nothing read in this stage is written in it
+                        store_score_bits(cs + (long long)dst * u.esz, bits, u.esz);
+                        og[dst] = o;
+                    }
                 }
-                store_score_bits(cs + (long long)dst * u.esz, bits, u.esz);
-                og[dst] = o;
+            }
+#pragma unroll
+            for (int r = 0; r < kUnroll; ++r) {
+                if (dsts[r] >= 0) {
+                    reinterpret_cast<uint4 *>(ck + (long long)dsts[r] * row)[cs_[r]] = rk[r];
+                    reinterpret_cast<uint4 *>(cv + (long long)dsts[r] * row)[cs_[r]] = rv[r];
+                }
             }
         }
         __syncthreads();
