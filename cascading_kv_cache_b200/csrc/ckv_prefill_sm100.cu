@@ -5,16 +5,17 @@
 //                            slots, the chunk itself) at its cache position into scratch, compacted
 //                            so that key row r of a lane is [sinks | cached | new][r]; copy the
 //                            values alongside.  (reference: cascade_attention.py:141-166, :284-291)
-//   2. prefill_attn_kernel   one CTA per (batch, KV head, pair of query heads, 128-query tile), two
-//                            phases over the key tiles:
-//                            A: S = Q K^T (tcgen05), running row max / sum;
+//   2. prefill_attn_kernel   one CTA per (batch, KV head, pair of query heads, 128-query tile, key
+//                            split); launched twice over the key tiles:
+//                            A: S = Q K^T (tcgen05), row max / sum of exp per key split -> scratch;
 //                            B: S^T = K Q^T, P^T = T(exp(S^T - max) / sum) exactly normalised,
 //                               out^T += V^T P^T (tcgen05, out^T in tensor memory), and the EMA
 //                               partial sum of every key over this query tile
 //                               (cascade_attention.py:293-323).
+//      prefill_combine_kernel sums the key splits' output partials (only when there are several).
 //   3. prefill_scores_kernel sums the partials over query tiles in a fixed order, reduces over the
 //                            GQA group, applies score = T(T(beta^K score) + ema) (:231-248, :329-330).
-//   4. the cache update of the chunk (ckv_update.cu).
+//   4. the cache update of the chunk (ckv_update_chunk.cu).
 //
 // Warp roles in prefill_attn_kernel (608 threads): warp 0 TMA producer, warp 1 Q K^T issuer and
 // tensor-memory owner, warps 2-9 softmax of the pair's first head, warps 10-17 of its second head (two
@@ -278,28 +279,13 @@ __device__ __forceinline__ float ex2f(float x) {
     return y;
 }
 
-// Shared-memory matrix descriptors (128-byte swizzle, rows of 128 bytes, 8-row groups of 1024 bytes).
-// K-major: the reduction dimension is contiguous inside the 128-byte row (Q, K, P tiles).
-__device__ __forceinline__ uint64_t desc_k_major(uint32_t saddr) {
-    uint64_t d = (uint64_t)((saddr & 0x3FFFFu) >> 4);
-    d |= (uint64_t)1 << 16;              // leading byte offset: unused for swizzled K-major
-    d |= (uint64_t)(1024 >> 4) << 32;    // stride byte offset between 8-row groups
-    d |= (uint64_t)1 << 46;              // descriptor version of this architecture
-    d |= (uint64_t)2 << 61;              // 128-byte swizzle
-    return d;
-}
-// MN-major: the N dimension (64 elements) is contiguous inside the row, rows step along K (V tile).
-__device__ __forceinline__ uint64_t desc_mn_major(uint32_t saddr, uint32_t n_atom_stride_bytes) {
-    uint64_t d = (uint64_t)((saddr & 0x3FFFFu) >> 4);
-    d |= (uint64_t)(n_atom_stride_bytes >> 4) << 16;
-    d |= (uint64_t)(1024 >> 4) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
-    return d;
-}
+// Shared-memory matrix descriptors (64 bits) for tiles of 128-byte rows in 8-row groups of 1024 bytes,
+// 128-byte swizzle:  bits 0-13 start address >> 4;  16-29 leading byte offset >> 4 (K-major, i.e. the
+// reduction dimension contiguous in the row: unused, 1;  MN-major: distance between the two 64-element
+// atoms of a row, one 16 KB sub-tile);  32-45 stride byte offset >> 4 (1024 bytes between 8-row
+// groups);  bit 46 descriptor version;  bits 61-63 swizzle mode (2 = 128 bytes).
 // The issuing thread's instruction stream is on the kernel's critical path, so descriptors are
-// assembled from a precomputed low word (start address >> 4 | leading offset << 16) plus a
-// compile-time offset, and a constant high word (stride offset, version, swizzle mode).
+// assembled from a precomputed low word plus a compile-time offset, and a constant high word.
 constexpr uint32_t kDescHi = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);
 __device__ __forceinline__ uint32_t desc_lo_k(uint32_t saddr) { return ((saddr & 0x3FFFFu) >> 4) | (1u << 16); }
 __device__ __forceinline__ uint32_t desc_lo_mn(uint32_t saddr) {
@@ -367,11 +353,6 @@ __device__ __forceinline__ void upk2(uint64_t v, float &lo, float &hi) { asm("mo
 __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
     uint64_t r;
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
-    return r;
-}
-__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
-    uint64_t r;
-    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
     return r;
 }
 __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
