@@ -140,3 +140,34 @@ def test_c3_chunked_prefill_full_size():
         for name in ("key_cache", "value_cache", "score_cache", "og_pos"):
             getattr(generic, name)[0].copy_(getattr(tuned, name)[0])
     _state_properties(tuned, w)
+
+
+def test_c1_fp32_stride_stream_in_full():
+    """The reference's own CPU-runnable configuration in full: fp32, B1 H32/KVH8 D128, 4 sinks, 4 x 512 slots,
+    stride rule without eager fill, 16384 tokens in chunks of 512 and then 64 single steps.  Outputs against
+    the oracle step by step; at the end slots, positions, counters and original positions bit for bit."""
+    from cascading_kv_cache_b200 import CascadingKVCache, cascade_attention
+    B, H, KVH, D, NS, W, C, theta = 1, 32, 8, 128, 4, 512, 4, 5e5
+    cache = CascadingKVCache(W, NS, B, KVH, D, W * C, device="cuda:0", dtype=torch.float32, layers=1,
+                             eager_fill=False, admission="stride")
+    ref = OracleCascadingKVCache(W, NS, B, KVH, D, W * C, dtype=torch.float32, layers=1, eager_fill=False)
+    g = torch.Generator().manual_seed(0)
+    worst = 0.0
+    for n in [512] * 32 + [1] * 64:
+        q = torch.randn(B, H, n, D, generator=g)
+        k = torch.randn(B, KVH, n, D, generator=g)
+        v = torch.randn(B, KVH, n, D, generator=g)
+        want = cascade_attention_step(q, k, v, ref, 0, theta, None, False, do_update=False)
+        ref.update(k, v, 0)
+        got = cascade_attention(q.cuda(), k.cuda(), v.cuda(), cache, 0, rope_theta=theta).cpu()
+        worst = max(worst, (got - want).abs().max().item())
+    assert worst <= 2e-4, worst
+    valid = ~ref.mask[0]
+    assert torch.equal(cache.mask[0].cpu(), ref.mask[0])
+    for name in ("pos", "og_pos"):
+        assert torch.equal(getattr(cache, name)[0].cpu()[valid], getattr(ref, name)[0][valid]), name
+    for name in ("key_cache", "value_cache"):
+        assert torch.equal(getattr(cache, name)[0].cpu()[valid], getattr(ref, name)[0][valid]), name
+    for name in ("stored_tokens", "start_indices", "sink_keys", "sink_values", "sink_pos"):
+        assert torch.equal(getattr(cache, name)[0].cpu(), getattr(ref, name)[0]), name
+    assert cache.seen_tokens_host(0) == 16384 + 64 and cache.kernel_status() == 0
