@@ -719,9 +719,11 @@ __global__ void __launch_bounds__(kFinishThreads) decode_finish_kernel(DecodePar
     }
     __syncthreads();
 
-    // 3. output rows (first block of the lane)
-    if (blockIdx.x == 0) {
-        for (int idx = tid; idx < p.G * 128; idx += kFinishThreads) {
+    // 3. output rows, shared out among the lane's blocks
+    {
+        const int n_out = p.G * 128, per_out = (n_out + gridDim.x - 1) / gridDim.x;
+        const int o_end = min(n_out, (int)(blockIdx.x + 1) * per_out);
+        for (int idx = blockIdx.x * per_out + tid; idx < o_end; idx += kFinishThreads) {
             const int gh = idx >> 7, d = idx & 127;
             float acc = __expf(s_snew[gh] - s_m[gh]) * Elem<T>::to_f(vrow[d]);
             for (int i = 0; i < n_parts; ++i) {
@@ -761,8 +763,9 @@ __global__ void __launch_bounds__(kFinishThreads) decode_finish_kernel(DecodePar
         }
     }
 
-    // 5. lane-invariant state after this token: lane 0's blocks rewrite positions / masks of their
-    //    slots from the advanced counters (nothing in this kernel reads them)
+    // 5. lane-invariant state after this token: positions / masks are rewritten from the advanced
+    //    counters, every block of the grid taking an equal share of the slots (nothing in this kernel
+    //    reads them)
     if (tid < p.C) {
         s_new_stored[tid] = p.stored_tokens[tid];
         s_new_start[tid] = p.start_indices[tid];
@@ -778,17 +781,18 @@ __global__ void __launch_bounds__(kFinishThreads) decode_finish_kernel(DecodePar
         s_new_total = total;
     }
     __syncthreads();
-    if (lane == 0) {
-        const int per_block = (p.S + p.finish_chunks - 1) / p.finish_chunks;
-        const int s_begin = blockIdx.x * per_block, s_end = min(p.S, s_begin + per_block);
+    {
+        const int n_blocks = gridDim.x * gridDim.y, me = blockIdx.y * gridDim.x + blockIdx.x;
+        const int per_block = (p.S + n_blocks - 1) / n_blocks;
+        const int s_begin = me * per_block, s_end = min(p.S, s_begin + per_block);
         const bool rewrite = sc.seen + 1 > p.NS;
         for (int t = s_begin + tid; t < s_end; t += kFinishThreads) {
             const int i = t / p.W, j = t % p.W;
-            const long long stored_i = s_new_stored[i];
+            const int stored_i = (int)s_new_stored[i];                  // counters are at most W
             if (j < stored_i) p.mask[t] = 0;
             const long long ub = s_new_total - (long long)i * p.W;
-            const long long seg = stored_i < p.W ? stored_i : p.W;
-            if (rewrite && ub > 0 && seg > 0) p.pos[t] = ((j + seg - s_new_start[i]) % seg) + ub - seg;
+            const int seg = stored_i < p.W ? stored_i : p.W;
+            if (rewrite && ub > 0 && seg > 0) p.pos[t] = (long long)((j + seg - (int)s_new_start[i]) % seg) + ub - seg;
         }
     }
 
