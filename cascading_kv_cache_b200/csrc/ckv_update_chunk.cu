@@ -26,11 +26,15 @@ namespace {
 constexpr int kChunkMax = 4096;      // tokens per launch (larger chunks are split by the launcher)
 constexpr int kThreads = 512;
 constexpr int kItemsPerThread = kChunkMax / kThreads;
+constexpr int kHdrInts = 2 * CKV_MAX_CASCADES + 1;
+constexpr int kSplitMovesFrom = 1024;   // chunks at least this long run their moves as one launch per cascade
+constexpr int kMoveBlocks = 32;         // CTAs per lane of such a launch
 
 struct ChunkParams {
     UpdateParams u;
     int *plan;            // [lanes][plan_stride][2]  (destination slot, item id)
     int plan_stride;
+    int *hdr;             // [lanes][kHdrInts]: moves of each cascade (offset, count) and the number of stages
     long long *pos, *sink_pos;
     long long *stored_tokens_w, *start_indices_w, *stored_sinks_w, *seen_w;
     uint8_t *mask, *sink_mask;
@@ -222,6 +226,70 @@ __device__ void load_counters(const UpdateParams &u, Shared &sh) {
     __syncthreads();
 }
 
+// The moves of one cascade of one lane: 16-byte pieces of the rows, kUnroll of them in flight per
+// thread (with few CTAs per lane the copy is bound by the latency of a dependent load-store pair).
+// `first` / `step` spread the pieces over the participating threads.
+__device__ __forceinline__ void execute_moves(const UpdateParams &u, int lane, const int *plan, int n, long long seen,
+                                              int first, int step) {
+    const int b = lane / u.KVH, h = lane % u.KVH;
+    const int nchunk = u.row_bytes / 16;
+    const long long row = u.row_bytes;
+    uint8_t *ck = u.cache_k + (long long)lane * u.S * row;
+    uint8_t *cv = u.cache_v + (long long)lane * u.S * row;
+    uint8_t *cs = u.cache_s + (long long)lane * u.S * u.esz;
+    long long *og = u.og_pos + (long long)lane * u.S;
+    constexpr int kUnroll = 8;
+    const int total = n * nchunk;
+    for (int base = first; base < total; base += step * kUnroll) {
+        uint4 rk[kUnroll], rv[kUnroll];
+        int dsts[kUnroll], cs_[kUnroll];
+#pragma unroll
+        for (int r = 0; r < kUnroll; ++r) {
+            const int idx = base + r * step;
+            dsts[r] = -1;
+            if (idx < total) {
+                const int e = idx / nchunk, c = idx % nchunk;
+                const int dst = plan[2 * e], id = plan[2 * e + 1];
+                const uint4 *sk, *sv;
+                if (id < u.K) {
+                    sk = reinterpret_cast<const uint4 *>(u.key + b * u.ksb + h * u.ksh + (long long)id * u.kst);
+                    sv = reinterpret_cast<const uint4 *>(u.val + b * u.ksb + h * u.ksh + (long long)id * u.kst);
+                } else {
+                    sk = reinterpret_cast<const uint4 *>(ck + (long long)(id - u.K) * row);
+                    sv = reinterpret_cast<const uint4 *>(cv + (long long)(id - u.K) * row);
+                }
+                rk[r] = sk[c];
+                rv[r] = sv[c];
+                dsts[r] = dst;
+                cs_[r] = c;
+                if (c == 0) {
+                    unsigned int bits;
+                    long long o;
+                    if (id < u.K) {
+                        bits = u.scr ? load_score_bits(u.scr + b * u.ssb + h * u.ssh + (long long)id * u.sst, u.esz) : 0u;
+                        o = seen + id + 1;
+                    } else {
+                        bits = load_score_bits(cs + (long long)(id - u.K) * u.esz, u.esz);
+                        o = og[id - u.K];
+                    }
+                    // a slot is the destination of at most one move of a stage, and a stage's sources
+                    // lie in the chunk or in earlier cascades: nothing read in this stage is written in it
+                    store_score_bits(cs + (long long)dst * u.esz, bits, u.esz);
+                    og[dst] = o;
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < kUnroll; ++r) {
+            if (dsts[r] >= 0) {
+                reinterpret_cast<uint4 *>(ck + (long long)dsts[r] * row)[cs_[r]] = rk[r];
+                reinterpret_cast<uint4 *>(cv + (long long)dsts[r] * row)[cs_[r]] = rv[r];
+            }
+        }
+    }
+}
+
+template <bool kFused>
 __global__ void __launch_bounds__(kThreads) update_chunk_kernel(ChunkParams p) {
     extern __shared__ uint8_t smem_raw[];
     Shared &sh = *reinterpret_cast<Shared *>(smem_raw);
@@ -259,68 +327,33 @@ __global__ void __launch_bounds__(kThreads) update_chunk_kernel(ChunkParams p) {
     __threadfence_block();
     __syncthreads();
 
-    // execute the moves from the last cascade to the first: sources are chunk rows or entries of
-    // EARLIER cascades, which are still untouched when they are read
-    uint8_t *ck = u.cache_k + (long long)lane * u.S * row;
-    uint8_t *cv = u.cache_v + (long long)lane * u.S * row;
-    uint8_t *cs = u.cache_s + (long long)lane * u.S * u.esz;
-    long long *og = u.og_pos + (long long)lane * u.S;
-    for (int i = n_stage - 1; i >= 0; --i) {
-        const int *plan = plan_lane + 2 * sh.casc_off[i];
-        const int n = sh.casc_cnt[i];
-        // 16-byte pieces of the rows, kUnroll of them in flight per thread: with one CTA per lane the
-        // copy is bound by the latency of a dependent load-store pair, not by bandwidth
-        constexpr int kUnroll = 8;
-        const int total = n * nchunk;
-        for (int base = tid; base < total; base += kThreads * kUnroll) {
-            uint4 rk[kUnroll], rv[kUnroll];
-            int dsts[kUnroll], cs_[kUnroll];
-#pragma unroll
-            for (int r = 0; r < kUnroll; ++r) {
-                const int idx = base + r * kThreads;
-                dsts[r] = -1;
-                if (idx < total) {
-                    const int e = idx / nchunk, c = idx % nchunk;
-                    const int dst = plan[2 * e], id = plan[2 * e + 1];
-                    const uint4 *sk, *sv;
-                    if (id < u.K) {
-                        sk = reinterpret_cast<const uint4 *>(u.key + b * u.ksb + h * u.ksh + (long long)id * u.kst);
-                        sv = reinterpret_cast<const uint4 *>(u.val + b * u.ksb + h * u.ksh + (long long)id * u.kst);
-                    } else {
-                        sk = reinterpret_cast<const uint4 *>(ck + (long long)(id - u.K) * row);
-                        sv = reinterpret_cast<const uint4 *>(cv + (long long)(id - u.K) * row);
-                    }
-                    rk[r] = sk[c];
-                    rv[r] = sv[c];
-                    dsts[r] = dst;
-                    cs_[r] = c;
-                    if (c == 0) {
-                        unsigned int bits;
-                        long long o;
-                        if (id < u.K) {
-                            bits = u.scr ? load_score_bits(u.scr + b * u.ssb + h * u.ssh + (long long)id * u.sst, u.esz) : 0u;
-                            o = seen + id + 1;
-                        } else {
-                            bits = load_score_bits(cs + (long long)(id - u.K) * u.esz, u.esz);
-                            o = og[id - u.K];
-                        }
-                        // a slot is the destination of at most one move of a stage, and a stage's sources
-                        // lie in the chunk or in earlier cascades: nothing read in this stage is written in it
-                        store_score_bits(cs + (long long)dst * u.esz, bits, u.esz);
-                        og[dst] = o;
-                    }
-                }
-            }
-#pragma unroll
-            for (int r = 0; r < kUnroll; ++r) {
-                if (dsts[r] >= 0) {
-                    reinterpret_cast<uint4 *>(ck + (long long)dsts[r] * row)[cs_[r]] = rk[r];
-                    reinterpret_cast<uint4 *>(cv + (long long)dsts[r] * row)[cs_[r]] = rv[r];
-                }
-            }
+    if constexpr (!kFused) {
+        // long chunks: the moves run as one launch per cascade with many CTAs per lane
+        int *hdr = p.hdr + (long long)lane * kHdrInts;
+        if (tid < CKV_MAX_CASCADES) {
+            hdr[2 * tid] = tid < n_stage ? sh.casc_off[tid] : 0;
+            hdr[2 * tid + 1] = tid < n_stage ? sh.casc_cnt[tid] : 0;
         }
-        __syncthreads();
+        if (tid == 0) hdr[2 * CKV_MAX_CASCADES] = n_stage;
+    } else {
+        // execute the moves from the last cascade to the first: sources are chunk rows or entries of
+        // EARLIER cascades, which are still untouched when they are read
+        for (int i = n_stage - 1; i >= 0; --i) {
+            execute_moves(u, lane, plan_lane + 2 * sh.casc_off[i], sh.casc_cnt[i], seen, tid, kThreads);
+            __syncthreads();
+        }
     }
+}
+
+// Moves of cascade `stage` for every lane; launched from the last cascade to the first, so that the
+// kernel boundary orders a cascade's reads of the previous cascade's entries before their rewrite.
+__global__ void __launch_bounds__(kThreads) update_chunk_move_kernel(ChunkParams p, int stage) {
+    const int lane = blockIdx.y;
+    const int *hdr = p.hdr + (long long)lane * kHdrInts;
+    if (stage >= hdr[2 * CKV_MAX_CASCADES]) return;
+    const int *plan = p.plan + (long long)lane * p.plan_stride * 2 + 2 * hdr[2 * stage];
+    execute_moves(p.u, lane, plan, hdr[2 * stage + 1], *p.u.seen, blockIdx.x * kThreads + threadIdx.x,
+                  gridDim.x * kThreads);
 }
 
 // Advance the lane-invariant counters with the same stages (no data), then rewrite positions and
@@ -385,7 +418,8 @@ int plan_stride_for(const Dims &d, int k) {
 
 size_t update_chunk_workspace_bytes(const Dims &d, int n_tokens) {
     const int k = n_tokens < kChunkMax ? n_tokens : kChunkMax;
-    return up256c((size_t)d.B * d.KVH * plan_stride_for(d, k) * 2 * sizeof(int));
+    return up256c((size_t)d.B * d.KVH * plan_stride_for(d, k) * 2 * sizeof(int)) +
+           up256c((size_t)d.B * d.KVH * kHdrInts * sizeof(int));
 }
 
 int launch_update_chunk(const Dims &d, const ckv_layer_state *st, const void *key, const void *value, int64_t ksb,
@@ -401,7 +435,9 @@ int launch_update_chunk(const Dims &d, const ckv_layer_state *st, const void *ke
                     update_chunk_workspace_bytes(d, n_tokens));
     static bool attr_set = false;
     if (!attr_set) {
-        CKV_CUDA_CHECK(cudaFuncSetAttribute(update_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        CKV_CUDA_CHECK(cudaFuncSetAttribute(update_chunk_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            (int)sizeof(Shared)));
+        CKV_CUDA_CHECK(cudaFuncSetAttribute(update_chunk_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             (int)sizeof(Shared)));
         CKV_CUDA_CHECK(cudaFuncSetAttribute(update_chunk_finalize_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             (int)sizeof(Shared)));
@@ -430,15 +466,24 @@ int launch_update_chunk(const Dims &d, const ckv_layer_state *st, const void *ke
         u.row_bytes = row_bytes; u.esz = d.esz; u.dtype = d.dtype; u.eager_fill = d.eager_fill;
         p.plan = (int *)workspace;
         p.plan_stride = plan_stride_for(d, k);
+        p.hdr = (int *)((uint8_t *)workspace + up256c((size_t)d.B * d.KVH * plan_stride_for(d, n_tokens < kChunkMax ? n_tokens : kChunkMax) * 2 * sizeof(int)));
         p.pos = (long long *)st->pos; p.sink_pos = (long long *)st->sink_pos;
         p.stored_tokens_w = (long long *)st->stored_tokens; p.start_indices_w = (long long *)st->start_indices;
         p.stored_sinks_w = (long long *)st->stored_sinks; p.seen_w = (long long *)st->seen_tokens;
         p.mask = st->mask; p.sink_mask = st->sink_mask;
-        update_chunk_kernel<<<d.B * d.KVH, kThreads, sizeof(Shared), stream>>>(p);
+        if (k >= kSplitMovesFrom) {
+            update_chunk_kernel<false><<<d.B * d.KVH, kThreads, sizeof(Shared), stream>>>(p);
+            for (int i = d.C - 1; i >= 0; --i)
+                update_chunk_move_kernel<<<dim3(kMoveBlocks, d.B * d.KVH), kThreads, 0, stream>>>(p, i);
+            launches += 1 + d.C;
+        } else {
+            update_chunk_kernel<true><<<d.B * d.KVH, kThreads, sizeof(Shared), stream>>>(p);
+            launches += 1;
+        }
         CKV_CUDA_CHECK(cudaGetLastError());
         update_chunk_finalize_kernel<<<1, kThreads, sizeof(Shared), stream>>>(p);
         CKV_CUDA_CHECK(cudaGetLastError());
-        launches += 2;
+        launches += 1;
     }
     note_launches(launches);
     return CKV_OK;
