@@ -48,7 +48,7 @@ constexpr int kOffW = kOffBar + 256;          // per-query constants (also the s
 constexpr int kAttnSmem = kOffW + 2048;       // 231680 of the 232448 bytes a block may have
 constexpr int kAttnThreads = 608;             // TMA warp, Q K^T warp, 2 x 8 softmax warps, P V warp
 constexpr int kPvWarp = 18;
-constexpr unsigned kSpin = 1u << 22;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // a wait that lasts two seconds has failed
 constexpr int kTmemCols = 512;
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -191,22 +191,35 @@ __device__ __forceinline__ void bar_arrive(uint64_t *bar) {
 __device__ __forceinline__ void bar_expect_tx(uint64_t *bar, unsigned bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s_u32(bar)), "r"(bytes) : "memory");
 }
+// One blocking test: the thread is suspended by the hardware until the phase completes or the time hint
+// (nanoseconds; the hardware may cut it short) runs out.  A waiting thread thus issues a handful of
+// instructions per hint period instead of spinning in the schedulers that the softmax warps need.
+constexpr unsigned kSuspendHintNs = 20000;
 __device__ __forceinline__ bool bar_try(uint64_t *bar, unsigned parity) {
     unsigned ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(s_u32(bar)), "r"(parity) : "memory");
+        : "=r"(ok) : "r"(s_u32(bar)), "r"(parity), "r"(kSuspendHintNs) : "memory");
     return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
 }
 // Bounded wait.  On a time-out the status word becomes 2 | (source line of the wait << 8) -- the first
 // wait to give up wins -- and every other wait of the grid returns false soon after.
 __device__ __forceinline__ bool bar_wait_at(uint64_t *bar, unsigned parity, int *status, int line) {
-    for (unsigned n = 0; n < kSpin; ++n) {
+    if (bar_try(bar, parity)) return true;
+    const unsigned long long t_start = global_ns();
+    for (unsigned n = 1;; ++n) {
         if (bar_try(bar, parity)) return true;
-        if (n > 4096) __nanosleep(64);
-        if ((n & 1023) == 1023 && *((volatile int *)status) != 0) return false;
+        if ((n & 15) == 15) {
+            if (*((volatile int *)status) != 0) return false;
+            if (global_ns() - t_start > kWaitLimitNs) break;
+        }
     }
     atomicCAS(status, 0, 2 | (line << 8));
     return false;
