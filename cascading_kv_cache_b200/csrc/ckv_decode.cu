@@ -638,7 +638,7 @@ __device__ __forceinline__ void ema_pass_vec(const DecodeParams &p, const Schedu
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kFinishThreads) decode_finish_kernel(DecodeParams p) {
+__global__ void __launch_bounds__(kFinishThreads, 3) decode_finish_kernel(DecodeParams p) {
     __shared__ float s_m[kMaxG], s_linv[kMaxG], s_snew[kMaxG], s_pnew[kMaxG];
     __shared__ long long s_stored[CKV_MAX_CASCADES], s_start[CKV_MAX_CASCADES], s_every[CKV_MAX_CASCADES];
     __shared__ long long s_new_stored[CKV_MAX_CASCADES], s_new_start[CKV_MAX_CASCADES];
@@ -979,7 +979,7 @@ int launch_decode_tuned(const Dims &d, const ckv_layer_state *st, const void *q,
     p.stream_grid = sm_count();
     int chunks = 1;
     if (ema) {
-        chunks = (int)((4 * (uint64_t)sm_count()) / lanes);  // one wave of blocks
+        chunks = (int)((3 * (uint64_t)sm_count()) / lanes);  // one wave: the kernel is built for three blocks per SM
         chunks = chunks < 1 ? 1 : (chunks > 64 ? 64 : chunks);
     }
     p.finish_chunks = chunks;
