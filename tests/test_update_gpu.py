@@ -141,3 +141,37 @@ def test_update_rejects_bad_shapes():
     # empty chunk is a no-op
     cache.update(torch.zeros(1, 2, 0, 8).cuda(), torch.zeros(1, 2, 0, 8).cuda(), 0)
     assert cache.seen_tokens_host(0) == 0
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_random_configurations_and_ragged_chunks(seed):
+    """Randomly drawn window / cascade / sink counts, cascade functions, dtypes and chunk lengths (from one
+    token to several thousand, so that the fused, the per-cascade and the split launches all run), EMA scores
+    with frequent ties: the whole state bit for bit against the oracle after every call."""
+    rng = np.random.default_rng(1000 + seed)
+    W = int(rng.choice([4, 8, 16, 32, 64, 128]))
+    C = int(rng.integers(1, 7))
+    NS = int(rng.integers(0, 7))
+    B, H = int(rng.integers(1, 3)), int(rng.integers(1, 4))
+    D = int(rng.choice([8, 32, 128]))
+    dtype = [torch.float32, torch.float16, torch.bfloat16][int(rng.integers(0, 3))]
+    eager_fill = bool(rng.integers(0, 2))
+    func = str(rng.choice(["pow2", "pow2-1", "pow2-1-4", "pow2-2-4", "pow2-3-4", "1-then-2", "pow3", "pow4", "iplus1"]))
+    rule = "ema" if seed % 2 else "stride"
+    g = torch.Generator().manual_seed(seed)
+    cache, ref = make_pair(W, C, NS, B, H, D, dtype, eager_fill, func)
+    total = 0
+    while total < 6000:
+        n = int(rng.choice([1, 2, int(rng.integers(3, 64)), int(rng.integers(64, 1024)), int(rng.integers(1024, 4600))]))
+        k = torch.randn(B, H, n, D, generator=g).to(dtype)
+        v = torch.randn(B, H, n, D, generator=g).to(dtype)
+        s = None
+        if rule == "ema":
+            s = (torch.randint(0, 5, (B, H, n), generator=g).float() / 8).to(dtype)
+            bump = (torch.randint(0, 3, (B, H, W * C), generator=g).float() / 8).to(dtype)
+            ref.score_cache[0] = (ref.score_cache[0] + bump).to(dtype)
+            cache.score_cache[0] = (cache.score_cache[0] + bump.cuda()).to(dtype)
+        cache.update(k.cuda(), v.cuda(), 0, score_states=None if s is None else s.cuda())
+        ref.update(k, v, 0, score_states=s)
+        total += n
+        assert_same_state(cache, ref)
