@@ -77,6 +77,31 @@ STREAMS = [
 ]
 
 
+def _random_stream_specs(n):
+    """Seeded random configurations of the tuned path (16-bit, head_dim 128, at least one sink)."""
+    rng = np.random.default_rng(7)
+    out = []
+    for _ in range(n):
+        KVH = int(rng.integers(1, 4))
+        G = int(rng.integers(1, 9))
+        W = int(rng.choice([32, 64, 128, 256]))
+        C = int(rng.integers(1, 5))
+        out.append((int(rng.integers(1, 3)), KVH * G, KVH, 128, int(rng.integers(1, 70)), W, C,
+                    int(rng.integers(2, 400)), int(rng.integers(3, 8)), int(rng.integers(1, 4)),
+                    [torch.bfloat16, torch.float16][int(rng.integers(0, 2))], str(rng.choice(["ema", "stride"])),
+                    str(rng.choice(["mean", "max", "median"])), False, bool(rng.integers(0, 2)),
+                    float(rng.choice([0.99, 0.999, 0.9999])), float(rng.choice([1e4, 5e5, 1e6]))))
+    return out
+
+
+_ids = lambda s: f"B{s[0]}H{s[1]}kv{s[2]}D{s[3]}NS{s[4]}W{s[5]}C{s[6]}k{s[7]}-{str(s[10])[6:]}-{s[11]}-{s[12]}"
+
+
+@pytest.mark.parametrize("spec", _random_stream_specs(10), ids=_ids)
+def test_random_streams_on_the_tuned_path(spec):
+    test_streams_against_oracle(spec, False)
+
+
 @pytest.mark.parametrize("spec", STREAMS, ids=lambda s: f"B{s[0]}H{s[1]}kv{s[2]}D{s[3]}-{str(s[10])[6:]}-{s[11]}-{s[12]}")
 @pytest.mark.parametrize("force_generic", [True, False], ids=["generic", "tuned"])
 def test_streams_against_oracle(spec, force_generic):
