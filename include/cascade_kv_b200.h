@@ -211,7 +211,9 @@ int ckv_profile_read(double *total_ms /* host */, int32_t *launches /* host */, 
 /*
  * Copy the status word of a ckv_attention workspace to the host (synchronises).  0 = no kernel of
  * the last call gave up on a bounded wait; non-zero = a pipeline wait ran out and the results of
- * that call are invalid.  (No counterpart in the reference: its kernels have no waits.)
+ * that call are invalid: low byte 1 (decode kernels) or 2 (prefill kernels, bits 8 and up then hold
+ * the source line of the wait that gave up), 3 = the prefill kernel found its shared-memory window
+ * misaligned.  (No counterpart in the reference: its kernels have no waits.)
  */
 int ckv_read_status(const void *workspace, int32_t *status /* host */);
 
