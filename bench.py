@@ -58,9 +58,10 @@ class ClockSampler:
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
-    # NVML clocks-event-reason bits, in the order of `NAMES`
-    BITS = (0x8, 0x40, 0x20, 0x4)
-    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+    # NVML clocks-event-reason bits, in the order of `NAMES` (the first four are what nvidia-smi is asked for)
+    BITS = (0x8, 0x40, 0x20, 0x4, 0x2, 0x10, 0x80, 0x100)
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap", "applications_clocks_setting",
+             "sync_boost", "hw_power_brake_slowdown", "display_clock_setting")
 
     def __init__(self, gpu_index):
         self.gpu_index = gpu_index
@@ -98,7 +99,8 @@ class ClockSampler:
                               "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5)
         parts = [p.strip() for p in out.stdout.strip().split(",")]
         if len(parts) >= 6:
-            self.samples.append((float(parts[0]), float(parts[1]), [x.lower().startswith("active") for x in parts[2:6]]))
+            self.samples.append((float(parts[0]), float(parts[1]),
+                                 [x.lower().startswith("active") for x in parts[2:6]] + [False] * 4))
 
     def _run(self):
         while not self._stop.is_set():
