@@ -65,7 +65,8 @@ class ClockSampler:
 
     def __init__(self, gpu_index):
         self.gpu_index = gpu_index
-        self.samples = []          # (sm_mhz, max_mhz, [bool] * 4)
+        self.samples = []          # (sm_mhz, max_mhz, [bool per reason])
+        self.power = []            # watts
         self.source = "nvidia-smi"
         self._stop = threading.Event()
         self._thread = None
@@ -93,6 +94,10 @@ class ClockSampler:
         except Exception:
             mask = n.nvmlDeviceGetCurrentClocksThrottleReasons(self._handle)
         self.samples.append((float(sm), float(mx), [bool(mask & b) for b in self.BITS]))
+        try:
+            self.power.append(n.nvmlDeviceGetPowerUsage(self._handle) / 1000.0)
+        except Exception:
+            pass
 
     def _sample_smi(self):
         out = subprocess.run(["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.FIELDS}",
@@ -127,8 +132,11 @@ class ClockSampler:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
         sm = sorted(s[0] for s in self.samples)
         reasons = [n for i, n in enumerate(self.NAMES) if any(s[2][i] for s in self.samples)]
-        return {"sm_mhz": sm[len(sm) // 2], "sm_min_mhz": sm[0], "sm_max_mhz": self.samples[0][1], "reasons": reasons,
-                "samples": len(sm), "source": self.source}
+        out = {"sm_mhz": sm[len(sm) // 2], "sm_min_mhz": sm[0], "sm_max_mhz": self.samples[0][1], "reasons": reasons,
+               "samples": len(sm), "source": self.source}
+        if self.power:
+            out["power_w"] = sorted(self.power)[len(self.power) // 2]
+        return out
 
 
 def algorithmic_bytes(w):
