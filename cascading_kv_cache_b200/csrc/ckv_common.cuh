@@ -137,4 +137,14 @@ int launch_prefill_tuned(const Dims &d, const ckv_layer_state *st, const void *q
                          const void *ema_w_new, void *out, int64_t osb, int64_t osh, int64_t ost, void *workspace,
                          size_t workspace_bytes, int flags, cudaStream_t stream, ProfileHook *hook);
 
+// Kernel attributes (opt-in shared memory sizes) belong to a device's context: a process that drives
+// several GPUs has to set them once on each.  Returns true the first time it sees the current device.
+inline bool first_use_on_this_device(bool (&seen)[64]) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return true;
+    if (seen[dev]) return false;
+    seen[dev] = true;
+    return true;
+}
+
 }  // namespace ckv

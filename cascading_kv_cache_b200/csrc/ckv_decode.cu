@@ -931,8 +931,8 @@ int launch_decode_tuned(const Dims &d, const ckv_layer_state *st, const void *q,
          (uintptr_t)st->sink_values) % 16 != 0)
         return fail(CKV_E_ARG, "cache tensors must be 16-byte aligned");
 
-    static bool attr_set = false;
-    if (!attr_set) {
+    static bool attr_set[64] = {};
+    if (first_use_on_this_device(attr_set)) {
         CKV_CUDA_CHECK(cudaFuncSetAttribute(decode_stream_kernel<__nv_bfloat16, 1>,
                                             cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmem));
         CKV_CUDA_CHECK(cudaFuncSetAttribute(decode_stream_kernel<__nv_bfloat16, 2>,
@@ -941,7 +941,6 @@ int launch_decode_tuned(const Dims &d, const ckv_layer_state *st, const void *q,
                                             cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmem));
         CKV_CUDA_CHECK(cudaFuncSetAttribute(decode_stream_kernel<__half, 2>,
                                             cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmem));
-        attr_set = true;
     }
     const uint64_t lanes = (uint64_t)d.B * d.KVH;
     CUtensorMap tmK, tmV, tmSK, tmSV, tmR;

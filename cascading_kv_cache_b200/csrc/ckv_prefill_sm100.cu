@@ -1130,8 +1130,8 @@ int launch_prefill_tuned(const Dims &d, const ckv_layer_state *st, const void *q
     for (int64_t sv : strides) aligned = aligned && (sv * 2) % 16 == 0;
     if (!aligned) return fail(CKV_E_ARG, "q/key/value/out rows must be 16-byte aligned");
 
-    static bool attr_set = false;
-    if (!attr_set) {
+    static bool attr_set[64] = {};
+    if (first_use_on_this_device(attr_set)) {
         const void *kernels[] = {
             (const void *)prefill_attn_kernel<__nv_bfloat16, true, false>, (const void *)prefill_attn_kernel<__nv_bfloat16, true, true>,
             (const void *)prefill_attn_kernel<__nv_bfloat16, false, false>, (const void *)prefill_attn_kernel<__nv_bfloat16, false, true>,
@@ -1139,7 +1139,6 @@ int launch_prefill_tuned(const Dims &d, const ckv_layer_state *st, const void *q
             (const void *)prefill_attn_kernel<__half, false, false>, (const void *)prefill_attn_kernel<__half, false, true>};
         for (const void *k : kernels)
             CKV_CUDA_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));
-        attr_set = true;
     }
     uint8_t *ws = (uint8_t *)workspace;
     PrefillParams p;

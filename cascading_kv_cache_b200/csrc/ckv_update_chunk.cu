@@ -433,15 +433,14 @@ int launch_update_chunk(const Dims &d, const ckv_layer_state *st, const void *ke
     if (!workspace || workspace_bytes < update_chunk_workspace_bytes(d, n_tokens))
         return fail(CKV_E_WORKSPACE, "update workspace of %zu bytes, need %zu", workspace_bytes,
                     update_chunk_workspace_bytes(d, n_tokens));
-    static bool attr_set = false;
-    if (!attr_set) {
+    static bool attr_set[64] = {};
+    if (first_use_on_this_device(attr_set)) {
         CKV_CUDA_CHECK(cudaFuncSetAttribute(update_chunk_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             (int)sizeof(Shared)));
         CKV_CUDA_CHECK(cudaFuncSetAttribute(update_chunk_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             (int)sizeof(Shared)));
         CKV_CUDA_CHECK(cudaFuncSetAttribute(update_chunk_finalize_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             (int)sizeof(Shared)));
-        attr_set = true;
     }
     int launches = 0;
     for (int j0 = 0; j0 < n_tokens; j0 += kChunkMax) {
