@@ -786,22 +786,27 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             float acc = 0.f;
             uint64_t acc2[2] = {0ull, 0ull};
             bool p_rdy = jb == 0;
-            // The tile is taken in two chunks of 32 queries: load, compute, store.  Few values are live at
-            // a time, which leaves the compiler registers to overlap the dependent chains of many elements.
+            // The whole tile is taken out of tensor memory at once, rounded to T and packed two logits to a
+            // register by the conversion instruction (32 registers for 64 logits): the accumulator is
+            // released at the very start of the tile's arithmetic, so the next tile's logits are ready well
+            // before they are needed.  The arithmetic then runs in two chunks of 32 queries (compute,
+            // store), which keeps few values live and lets the dependent chains of many elements overlap.
+            uint32_t sp[2][16];
 #pragma unroll
             for (int ch = 0; ch < 2; ++ch) {
                 uint32_t v[32];
                 tc_ld32(tms + 32 * ch, v);
                 tc_ld_wait();
-                if (ch == 1) {
-                    // the accumulator can be overwritten as soon as it is in registers
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane_id == 0) bar_arrive(&s_free[grp]);
-                } else if (!p_rdy) {
-                    // asked now, needed after the arithmetic: has the P V product of the previous tile read P^T?
-                    p_rdy = bar_probe(&p_free[grp], (jb - 1) & 1);
-                }
+#pragma unroll
+                for (int i = 0; i < 16; ++i) sp[ch][i] = P2<T>::pack(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane_id == 0) bar_arrive(&s_free[grp]);
+            // asked now, needed after the arithmetic: has the P V product of the previous tile read P^T?
+            if (!p_rdy) p_rdy = bar_probe(&p_free[grp], (jb - 1) & 1);
+#pragma unroll
+            for (int ch = 0; ch < 2; ++ch) {
                 uint32_t pk[16];
                 const int qbase = 64 * half + 32 * ch;
                 if (fast_tile) {
@@ -809,8 +814,10 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     for (int c4 = 0; c4 < 32; c4 += 4) {
                         // per-query constants arrive as two packed pairs per 16-byte load
                         const ulonglong2 cq = *reinterpret_cast<const ulonglong2 *>(cq_h + qbase + c4);
-                        const uint64_t sa = round2_to_t<T>(pk2(__uint_as_float(v[c4]), __uint_as_float(v[c4 + 1])));
-                        const uint64_t sb = round2_to_t<T>(pk2(__uint_as_float(v[c4 + 2]), __uint_as_float(v[c4 + 3])));
+                        float s0, s1, s2, s3;
+                        P2<T>::unpack(sp[ch][c4 >> 1], s0, s1);
+                        P2<T>::unpack(sp[ch][(c4 >> 1) + 1], s2, s3);
+                        const uint64_t sa = pk2(s0, s1), sb = pk2(s2, s3);
                         float a0, a1, b0, b1;
                         upk2(fma2(sa, l2e2, cq.x), a0, a1);
                         upk2(fma2(sb, l2e2, cq.y), b0, b1);
@@ -836,10 +843,12 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                         const float4 wq4 = *reinterpret_cast<const float4 *>(wq_h + qbase + c4);
                         const float cqv[4] = {cq4.x, cq4.y, cq4.z, cq4.w};
                         const float wqv[4] = {wq4.x, wq4.y, wq4.z, wq4.w};
-                        float pr[4];
+                        float pr[4], sr[4];
+                        P2<T>::unpack(sp[ch][c4 >> 1], sr[0], sr[1]);
+                        P2<T>::unpack(sp[ch][(c4 >> 1) + 1], sr[2], sr[3]);
 #pragma unroll
                         for (int uu = 0; uu < 4; ++uu) {
-                            const float sv = round_to_t<T>(__uint_as_float(v[c4 + uu]));
+                            const float sv = sr[uu];
                             float pv = ex2f(fmaf(sv, kLog2e, cqv[uu]));
                             if (!full_tile && (qbase + c4 + uu) < q_min) pv = 0.f;
                             pr[uu] = round_prob_to_t<T>(pv);
