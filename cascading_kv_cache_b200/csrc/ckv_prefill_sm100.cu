@@ -448,7 +448,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     uint64_t *q_full = bars + 0, *ra_full = bars + 1, *ra_empty = bars + 6, *rb_full = bars + 11, *rb_empty = bars + 15;
     static_assert(kRingA <= 5 && kRingB <= 4, "barrier table layout");
     uint64_t *s_full = bars + 19, *s_free = bars + 21, *p_full = bars + 23, *p_free = bars + 25;
-    uint64_t *o_full = bars + 27, *qt_ready = bars + 28, *a_done = bars + 29;
+    uint64_t *o_full = bars + 27, *qt_ready = bars + 28;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 30);
     float *c_q = reinterpret_cast<float *>(smem + kOffW);       // [2 heads][128] softmax shift of each query
     float *w_q = c_q + 256;                                     // [2 heads][128] EMA weight of each query (one copy per group)
@@ -488,7 +488,6 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
         bar_init(o_full, 1);
         bar_init(qt_ready, 16);
-        bar_init(a_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
