@@ -137,9 +137,10 @@ def test_streams_against_oracle(spec, force_generic):
         if teacher:
             valid = ~ref.mask[0]
             assert torch.equal(cache.pos[0].cpu()[valid], ref.pos[0][valid])
-            step_agree.append((cache.og_pos[0].cpu()[valid] == ref.og_pos[0][valid]).float().mean().item())
-            same = (cache.og_pos[0].cpu() == ref.og_pos[0]) & valid
-            score_bits.append((cache.score_cache[0].cpu()[same] == ref.score_cache[0][same]).float().mean().item())
+            if bool(valid.any()):      # a first chunk shorter than the sink count leaves the cascades empty
+                step_agree.append((cache.og_pos[0].cpu()[valid] == ref.og_pos[0][valid]).float().mean().item())
+                same = (cache.og_pos[0].cpu() == ref.og_pos[0]) & valid
+                score_bits.append((cache.score_cache[0].cpu()[same] == ref.score_cache[0][same]).float().mean().item())
             copy_state_to_gpu(ref, cache)
     assert cache.kernel_status() == 0
     valid = ~ref.mask[0]
@@ -150,8 +151,9 @@ def test_streams_against_oracle(spec, force_generic):
     if teacher:
         # per step, the tokens admitted / kept agree on (almost) every slot, and the EMA scores of the
         # slots that hold the same token are the same 16 bits (what is left differs by one rounding)
-        assert min(step_agree) >= 0.998 and sum(step_agree) / len(step_agree) >= 0.9995, step_agree
-        assert min(score_bits) >= 0.99, score_bits
+        if step_agree:
+            assert min(step_agree) >= 0.998 and sum(step_agree) / len(step_agree) >= 0.9995, step_agree
+            assert min(score_bits) >= 0.99, score_bits
         return
     agree = (cache.og_pos[0].cpu()[valid] == ref.og_pos[0][valid]).float().mean().item()
     if rule == "stride":
