@@ -22,7 +22,7 @@ CKV_ATTN_FORCE_GENERIC = 2
 DTYPE_CODE = {torch.float32: CKV_F32, torch.float16: CKV_F16, torch.bfloat16: CKV_BF16}
 
 EXPORTS = ("ckv_abi_version", "ckv_last_error", "ckv_cascade_update", "ckv_update_workspace_bytes",
-           "ckv_attention_workspace_bytes",
+           "ckv_attention_workspace_bytes", "ckv_attention_workspace_bytes_for",
            "ckv_attention", "ckv_last_launch_count", "ckv_profile_enable", "ckv_profile_read", "ckv_read_status",
            "ckv_static_scratch_bytes", "ckv_attention_static")
 
@@ -64,6 +64,8 @@ def load():
     lib.ckv_update_workspace_bytes.argtypes = [cfgp, i32]
     lib.ckv_attention_workspace_bytes.restype = sz
     lib.ckv_attention_workspace_bytes.argtypes = [cfgp, i32]
+    lib.ckv_attention_workspace_bytes_for.restype = sz
+    lib.ckv_attention_workspace_bytes_for.argtypes = [cfgp, i32, i32]
     lib.ckv_attention.restype = ctypes.c_int
     lib.ckv_attention.argtypes = [cfgp, stp, vp, i64, i64, i64, vp, vp, i64, i64, i64, i32, vp, i64, vp, vp,
                                   vp, i64, i64, i64, vp, sz, i32, vp]

@@ -71,7 +71,9 @@ def cascade_attention(
     lib = cache._lib
     cfg = cache.ckv_config(layer_idx, q_heads=H, homogeneous_heads=homogeneous_heads, head_reduction=head_reduction)
     st = cache.ckv_state(layer_idx)
-    nbytes = lib.ckv_attention_workspace_bytes(ctypes.byref(cfg), K)
+    flags = (_lib.CKV_ATTN_UPDATE if update else 0) | (_lib.CKV_ATTN_FORCE_GENERIC if force_generic else 0)
+    # sized for the path this call takes: the generic path's logit rows are only allocated once it is asked for
+    nbytes = lib.ckv_attention_workspace_bytes_for(ctypes.byref(cfg), K, flags)
     cache.workspace(nbytes)
     ws_ptr = cache.workspace_ptr()
     rope = cache.rope_table(rope_theta, cache.num_sink_tokens + cache.max_seq_len[layer_idx] + K + 1)
@@ -80,7 +82,6 @@ def cascade_attention(
         w_cache_ptr, w_new_ptr = w_cache.data_ptr(), w_new.data_ptr()
     else:
         w_cache_ptr, w_new_ptr = None, None
-    flags = (_lib.CKV_ATTN_UPDATE if update else 0) | (_lib.CKV_ATTN_FORCE_GENERIC if force_generic else 0)
     rc = lib.ckv_attention(
         ctypes.byref(cfg), ctypes.byref(st),
         q.data_ptr(), q.stride(0), q.stride(1), q.stride(2),

@@ -88,19 +88,20 @@ extern "C" size_t ckv_update_workspace_bytes(const ckv_config *cfg, int32_t n_to
     return update_chunk_workspace_bytes(d, n_tokens);
 }
 
-extern "C" size_t ckv_attention_workspace_bytes(const ckv_config *cfg, int32_t n_tokens) {
+extern "C" size_t ckv_attention_workspace_bytes_for(const ckv_config *cfg, int32_t n_tokens, int32_t flags) {
     Dims d;
     if (make_dims(cfg, &d) != CKV_OK || n_tokens < 1) return 0;
-    size_t n = generic_workspace_bytes(d, n_tokens);
-    if (decode_tuned_supported(d, n_tokens)) {
-        const size_t t = decode_workspace_bytes(d);
-        n = t > n ? t : n;
-    }
-    if (prefill_tuned_supported(d, n_tokens)) {
-        const size_t t = prefill_workspace_bytes(d, n_tokens);
-        n = t > n ? t : n;
-    }
-    return n;
+    // the same choice of path as ckv_attention makes
+    if (!(flags & CKV_ATTN_FORCE_GENERIC) && decode_tuned_supported(d, n_tokens)) return decode_workspace_bytes(d);
+    if (!(flags & CKV_ATTN_FORCE_GENERIC) && prefill_tuned_supported(d, n_tokens))
+        return prefill_workspace_bytes(d, n_tokens);
+    return generic_workspace_bytes(d, n_tokens);
+}
+
+extern "C" size_t ckv_attention_workspace_bytes(const ckv_config *cfg, int32_t n_tokens) {
+    const size_t a = ckv_attention_workspace_bytes_for(cfg, n_tokens, 0);
+    const size_t b = ckv_attention_workspace_bytes_for(cfg, n_tokens, CKV_ATTN_FORCE_GENERIC);
+    return a > b ? a : b;
 }
 
 extern "C" int ckv_last_launch_count(void) { return g_launches; }

@@ -41,7 +41,7 @@ extern "C" int ckv_attention_static(const ckv_config *cfg, const ckv_layer_state
                                     int32_t n_tokens, const void *rope, int64_t rope_rows, const float *ema_w_cache,
                                     const void *ema_w_new, void *out, int64_t o_stride_b, int64_t o_stride_h,
                                     int64_t o_stride_t, int32_t flags, void *cuda_stream) {
-    const size_t need = ckv_attention_workspace_bytes(cfg, n_tokens);
+    const size_t need = ckv_attention_workspace_bytes_for(cfg, n_tokens, flags);
     if (need == 0) return fail(CKV_E_ARG, "invalid configuration or n_tokens");
     if (need > (size_t)CKV_STATIC_SCRATCH_BYTES)
         return fail(CKV_E_WORKSPACE,

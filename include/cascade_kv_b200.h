@@ -124,8 +124,18 @@ int ckv_cascade_update(const ckv_config *cfg, const ckv_layer_state *st,
                        const void *scores, int64_t s_stride_b, int64_t s_stride_h, int64_t s_stride_t,
                        int32_t n_tokens, void *workspace, size_t workspace_bytes, void *cuda_stream);
 
-/* Bytes of scratch ckv_attention needs for calls of up to n_tokens query tokens. */
+/* Bytes of scratch ckv_attention needs for calls of up to n_tokens query tokens, whatever their
+ * flags: the larger of the tuned path's need and the generic path's.  (The reference has no
+ * counterpart: its eager path allocates the logits and the concatenated, repeated and rotated
+ * keys through torch on every call, cascade/models/cascade_attention.py:250-340.) */
 size_t ckv_attention_workspace_bytes(const ckv_config *cfg, int32_t n_tokens);
+
+/* The same for calls that pass exactly these flags.  A caller that never sets
+ * CKV_ATTN_FORCE_GENERIC needs far less where a tuned kernel exists: the generic path keeps a
+ * logit row per (query head, query), the tuned decode path only its split-K partials (Llama-3.1-8B
+ * heads, 16 sequences, 8 x 8192 slots, one token: 86 MB instead of 2.3 GB).  Only
+ * CKV_ATTN_FORCE_GENERIC changes the answer. */
+size_t ckv_attention_workspace_bytes_for(const ckv_config *cfg, int32_t n_tokens, int32_t flags);
 
 /*
  * Attention of n_tokens new tokens over [sinks | cascade cache | the new tokens
@@ -148,7 +158,7 @@ size_t ckv_attention_workspace_bytes(const ckv_config *cfg, int32_t n_tokens);
  *               (1-beta)*beta^j                         (cascade_attention.py:269-282)
  *               (both may be NULL under CKV_ADMIT_STRIDE)
  *   out         [B, H, n_tokens, D]    element strides for b/h/t
- *   workspace   at least ckv_attention_workspace_bytes(cfg, n_tokens) bytes, 256-byte aligned
+ *   workspace   at least ckv_attention_workspace_bytes_for(cfg, n_tokens, flags) bytes, 256-byte aligned
  */
 int ckv_attention(const ckv_config *cfg, const ckv_layer_state *st,
                   const void *q, int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_t,
@@ -172,7 +182,7 @@ int ckv_attention(const ckv_config *cfg, const ckv_layer_state *st,
  * that is part of this library's device image: every GPU that loads the library holds those bytes
  * until the process exits.  Arguments are those of ckv_attention minus the workspace pair.
  *
- *  - Configurations whose ckv_attention_workspace_bytes() exceeds CKV_STATIC_SCRATCH_BYTES are
+ *  - Calls whose ckv_attention_workspace_bytes_for() exceeds CKV_STATIC_SCRATCH_BYTES are
  *    refused with CKV_E_WORKSPACE; use ckv_attention with your own buffer for those.
  *  - The first call on each device looks up the array's device address (with that device
  *    current); make that first call outside any stream capture.

@@ -43,6 +43,28 @@ def test_argument_errors_do_not_need_a_gpu():
     assert rc == -1 and b"null" in lib.ckv_last_error()
 
 
+def test_workspace_is_sized_for_the_path_the_flags_select():
+    """Decode at Llama-3.1-8B heads, 16 sequences, 8 x 8192 slots: the tuned path needs its split-K
+    partials and one 16-bit logit row per query head, the generic path fp32 logit rows and rotated keys."""
+    from cascading_kv_cache_b200 import _lib
+    lib = _lib.load()
+    cfg = _lib.CkvConfig(batch=16, kv_heads=8, q_heads=32, head_dim=128, num_sinks=64, window=8192, cascades=8,
+                         dtype=_lib.CKV_BF16, eager_fill=1, head_reduction=1, homogeneous_heads=0, admission=1,
+                         beta=0.9999)
+    ref = ctypes.byref(cfg)
+    tuned = lib.ckv_attention_workspace_bytes_for(ref, 1, _lib.CKV_ATTN_UPDATE)
+    generic = lib.ckv_attention_workspace_bytes_for(ref, 1, _lib.CKV_ATTN_UPDATE | _lib.CKV_ATTN_FORCE_GENERIC)
+    assert 0 < tuned < 128 << 20 < generic
+    assert lib.ckv_attention_workspace_bytes_for(ref, 1, 0) == tuned          # only the generic flag matters
+    assert lib.ckv_attention_workspace_bytes(ref, 1) == max(tuned, generic)
+    # fp32 has no tuned path: both answers are the generic one
+    cfg.dtype = _lib.CKV_F32
+    assert lib.ckv_attention_workspace_bytes_for(ref, 1, 0) == \
+        lib.ckv_attention_workspace_bytes_for(ref, 1, _lib.CKV_ATTN_FORCE_GENERIC) > 0
+    cfg.q_heads = 33
+    assert lib.ckv_attention_workspace_bytes_for(ref, 1, 0) == 0
+
+
 def test_cache_refuses_cpu_device_and_bad_configs():
     from cascading_kv_cache_b200 import CascadingKVCache, cascade_every_n
     with pytest.raises(RuntimeError):
