@@ -192,12 +192,14 @@ def measured_peak_tflops():
     return 1590.0, 1400.0, "fallback"
 
 
-def run_prefill_leg(dev, chunks=6, warm=2):
-    """Chunked prefill at the c3 shapes (batch 1, 32/8 heads, 4 sinks, 4 x 8192 slots, chunk 4096, EMA rule)
-    on a full cache: attention of the chunk + fused score/cache update per chunk."""
+def run_prefill_leg(dev, chunks=6, warm=2, admission=None):
+    """Chunked prefill at the c3 shapes (batch 1, 32/8 heads, 4 sinks, 4 x 8192 slots, chunk 4096) on a full
+    cache: attention of the chunk + fused score/cache update per chunk.  ``admission`` "ema" (c3 itself: two
+    passes over the keys, because the column scores need exactly normalised probabilities) or "stride" (the
+    other admission rule at the same shapes: no column scores, one pass)."""
     from cascading_kv_cache_b200 import CascadingKVCache, cascade_attention, profiling
     from cascading_kv_cache_b200.synthetic import populate_steady_state, prefill_algorithmic_flops
-    w = PREFILL
+    w = dict(PREFILL, admission=admission or PREFILL["admission"])
     B, H, KVH, D, NS, W, C, K = (w[k] for k in ("B", "H", "KVH", "D", "NS", "W", "C", "K"))
     S = W * C
     dt = torch.bfloat16
@@ -231,7 +233,8 @@ def run_prefill_leg(dev, chunks=6, warm=2):
     torch.cuda.synchronize()
     flops = prefill_algorithmic_flops(B, H, D, K, NS + S)
     burst, sustained, kind = measured_peak_tflops()
-    return {"workload": "c3_chunked_prefill_full_cache", "chunk_tokens": K, "tokens_per_s": K / (ms_chunk * 1e-3),
+    return {"workload": "c3_chunked_prefill_full_cache", "admission": w["admission"], "chunk_tokens": K,
+            "tokens_per_s": K / (ms_chunk * 1e-3),
             "ms_per_chunk": ms_chunk, "algorithmic_tflop_per_chunk": flops / 1e12,
             "tflops": flops / (ms_chunk * 1e-3) / 1e12, "kernel": k_name, "kernel_ms": k_ms,
             "kernel_tflops": flops / (k_ms * 1e-3) / 1e12, "peak_tflops": burst, "peak_kind": kind,
@@ -273,6 +276,7 @@ def main():
     ap.add_argument("--no-prefill", action="store_true", help="skip the chunked-prefill leg")
     ap.add_argument("--prefill-only", action="store_true", help="run only the chunked-prefill leg (profiler captures)")
     ap.add_argument("--prefill-chunks", type=int, default=6)
+    ap.add_argument("--prefill-admission", choices=["ema", "stride"], default="ema")
     args = ap.parse_args()
     w = dict(WORKLOADS[args.workload])
     if args.batch > 0:
@@ -288,7 +292,7 @@ def main():
     if args.prefill_only:
         torch.cuda.set_device(local_rank)
         print(json.dumps({"prefill": run_prefill_leg(torch.device("cuda", local_rank), chunks=args.prefill_chunks,
-                                                     warm=1)}), flush=True)
+                                                     warm=1, admission=args.prefill_admission)}), flush=True)
         return
 
     import torch.distributed as dist
@@ -409,6 +413,7 @@ def main():
         if not args.no_prefill:
             del qs, ks, vs
             line["prefill"] = run_prefill_leg(dev)
+            line["prefill_stride_rule"] = run_prefill_leg(dev, admission="stride")
         if not args.no_cpu_baseline:
             sec, threads, cpu_bytes = time_cpu_port(w, steps=2, warmup=1)
             line["cpu_baseline"] = {

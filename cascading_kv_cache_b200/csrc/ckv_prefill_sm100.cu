@@ -27,6 +27,7 @@
 // completions behind it.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <type_traits>
 
 #include "ckv_common.cuh"
@@ -932,6 +933,343 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
 }
 
+// ------------------------------------------------------------------- single pass (no column scores)
+// Calls that need no column scores -- the stride rule, or no update at all -- have no use for exactly
+// normalised probabilities, so one pass over the keys suffices: a running reference maximum per query,
+// unnormalised probabilities exp(s - m_ref) into P, O += P V, and a division by the row sum at the end.
+// Rows are queries here (S = Q K^T, O = P V), so maximum and sum are private to a thread; the two warps
+// that share a row (one per half of the tile's 128 keys) agree on the tile's maximum through shared
+// memory.  The reference maximum moves only when a tile exceeds it by more than kLazy: the accumulator
+// is then rescaled in tensor memory by the threads of the row, which after the first tiles is rare.
+constexpr float kLazy = 5.545177f;   // ln 256: unnormalised probabilities stay below 256
+
+template <typename T> __device__ __forceinline__ uint32_t max2_t(uint32_t a, uint32_t b);
+template <> __device__ __forceinline__ uint32_t max2_t<__nv_bfloat16>(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("max.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+template <> __device__ __forceinline__ uint32_t max2_t<__half>(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("max.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+// barrier between the two warps that share the rows of one quarter of one head
+__device__ __forceinline__ void pair_sync(int grp, int quarter) {
+    asm volatile("bar.sync %0, 64;" ::"r"(4 + 4 * grp + quarter) : "memory");
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+prefill_single_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                      const __grid_constant__ CUtensorMap tmV, PrefillParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    if ((s_u32(smem) & 1023u) != 0) {
+        if (threadIdx.x == 0) atomicExch(p.status, 3);
+        return;
+    }
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kOffBar);
+    uint64_t *q_full = bars + 0, *rb_full = bars + 11, *rb_empty = bars + 15;
+    uint64_t *s_full = bars + 19, *s_free = bars + 21, *p_full = bars + 23, *p_free = bars + 25, *o_full = bars + 27;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 30);
+
+    const int warp = threadIdx.x >> 5, lane_id = threadIdx.x & 31;
+    const int qt = blockIdx.x;
+    const int pairs = (p.G + 1) / 2;
+    const int lane_i = blockIdx.y / pairs, pair = blockIdx.y % pairs;
+    const int b = lane_i / p.KVH, kvh = lane_i % p.KVH;
+    const long long lane = lane_i;
+    const int head[2] = {kvh * p.G + 2 * pair, kvh * p.G + 2 * pair + 1};
+    const bool head_ok[2] = {true, 2 * pair + 1 < p.G};
+    const int bh[2] = {b * p.H + head[0], b * p.H + (head_ok[1] ? head[1] : head[0])};
+    const Extents e = make_extents(p);
+    const int q_hi = min(p.K, kBM * (qt + 1));
+    const int n_keys = e.n_cached + q_hi;
+    const int nT_all = (n_keys + kBN - 1) / kBN;
+    const int split = blockIdx.z;
+    const int t0 = (int)((long long)nT_all * split / p.nSplit);
+    const int nT = (int)((long long)nT_all * (split + 1) / p.nSplit) - t0;
+
+    if (threadIdx.x == 0) {
+        bar_init(q_full, 1);
+        for (int i = 0; i < kRingB; ++i) {
+            bar_init(&rb_full[i], 1);
+            bar_init(&rb_empty[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            bar_init(&s_full[i], 1);
+            bar_init(&s_free[i], 8);
+            bar_init(&p_full[i], 8);
+            bar_init(&p_free[i], 1);
+        }
+        bar_init(o_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s_u32(tmem_slot)), "r"(kTmemCols));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t tm_s[2] = {tmem, tmem + 128u};
+    const uint32_t tm_o[2] = {tmem + 256u, tmem + 384u};
+    constexpr uint32_t kSlotStep = (uint32_t)(kTileBytes >> 4);
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer: K_j into slot 0, V_j into 1 + (j & 1)
+        if (lane_id == 0) {
+            bar_expect_tx(q_full, 2 * kTileBytes);
+#pragma unroll
+            for (int hd = 0; hd < 2; ++hd) {
+                const int yq = bh[hd] * p.Kpad + qt * kBM;
+                tma_2d(smem + kOffQ + hd * kTileBytes, &tmQ, 0, yq, q_full);
+                tma_2d(smem + kOffQ + hd * kTileBytes + kSubBytes, &tmQ, 64, yq, q_full);
+            }
+            bool ok = true;
+            auto load_tile = [&](const CUtensorMap *tm, int j, int slot, uint64_t *full) {
+                const int y = (int)(lane * p.Rpad) + j * kBN;
+                uint8_t *dst = smem + kOffRing + slot * kTileBytes;
+                bar_expect_tx(full, kTileBytes);
+                tma_2d(dst, tm, 0, y, full);
+                tma_2d(dst + kSubBytes, tm, 64, y, full);
+            };
+            for (int j = 0; ok && j < nT; ++j) {
+                const int vs = 1 + (j & 1);
+                if (j >= 1) ok = bar_wait(&rb_empty[0], (j - 1) & 1, p.status);
+                if (ok) load_tile(&tmK, t0 + j, 0, &rb_full[0]);
+                if (ok && j >= 2) ok = bar_wait(&rb_empty[vs], ((j >> 1) - 1) & 1, p.status);
+                if (ok) load_tile(&tmV, t0 + j, vs, &rb_full[vs]);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ S[hd] = Q[hd] K^T (both operands K-major)
+        if (lane_id == 0) {
+            const uint32_t id_kk = idesc<T>(false, false);
+            const uint32_t q_addr = s_u32(smem + kOffQ);
+            const uint32_t q_lo[2] = {desc_lo_k(q_addr), desc_lo_k(q_addr + kTileBytes)};
+            const uint32_t k_lo = desc_lo_k(s_u32(smem + kOffRing));
+            bool ok = bar_wait(q_full, 0, p.status);
+            for (int j = 0; ok && j < nT; ++j) {
+                ok = bar_wait(&rb_full[0], j & 1, p.status);
+#pragma unroll
+                for (int hd = 0; hd < 2; ++hd) {
+                    if (ok && j >= 1) ok = bar_wait(&s_free[hd], (j - 1) & 1, p.status);
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int ks = 0; ks < 8; ++ks) {
+                        const uint32_t off = (uint32_t)(((ks >> 2) * kSubBytes + (ks & 3) * 32) >> 4);
+                        tc_mma(tm_s[hd], desc_from(q_lo[hd] + off), desc_from(k_lo + off), id_kk, ks > 0 ? 1u : 0u);
+                    }
+                    if (hd == 1) tc_commit(&rb_empty[0]);
+                    tc_commit(&s_full[hd]);
+                }
+            }
+        }
+    } else if (warp == kPvWarp) {
+        // ------------------------------------------------------------ O[hd] += P[hd] V (P K-major, V MN-major)
+        if (lane_id == 0) {
+            const uint32_t id_pv = idesc<T>(false, true);
+            const uint32_t p_lo[2] = {desc_lo_k(s_u32(smem + kOffP)), desc_lo_k(s_u32(smem + kOffP + kTileBytes))};
+            const uint32_t r_lo_mn = desc_lo_mn(s_u32(smem + kOffRing));
+            bool ok = true;
+            for (int j = 0; ok && j < nT; ++j) {
+                const int slot = 1 + (j & 1);
+                const uint32_t v_lo = r_lo_mn + slot * kSlotStep;
+#pragma unroll
+                for (int hd = 0; hd < 2; ++hd) {
+                    if (ok) ok = bar_wait(&p_full[hd], j & 1, p.status);
+                    if (ok && hd == 0) ok = bar_wait(&rb_full[slot], (j >> 1) & 1, p.status);
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int ks = 0; ks < 8; ++ks) {
+                        // 16 keys per step: 32 bytes along a row of P, 16 rows of V
+                        const uint32_t p_off = (uint32_t)(((ks >> 2) * kSubBytes + (ks & 3) * 32) >> 4);
+                        const uint32_t v_off = (uint32_t)((ks * 2048) >> 4);
+                        tc_mma(tm_o[hd], desc_from(p_lo[hd] + p_off), desc_from(v_lo + v_off), id_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                    }
+                    if (hd == 1) tc_commit(&rb_empty[slot]);
+                    tc_commit(&p_free[hd]);
+                }
+            }
+            if (ok) tc_commit(o_full);
+        }
+    } else {
+        // ------------------------------------------------------------ softmax warps (2 groups of 8)
+        // group = head of the pair; row = query = tensor-memory lane; the two warps of a quarter split the
+        // tile's 128 keys (S columns, P columns) and the 128 dims of O
+        const int grp = (warp - 2) >> 3;
+        const int half = ((warp - 2) >> 2) & 1;
+        const int quarter = warp & 3;
+        const int row = 32 * quarter + lane_id;
+        const uint32_t lane_base = (uint32_t)(32 * quarter) << 16;
+        const uint32_t tms = tmem + 128u * grp + lane_base + 64 * half;
+        const uint32_t tmo = tmem + 256u + 128u * grp + lane_base + 64 * half;
+        const int head_g = kvh * p.G + 2 * pair + grp;
+        const bool head_ok_g = grp == 0 || 2 * pair + 1 < p.G;
+        const int bh_g = b * p.H + (head_ok_g ? head_g : head_g - 1);
+        const uint64_t l2e2 = pk2(kLog2e, kLog2e);
+        const int qg = qt * kBM + row;
+        const bool row_ok = qg < p.K;
+        const int row_limit = e.n_cached + (row_ok ? qg + 1 : 0);         // visible keys: [0, row_limit)
+        uint8_t *pt_row = smem + kOffP + grp * kTileBytes + half * kSubBytes + row * 128;
+        // tile maxima of the two halves, as 16-bit patterns of T: [tile parity][head][half][row]
+        uint16_t *mx_buf = reinterpret_cast<uint16_t *>(smem + kOffW);
+        float m_ref = kMasked, l_run = 0.f;
+        bool ok = true, s_rdy = false;
+        for (int g = 0; g < nT; ++g) {
+            const int gg = t0 + g;
+            const bool full_tile = (gg + 1) * kBN <= e.n_cached + qt * kBM + 1 && (qt + 1) * kBM <= p.K;
+            // after a failed (timed-out) wait the warp keeps walking the loops without waiting, so that
+            // the pair and group barriers below are still reached by everyone
+            if (ok && !s_rdy) ok = bar_wait(&s_full[grp], g & 1, p.status);
+            tc_fence_after();
+            // the tile's logits, rounded to T and packed in pairs; the accumulator is released at once
+            uint32_t sp[2][16];
+#pragma unroll
+            for (int ch = 0; ch < 2; ++ch) {
+                uint32_t v[32];
+                tc_ld32(tms + 32 * ch, v);
+                tc_ld_wait();
+                if (!full_tile) {
+                    const int col0 = gg * kBN + 64 * half + 32 * ch;
+#pragma unroll
+                    for (int c = 0; c < 32; ++c)
+                        if (col0 + c >= row_limit) v[c] = __float_as_uint(kMasked);
+                }
+#pragma unroll
+                for (int i = 0; i < 16; ++i) sp[ch][i] = P2<T>::pack(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane_id == 0) bar_arrive(&s_free[grp]);
+            bool p_rdy = g == 0;
+            if (!p_rdy) p_rdy = bar_probe(&p_free[grp], (g - 1) & 1);
+            // maximum of this half of the row, on the packed pairs; the row's other half through shared memory
+            uint32_t mx2 = max2_t<T>(sp[0][0], sp[1][0]);
+#pragma unroll
+            for (int i = 1; i < 16; ++i) mx2 = max2_t<T>(mx2, max2_t<T>(sp[0][i], sp[1][i]));
+            mx2 = max2_t<T>(mx2, mx2 >> 16);
+            uint16_t *mx_slot = mx_buf + (((g & 1) * 2 + grp) * 2) * 128;
+            mx_slot[half * 128 + row] = (uint16_t)(mx2 & 0xFFFFu);
+            pair_sync(grp, quarter);
+            float m_mine, m_other;
+            P2<T>::unpack((mx2 & 0xFFFFu) | ((uint32_t)mx_slot[(half ^ 1) * 128 + row] << 16), m_mine, m_other);
+            const float m_tile = fmaxf(m_mine, m_other);
+            const bool fix = m_tile > m_ref + kLazy;
+            float scale = 1.f;
+            if (fix) {
+                scale = ex2f((m_ref - m_tile) * kLog2e);     // 0 while nothing had been seen
+                m_ref = m_tile;
+                l_run *= scale;
+            }
+            const float mneg = -m_ref * kLog2e;
+            const uint64_t mneg2 = pk2(mneg, mneg);
+            uint64_t sum2[2] = {0ull, 0ull};
+#pragma unroll
+            for (int ch = 0; ch < 2; ++ch) {
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    float s0, s1, a0, a1;
+                    P2<T>::unpack(sp[ch][i], s0, s1);
+                    upk2(fma2(pk2(s0, s1), l2e2, mneg2), a0, a1);
+                    const float e0 = ex2f(a0), e1 = ex2f(a1);
+                    sum2[i & 1] = add2(sum2[i & 1], pk2(e0, e1));
+                    pk[i] = P2<T>::pack(e0, e1);
+                }
+                if (ch == 0) {
+                    // P may be rewritten, and O rescaled, once the P V product of the previous tile is complete
+                    if (ok && !p_rdy) ok = bar_wait(&p_free[grp], (g - 1) & 1, p.status);
+                    if (g > 0 && __any_sync(0xFFFFFFFFu, fix)) {
+                        tc_fence_after();
+#pragma unroll 1
+                        for (int c2 = 0; c2 < 2; ++c2) {
+                            uint32_t o[32];
+                            tc_ld32(tmo + 32 * c2, o);
+                            tc_ld_wait();
+#pragma unroll
+                            for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * scale);
+                            tc_st32(tmo + 32 * c2, o);
+                        }
+                        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                        tc_fence_before();
+                    }
+                } else {
+                    s_rdy = bar_probe(&s_full[grp], (g + 1) & 1);
+                }
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const int chunk = ch * 4 + q4;
+                    *reinterpret_cast<uint4 *>(pt_row + ((chunk ^ (row & 7)) << 4)) =
+                        make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
+                }
+            }
+            float t0s, t1s;
+            upk2(add2(sum2[0], sum2[1]), t0s, t1s);
+            l_run += t0s + t1s;
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane_id == 0) bar_arrive(&p_full[grp]);
+        }
+
+        // ---- the row's sum is the sum of its two halves (the exchange area is free once the group is out of the loop)
+        float *l_buf = reinterpret_cast<float *>(smem + kOffW);            // [half][head][row], inside the head's own part
+        group_sync(grp);
+        l_buf[half * 256 + grp * 128 + row] = l_run;
+        group_sync(grp);
+        const float l_tot = l_run + l_buf[(half ^ 1) * 256 + grp * 128 + row];
+
+        // ---- epilogue: this thread holds dims [64 half, 64 half + 64) of its query's row of O
+        //      (tensor-memory loads are warp-wide: only the stores depend on the row being a real query)
+        if (ok && bar_wait(o_full, 0, p.status) && head_ok_g) {
+            tc_fence_after();
+            const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
+#pragma unroll 1
+            for (int ch = 0; ch < 2; ++ch) {
+                uint32_t v[32];
+                if (nT > 0) {
+                    tc_ld32(tmo + 32 * ch, v);
+                    tc_ld_wait();
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) v[c] = 0u;                // an empty key split contributes nothing
+                }
+                const int d0 = 64 * half + 32 * ch;
+                if (!row_ok) continue;
+                if (p.nSplit == 1) {
+                    T *orow = reinterpret_cast<T *>(p.out) + b * p.osb + head_g * p.osh + (long long)qg * p.ost + d0;
+#pragma unroll
+                    for (int c = 0; c < 32; c += 8) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u)
+                            w[u] = P2<T>::pack(__uint_as_float(v[c + 2 * u]) * inv, __uint_as_float(v[c + 2 * u + 1]) * inv);
+                        *reinterpret_cast<uint4 *>(orow + c) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                } else {
+                    float *orow = p.opart + (((long long)split * p.B * p.H + bh_g) * p.Kpad + qg) * 128 + d0;
+#pragma unroll
+                    for (int c = 0; c < 32; c += 4)
+                        *reinterpret_cast<uint4 *>(orow + c) = make_uint4(v[c], v[c + 1], v[c + 2], v[c + 3]);
+                }
+            }
+            if (p.nSplit > 1 && half == 0 && row_ok)
+                p.stats[((long long)bh_g * p.nSplit + split) * p.Kpad + qg] = make_float2(m_ref, l_tot);
+        }
+        tc_fence_before();
+    }
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols));
+    }
+}
+
 // Sum of the key splits' fp32 partials, in split order, rounded to T.  One thread per 4 dims.
 template <typename T>
 __global__ void __launch_bounds__(256) prefill_combine_kernel(PrefillParams p) {
@@ -955,6 +1293,42 @@ __global__ void __launch_bounds__(256) prefill_combine_kernel(PrefillParams p) {
     o[1] = Elem<T>::from_f(acc.y);
     o[2] = Elem<T>::from_f(acc.z);
     o[3] = Elem<T>::from_f(acc.w);
+}
+
+// Key splits of the single pass: each left its unnormalised fp32 partial with its reference maximum
+// and row sum; the result is the partials brought to the common maximum, summed and divided by the
+// sums brought there too.  One thread per 4 dims.
+template <typename T>
+__global__ void __launch_bounds__(256) prefill_combine_single_kernel(PrefillParams p) {
+    const long long n4 = (long long)p.B * p.H * p.K * 32;
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n4) return;
+    const int d4 = (int)(idx & 31);
+    const long long row = idx >> 5;                 // (b, h, q)
+    const int q = (int)(row % p.K);
+    const int bh = (int)(row / p.K);
+    const long long split_stride = (long long)p.B * p.H * p.Kpad * 128;
+    const float *src = p.opart + ((long long)bh * p.Kpad + q) * 128 + 4 * d4;
+    const float2 *st = p.stats + (long long)bh * p.nSplit * p.Kpad + q;
+    float mm = kMasked;
+    for (int sp = 0; sp < p.nSplit; ++sp) mm = fmaxf(mm, st[(long long)sp * p.Kpad].x);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float l = 0.f;
+    for (int sp = 0; sp < p.nSplit; ++sp) {
+        const float2 ml = st[(long long)sp * p.Kpad];
+        if (ml.y <= 0.f) continue;                  // a split in which the query saw no key
+        const float w = ex2f((ml.x - mm) * kLog2e);
+        const float4 x = *reinterpret_cast<const float4 *>(src + sp * split_stride);
+        acc.x = fmaf(x.x, w, acc.x); acc.y = fmaf(x.y, w, acc.y); acc.z = fmaf(x.z, w, acc.z); acc.w = fmaf(x.w, w, acc.w);
+        l = fmaf(ml.y, w, l);
+    }
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    const int b = bh / p.H, h = bh % p.H;
+    T *o = reinterpret_cast<T *>(p.out) + b * p.osb + h * p.osh + (long long)q * p.ost + 4 * d4;
+    o[0] = Elem<T>::from_f(acc.x * inv);
+    o[1] = Elem<T>::from_f(acc.y * inv);
+    o[2] = Elem<T>::from_f(acc.z * inv);
+    o[3] = Elem<T>::from_f(acc.w * inv);
 }
 
 // ----------------------------------------------------------------------------------- score reduce
@@ -1147,6 +1521,10 @@ int launch_prefill_tuned(const Dims &d, const ckv_layer_state *st, const void *q
             (const void *)prefill_attn_kernel<__half, false, false>, (const void *)prefill_attn_kernel<__half, false, true>};
         for (const void *k : kernels)
             CKV_CUDA_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));
+        CKV_CUDA_CHECK(cudaFuncSetAttribute(prefill_single_kernel<__nv_bfloat16>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));
+        CKV_CUDA_CHECK(cudaFuncSetAttribute(prefill_single_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            kAttnSmem));
     }
     uint8_t *ws = (uint8_t *)workspace;
     PrefillParams p;
@@ -1183,33 +1561,46 @@ int launch_prefill_tuned(const Dims &d, const ckv_layer_state *st, const void *q
     p.nSplit = s.nSplit;
     const dim3 grid(s.nQT, d.B * d.KVH * ((d.G + 1) / 2), p.nSplit);
     const long long comb = (long long)d.B * d.H * n_tokens * 32;
+    // calls without column scores take the single pass; the environment switch keeps the two-pass
+    // kernels reachable for them (comparison runs)
+    static const bool two_pass_always = getenv("CKV_PREFILL_TWO_PASS") != nullptr;
     if (d.dtype == CKV_BF16) {
         prefill_prep_kernel<__nv_bfloat16><<<prep_blocks, 256, 0, stream>>>(p);
-        if (hook) hook->before(stream, "prefill_attn_kernel");
+        if (hook) hook->before(stream, (ema || two_pass_always) ? "prefill_attn_kernel" : "prefill_single_kernel");
         if (ema) {
             prefill_attn_kernel<__nv_bfloat16, true, false><<<grid, kAttnThreads, kAttnSmem, stream>>>(tmQ, tmK, tmV, p);
             prefill_attn_kernel<__nv_bfloat16, true, true><<<grid, kAttnThreads, kAttnSmem, stream>>>(tmQ, tmK, tmV, p);
-        } else {
+            if (p.nSplit > 1) prefill_combine_kernel<__nv_bfloat16><<<(unsigned)((comb + 255) / 256), 256, 0, stream>>>(p);
+        } else if (two_pass_always) {
             prefill_attn_kernel<__nv_bfloat16, false, false><<<grid, kAttnThreads, kAttnSmem, stream>>>(tmQ, tmK, tmV, p);
             prefill_attn_kernel<__nv_bfloat16, false, true><<<grid, kAttnThreads, kAttnSmem, stream>>>(tmQ, tmK, tmV, p);
+            if (p.nSplit > 1) prefill_combine_kernel<__nv_bfloat16><<<(unsigned)((comb + 255) / 256), 256, 0, stream>>>(p);
+        } else {
+            prefill_single_kernel<__nv_bfloat16><<<grid, kAttnThreads, kAttnSmem, stream>>>(tmQ, tmK, tmV, p);
+            if (p.nSplit > 1)
+                prefill_combine_single_kernel<__nv_bfloat16><<<(unsigned)((comb + 255) / 256), 256, 0, stream>>>(p);
         }
-        if (p.nSplit > 1) prefill_combine_kernel<__nv_bfloat16><<<(unsigned)((comb + 255) / 256), 256, 0, stream>>>(p);
         if (hook) hook->after(stream);
     } else {
         prefill_prep_kernel<__half><<<prep_blocks, 256, 0, stream>>>(p);
-        if (hook) hook->before(stream, "prefill_attn_kernel");
+        if (hook) hook->before(stream, (ema || two_pass_always) ? "prefill_attn_kernel" : "prefill_single_kernel");
         if (ema) {
             prefill_attn_kernel<__half, true, false><<<grid, kAttnThreads, kAttnSmem, stream>>>(tmQ, tmK, tmV, p);
             prefill_attn_kernel<__half, true, true><<<grid, kAttnThreads, kAttnSmem, stream>>>(tmQ, tmK, tmV, p);
-        } else {
+            if (p.nSplit > 1) prefill_combine_kernel<__half><<<(unsigned)((comb + 255) / 256), 256, 0, stream>>>(p);
+        } else if (two_pass_always) {
             prefill_attn_kernel<__half, false, false><<<grid, kAttnThreads, kAttnSmem, stream>>>(tmQ, tmK, tmV, p);
             prefill_attn_kernel<__half, false, true><<<grid, kAttnThreads, kAttnSmem, stream>>>(tmQ, tmK, tmV, p);
+            if (p.nSplit > 1) prefill_combine_kernel<__half><<<(unsigned)((comb + 255) / 256), 256, 0, stream>>>(p);
+        } else {
+            prefill_single_kernel<__half><<<grid, kAttnThreads, kAttnSmem, stream>>>(tmQ, tmK, tmV, p);
+            if (p.nSplit > 1)
+                prefill_combine_single_kernel<__half><<<(unsigned)((comb + 255) / 256), 256, 0, stream>>>(p);
         }
-        if (p.nSplit > 1) prefill_combine_kernel<__half><<<(unsigned)((comb + 255) / 256), 256, 0, stream>>>(p);
         if (hook) hook->after(stream);
     }
     CKV_CUDA_CHECK(cudaGetLastError());
-    int launches = 3 + (p.nSplit > 1 ? 1 : 0);
+    int launches = ((ema || two_pass_always) ? 3 : 2) + (p.nSplit > 1 ? 1 : 0);
     if (ema) {
         const long long n = (long long)d.B * d.KVH * (d.S + n_tokens);
         if (d.dtype == CKV_BF16) prefill_scores_kernel<__nv_bfloat16><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(p);

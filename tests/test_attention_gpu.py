@@ -266,3 +266,60 @@ def test_tuned_kernels_are_the_ones_that_run():
     assert profiling.last_launch_count() == 3       # cos/sin image, stream, finish
     assert profiling.time_dominant_kernel(generic, 1)[2] == "attn_rows_kernel"
     assert cache.kernel_status() == 0
+
+
+def test_chunks_without_column_scores_take_the_single_pass():
+    """Stride rule, or no update: one pass over the keys (prep, single-pass attention; then the update's
+    walk and finalize when asked for)."""
+    from cascading_kv_cache_b200 import CascadingKVCache, cascade_attention, profiling
+    g = torch.Generator().manual_seed(4)
+    mk = lambda h, n: torch.randn(1, h, n, 128, generator=g).bfloat16().cuda()
+    for rule, update, launches in (("stride", True, 4), ("stride", False, 2), ("ema", False, 2)):
+        cache = CascadingKVCache(128, 4, 1, 2, 128, 512, device="cuda:0", dtype=torch.bfloat16, layers=1,
+                                 admission=rule)
+
+        def chunk(_):
+            cascade_attention(mk(8, 200), mk(2, 200), mk(2, 200), cache, 0, update=update)
+
+        assert profiling.time_dominant_kernel(chunk, 2)[2] == "prefill_single_kernel"
+        assert profiling.last_launch_count() == launches, (rule, update)
+        assert cache.kernel_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "fp16"])
+@pytest.mark.parametrize("growth", [1.0, -1.0], ids=["rising", "falling"])
+def test_single_pass_rescales_its_accumulator(dtype, growth):
+    """Logits that grow along the key order (sinks, cache, chunk) by far more than the single pass lets its
+    reference maximum lag: the accumulator in tensor memory is rescaled several times after the first tile.
+    Falling logits never move the reference after the first tile.  Both against the CPU oracle.
+
+    The growth is a shift, not a spread: every key carries ``a_j`` and every query 17 in the slowest-rotating
+    RoPE pair (its angle stays below 0.003 rad here), so the logit of key j is about 17 a_j / sqrt(128) plus
+    unit noise, up to 25 -- and each row's mass stays on some tens of comparable keys, which keeps the
+    comparison insensitive to a logit that rounds the other way in 16 bits."""
+    from cascading_kv_cache_b200 import CascadingKVCache, cascade_attention
+    B, H, KVH, D, NS, W, C, theta = 1, 4, 2, 128, 4, 256, 2, 5e5
+    S = W * C
+    total = NS + S + 431
+    g = torch.Generator().manual_seed(11)
+    cache = CascadingKVCache(W, NS, B, KVH, D, S, device="cuda:0", dtype=dtype, layers=1, eager_fill=True,
+                             admission="stride")
+    ref = OracleCascadingKVCache(W, NS, B, KVH, D, S, dtype=dtype, layers=1, eager_fill=True)
+    seen = 0
+    for n in (NS + S, 300, 131):
+        t = torch.arange(seen, seen + n, dtype=torch.float32) / float(total)
+        a = 17.0 * (t if growth > 0 else 1.0 - t)
+        q = torch.randn(B, H, n, D, generator=g)
+        k = torch.randn(B, KVH, n, D, generator=g)
+        q[..., D // 2 - 1] = 17.0
+        k[..., D // 2 - 1] = a[None, None, :]
+        q, k = q.to(dtype), k.to(dtype)
+        v = torch.randn(B, KVH, n, D, generator=g).to(dtype)
+        want = cascade_attention_step(q, k, v, ref, 0, theta, None, False, do_update=False)
+        ref.update(k, v, 0)
+        got = cascade_attention(q.cuda(), k.cuda(), v.cuda(), cache, 0, rope_theta=theta).float().cpu()
+        ok, err = close_enough(got, want.float(), True)
+        assert ok, (n, err)
+        seen += n
+    assert torch.equal(cache.og_pos[0].cpu(), ref.og_pos[0])
+    assert cache.kernel_status() == 0

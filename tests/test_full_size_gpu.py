@@ -171,3 +171,25 @@ def test_c1_fp32_stride_stream_in_full():
     for name in ("stored_tokens", "start_indices", "sink_keys", "sink_values", "sink_pos"):
         assert torch.equal(getattr(cache, name)[0].cpu(), getattr(ref, name)[0]), name
     assert cache.seen_tokens_host(0) == 16384 + 64 and cache.kernel_status() == 0
+
+
+def test_c3_shapes_stride_rule_single_pass_full_size():
+    """The c3 shapes under the stride rule: the single-pass tcgen05 kernel (key tiles split over two CTAs per
+    query tile, partials merged by their maxima and sums) against the CUDA-core path; the cache bit for bit."""
+    from cascading_kv_cache_b200 import cascade_attention
+    w = dict(C3, rule="stride")
+    tuned, generic = _gpu_cache(w), _gpu_cache(w)
+    g = torch.Generator().manual_seed(103)
+    for _ in range(2):
+        q = torch.randn(w["B"], w["H"], w["K"], w["D"], generator=g).bfloat16().cuda()
+        k = torch.randn(w["B"], w["KVH"], w["K"], w["D"], generator=g).bfloat16().cuda()
+        v = torch.randn(w["B"], w["KVH"], w["K"], w["D"], generator=g).bfloat16().cuda()
+        got = cascade_attention(q, k, v, tuned, 0, rope_theta=w["theta"]).float().cpu()
+        alt = cascade_attention(q, k, v, generic, 0, rope_theta=w["theta"], force_generic=True).float().cpu()
+        ok, err = close_enough(got, alt, True)
+        assert ok, err
+        for name in ("_pos", "_mask", "_stored_tokens", "_start_indices"):
+            assert torch.equal(getattr(tuned, name)[0], getattr(generic, name)[0]), name
+        for name in ("og_pos", "key_cache", "value_cache"):
+            assert torch.equal(getattr(tuned, name)[0], getattr(generic, name)[0]), name
+    _state_properties(tuned, w)
