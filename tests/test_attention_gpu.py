@@ -155,6 +155,8 @@ def test_streams_against_oracle(spec, force_generic):
             assert min(step_agree) >= 0.998 and sum(step_agree) / len(step_agree) >= 0.9995, step_agree
             assert min(score_bits) >= 0.99, score_bits
         return
+    if not bool(valid.any()):       # a stream shorter than the sink count never reaches the cascades
+        return
     agree = (cache.og_pos[0].cpu()[valid] == ref.og_pos[0][valid]).float().mean().item()
     if rule == "stride":
         assert agree == 1.0
