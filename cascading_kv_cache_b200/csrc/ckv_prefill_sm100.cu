@@ -79,7 +79,7 @@ struct PrefillParams {
     void *new_scores;  // [B*KVH][K]
     int B, KVH, H, G, NS, S, C, K, Kpad, Rpad, nQT;
     int ema, head_reduction;
-    float rs, beta_pow;
+    float rs, beta_pow, beta;
 };
 
 struct Extents {
@@ -711,7 +711,11 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                         uint64_t sum2[2] = {0ull, 0ull};
 #pragma unroll
                         for (int i = 0; i < 16; ++i) {
-                            const uint64_t r = round2_to_t<T>(pk2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])));
+                            // rounded by the conversion instruction and unpacked again: the ALU pipe is the idle
+                            // one in this phase, the FMA pipe (which the Veltkamp form uses) is not
+                            float r0, r1;
+                            P2<T>::unpack(P2<T>::pack(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])), r0, r1);
+                            const uint64_t r = pk2(r0, r1);
                             float a0, a1;
                             upk2(fma2(r, l2e2, mneg2), a0, a1);
                             sum2[i & 1] = add2(sum2[i & 1], pk2(ex2f(a0), ex2f(a1)));
@@ -770,6 +774,9 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         // EMA partial of (head, query tile, query half): summed over tiles and halves by prefill_scores_kernel
         float *part = (kEma && head_ok_g) ? p.colpart + (((long long)bh_g * p.nQT + qt) * 2 + half) * p.Rpad : nullptr;
         bool s_rdy = false;
+        const float b2 = p.beta * p.beta, b4 = b2 * b2;
+        const uint64_t beta4 = pk2(b4, b4);
+        const float w_last = kEma ? wq_h[64 * half + 63] : 0.f;   // weight of the last query of this thread's half
         for (int jb = 0; jb < nTb; ++jb) {
             const int jg = t0 + jb;                              // tile index among all the keys
             const int key = jg * kBN + row;                      // row of the compacted key matrix
@@ -826,12 +833,15 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                         const uint32_t qa = P2<T>::pack(ex2f(a0), ex2f(a1));
                         const uint32_t qb = P2<T>::pack(ex2f(b0), ex2f(b1));
                         if (kEma) {
-                            const ulonglong2 wq = *reinterpret_cast<const ulonglong2 *>(wq_h + qbase + c4);
+                            // The weights are geometric, w_q = w_63 beta^(63 - q) over the thread's 64 queries,
+                            // so the weighted sum is a Horner recurrence with one constant instead of a
+                            // weight per query from shared memory: four interleaved chains (queries
+                            // q mod 4), each sum_q beta^(last - q) p_q, joined after the tile.
                             float p0, p1, p2, p3;
                             P2<T>::unpack(qa, p0, p1);
                             P2<T>::unpack(qb, p2, p3);
-                            acc2[0] = fma2(pk2(p0, p1), wq.x, acc2[0]);
-                            acc2[1] = fma2(pk2(p2, p3), wq.y, acc2[1]);
+                            acc2[0] = fma2(acc2[0], beta4, pk2(p0, p1));
+                            acc2[1] = fma2(acc2[1], beta4, pk2(p2, p3));
                         }
                         pk[(c4 >> 1)] = qa;
                         pk[(c4 >> 1) + 1] = qb;
@@ -880,9 +890,12 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 }
             }
             if (fast_tile) {
-                float t0, t1;
-                upk2(add2(acc2[0], acc2[1]), t0, t1);
-                acc = t0 + t1;
+                // the chains end at queries 60, 61 (acc2[0]) and 62, 63 (acc2[1]) of the half: bring them to
+                // query 63 and apply that query's weight
+                float t0, t1, t2, t3;
+                upk2(acc2[0], t0, t1);
+                upk2(acc2[1], t2, t3);
+                acc = (((t0 * p.beta + t1) * p.beta + t2) * p.beta + t3) * w_last;
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
@@ -1547,6 +1560,7 @@ int launch_prefill_tuned(const Dims &d, const ckv_layer_state *st, const void *q
     p.ema = ema; p.head_reduction = d.head_reduction;
     p.rs = (float)sqrt(1.0 / sqrt((double)d.D));
     p.beta_pow = (float)pow(d.beta, (double)n_tokens);
+    p.beta = (float)d.beta;
 
     CUtensorMap tmQ, tmK, tmV;
     int rc;
