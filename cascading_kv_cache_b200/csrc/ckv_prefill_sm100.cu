@@ -1388,6 +1388,8 @@ __global__ void __launch_bounds__(256) prefill_scores_kernel(PrefillParams p) {
         for (int gh = 0; gh < p.G; ++gh) {
             const float *part = p.colpart + ((long long)(b * p.H + kvh * p.G + gh) * p.nQT) * 2 * p.Rpad + r;
             float s = 0.f;
+            // same order of additions, eight loads in flight
+#pragma unroll 8
             for (int i = 2 * qt0; i < 2 * p.nQT; ++i) s += part[(long long)i * p.Rpad];
             v[gh] = rnd<T>(s);
         }
