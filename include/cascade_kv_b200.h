@@ -148,6 +148,12 @@ size_t ckv_attention_workspace_bytes_for(const ckv_config *cfg, int32_t n_tokens
  * cascade/models/flash_attention.py:540-652) with the eager path's exact score
  * definition.
  *
+ * With a 16-bit cache and D = 128 the call is served by tuned kernels: one token by the streaming
+ * decode kernels; a chunk that needs column scores (EMA rule with CKV_ATTN_UPDATE) by the two-pass
+ * tcgen05 kernels, whose probabilities are normalised and rounded exactly where the reference rounds
+ * them; any other chunk by the single-pass tcgen05 kernel.  Everything else, and every call with
+ * CKV_ATTN_FORCE_GENERIC, runs on plain CUDA-core kernels.
+ *
  *   q           [B, H, n_tokens, D]    un-rotated, element strides for b/h/t
  *   key, value  [B, KVH, n_tokens, D]  un-rotated, element strides for b/h/t
  *   rope        [rope_rows, D] cache dtype: row p = (cos(p*f_0..f_{D/2-1}) | sin(...)),
