@@ -455,7 +455,10 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     float *w_q = c_q + 256;                                     // [2 heads][128] EMA weight of each query (one copy per group)
 
     const int warp = threadIdx.x >> 5, lane_id = threadIdx.x & 31;
-    const int qt = blockIdx.x;
+    // query tiles in descending order: the later ones see more keys, and CTAs are handed out in index
+    // order, so the longest ones start first (measured: 2 % on the two-pass kernels; the single-pass
+    // kernel below is 5 % slower that way and keeps the ascending order)
+    const int qt = gridDim.x - 1 - blockIdx.x;
     const int pairs = (p.G + 1) / 2;                            // head pairs per KV head
     const int lane_i = blockIdx.y / pairs, pair = blockIdx.y % pairs;
     const int b = lane_i / p.KVH, kvh = lane_i % p.KVH;
