@@ -3,23 +3,35 @@
 
     python bench.py --gpus N --steps K --warmup W [--impl reference]
 
-Workload (``config.workload`` = "c2_llama8b_decode"): one decode step at Llama-3.1-8B attention
-shapes in bf16 -- batch 16, 32 query / 8 KV heads, head_dim 128, 64 sinks, 8 cascades x 8192 slots
-(65536), cache fully populated, EMA admission rule (beta 0.9999, max head reduction).  A step =
-attention of one new token per sequence over sinks + cache + itself with cache-position RoPE, the
-EMA score update of all slots, and the cascade cache update.  With N > 1 every rank runs the same
-workload on its own GPU (lanes are independent: no data-path collective), so scaling is weak.
+Headline workload (``config.workload`` = "c2_llama8b_decode"): one decode step at Llama-3.1-8B attention
+shapes in bf16 -- batch 16, 32 query / 8 KV heads, head_dim 128, 64 sinks, 8 cascades x 8192 slots (65536),
+cache fully populated, EMA admission rule (beta 0.9999, max head reduction).  A step = attention of one new
+token per sequence over sinks + cache + itself with cache-position RoPE, the EMA score update of all slots,
+and the cascade cache update.
 
-Reported metric: achieved HBM GB/s = algorithmic bytes per step (K and V read once, score cache
-read+written once, q/out/new k,v once) / step time, summed over ranks; ``ms_per_step`` carries the
-latency.  ``e2e`` is the same metric with the step's q/k/v copied from pinned host memory and the
-output copied back inside the timed region.
+With N > 1 the GLOBAL workload is partitioned: lanes (sequence, KV head) are independent, so rank r owns
+sequences [r*16/N, (r+1)*16/N) with exactly the data a single GPU holds for them (no data-path collective;
+``torch.distributed`` only carries the barrier and the max-over-ranks of the times) -> ``"scaling": "strong"``.
+The old behaviour, every rank running the whole batch, is reported next to it as ``weak_replicas``.
 
-``--impl reference`` times the CPU restatement of the reference path (oracle/) on the host cores
-on a bounded sample (one sequence of the batch) of the same workload.
+Reported metric: achieved HBM GB/s = algorithmic bytes of the whole job per step (K and V read once, score
+cache read+written once, q/out/new k,v once) / step time (max over ranks); ``ms_per_step`` carries the latency.
+The timed loop replays CUDA graphs of several consecutive steps (the kernels take every counter from device
+memory, so a step needs nothing from the host).  ``e2e`` is the same metric through the Python call a user
+makes, with the step's q/k/v copied from pinned host memory and the output copied back inside the timed region.
+
+Further keys of the same JSON line: ``sustained`` (1000 steps, as the configuration is written), ``c4`` (the
+Qwen2-7B decode configuration, batch 32 split over the ranks), ``prefill`` / ``prefill_stride_rule`` (a
+4096-token chunk over the full 4 x 8192 cache at the c3 shapes, KV heads split over the ranks),
+``prefill_stream`` (c3 as written: 1,048,576 tokens in 256 chunks from an empty cache), ``host_us_per_call``,
+``cpu_baseline`` (the CPU restatement of the reference path under oracle/ on the host cores, bounded samples).
+
+``--impl reference`` times that CPU restatement alone, on all host threads, on a bounded sample of the same
+workload (the reference is a Python project and does not travel to the GPU box).
 """
 import argparse
 import json
+import math
 import os
 import subprocess
 import sys
@@ -38,18 +50,32 @@ WORKLOADS = {
     "c4_qwen2_decode": dict(B=32, H=28, KVH=4, D=128, NS=4, W=2048, C=8, theta=1000000.0, beta=0.9999,
                             admission="stride", head_reduction="max", seed=3),
 }
+PREFILL = dict(B=1, H=32, KVH=8, D=128, NS=4, W=8192, C=4, K=4096, theta=500000.0, beta=0.9999,
+               admission="ema", head_reduction="max", seed=2)
 METRIC = "decode_attn_cache_update_hbm_gbs"
 UNIT = "GB/s"
 
 
-def measured_peak_hbm():
+def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         try:
-            return float(json.load(open(path))["hbm_gbs"]), "measured"
+            d = json.load(open(path))
+            return dict(hbm=float(d["hbm_gbs"]), tf=float(d["bf16_tflops"]),
+                        tf_sustained=float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), kind="measured")
         except Exception:
             pass
-    return 6650.0, "fallback"
+    return dict(hbm=6650.0, tf=1590.0, tf_sustained=1400.0, kind="fallback")
+
+
+def recorded_dram_traffic(workload, kernel, lanes):
+    """DRAM bytes per launch of ``kernel`` from the committed ncu summary (profiles/dram_traffic.json holds
+    bytes per lane of the captured case; traffic grows in proportion to the lanes a launch covers)."""
+    try:
+        per_lane = json.load(open(os.path.join(ROOT, "profiles", "dram_traffic.json")))[workload][kernel]["bytes_per_lane"]
+        return int(per_lane * lanes)
+    except Exception:
+        return None
 
 
 class ClockSampler:
@@ -139,21 +165,266 @@ class ClockSampler:
         return out
 
 
-def algorithmic_bytes(w):
+class Job:
+    """Rank bookkeeping: barrier, max over ranks, device."""
+
+    def __init__(self):
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        self.dev = None
+        self.dist = None
+
+    def start(self):
+        torch.cuda.set_device(self.local_rank)
+        self.dev = torch.device("cuda", self.local_rank)
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.init_process_group("nccl", device_id=self.dev)
+            self.dist = dist
+
+    def barrier(self):
+        if self.dist is not None:
+            self.dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(self, values):
+        from cascading_kv_cache_b200.dist_utils import max_over_ranks
+        return max_over_ranks(values, device=self.dev)
+
+    def stop(self):
+        if self.dist is not None:
+            self.dist.barrier()
+            self.dist.destroy_process_group()
+
+
+def steps_per_graph(steps, limit=20):
+    """Largest divisor of ``steps`` up to ``limit``: the timed loop replays whole graphs and runs exactly ``steps``."""
+    for g in range(min(steps, limit), 0, -1):
+        if steps % g == 0:
+            return g
+    return 1
+
+
+def timed_steps(job, step, note_seen, steps, warmup, graph=True, sample_clocks=True):
+    """``warmup`` untimed steps, then exactly ``steps`` steps bracketed by barrier + synchronize on both sides,
+    CUDA events on the launching stream.  Returns (ms for all steps, max over ranks; clock summary)."""
+    for i in range(warmup):
+        step(i)
+    torch.cuda.synchronize()
+    G = steps_per_graph(steps) if graph else 1
+    if G > 1:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        cg = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(cg, stream=side):
+            for j in range(G):
+                step(warmup + j)
+        note_seen(-G)                      # capturing ran the host mirror forward, not the device
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+
+        def run(i):
+            cg.replay()
+            note_seen(G)
+        run(0)                             # one untimed replay
+        n_iter = steps // G
+    else:
+        run, n_iter = (lambda i: step(warmup + i)), steps
+    job.barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(job.local_rank) if sample_clocks else None
+    if sampler:
+        sampler.__enter__()
+    job.barrier()
+    ev0.record()
+    for i in range(n_iter):
+        run(i)
+    ev1.record()
+    job.barrier()
+    if sampler:
+        sampler.__exit__()
+    ms = job.max_over_ranks([ev0.elapsed_time(ev1)])[0]
+    return ms, (sampler.summary() if sampler else None), G
+
+
+def decode_bytes(w, B):
     from cascading_kv_cache_b200.synthetic import decode_algorithmic_bytes
-    return decode_algorithmic_bytes(w["B"], w["H"], w["KVH"], w["D"], w["NS"], w["W"] * w["C"],
-                                    ema=w["admission"] == "ema")
+    return decode_algorithmic_bytes(B, w["H"], w["KVH"], w["D"], w["NS"], w["W"] * w["C"], ema=w["admission"] == "ema")
 
 
-def time_cpu_port(w, steps, warmup, batch_sample=1):
+class DecodeCase:
+    """One rank's share of a decode workload: cache, a pool of fresh N(0,1) inputs resident in HBM, the step."""
+
+    def __init__(self, job, w, partition=True, force_generic=False):
+        from cascading_kv_cache_b200 import CascadingKVCache
+        from cascading_kv_cache_b200.dist_utils import shard_lanes
+        from cascading_kv_cache_b200.synthetic import populate_steady_state
+        self.w, self.job, self.force_generic = w, job, force_generic
+        B, H, KVH, D, NS, W, C = (w[k] for k in ("B", "H", "KVH", "D", "NS", "W", "C"))
+        b0, b1 = shard_lanes(B, KVH, job.world, job.rank)["batch"] if partition else (0, B)
+        self.B_local, self.B_global = b1 - b0, (B if partition else B * job.world)
+        dt, dev = torch.bfloat16, job.dev
+        self.cache = CascadingKVCache(W, NS, self.B_local, KVH, D, W * C, device=dev, dtype=dt,
+                                      head_reduction=w["head_reduction"], layers=1, eager_fill=True,
+                                      admission=w["admission"], verbose=False)
+        first = b0 if partition else job.rank * B      # replicas: every rank its own sequences
+        populate_steady_state(self.cache, 0, seed=w["seed"], beta=w["beta"], first_sequence=first)
+        self.pool = 64
+        g = torch.Generator(device=dev).manual_seed(1000 + w["seed"])
+        full = lambda h: torch.randn(self.pool, B, h, 1, D, generator=g, device=dev).to(dt)
+        sl = slice(b0, b1) if partition else slice(0, B)
+        self.qs, self.ks, self.vs = (full(h)[:, sl].contiguous() for h in (H, KVH, KVH))
+        self.out = torch.empty(self.B_local, H, 1, D, device=dev, dtype=dt)
+        self.bytes_local = decode_bytes(w, self.B_local)
+        self.bytes_global = decode_bytes(w, self.B_global)
+
+    def step(self, i):
+        from cascading_kv_cache_b200 import cascade_attention
+        j = i % self.pool
+        cascade_attention(self.qs[j], self.ks[j], self.vs[j], self.cache, 0, rope_theta=self.w["theta"], out=self.out,
+                          force_generic=self.force_generic)
+
+    def note_seen(self, n):
+        self.cache.note_tokens_seen(0, n)
+
+    def run(self, steps, warmup, graph=True):
+        ms, clocks, G = timed_steps(self.job, self.step, self.note_seen, steps, warmup, graph=graph)
+        ms_step = ms / steps
+        return dict(ms_per_step=ms_step, us_per_step=ms_step * 1e3, gbs=self.bytes_global / (ms_step * 1e-3) / 1e9,
+                    batch_per_gpu=self.B_local, steps=steps, steps_per_graph=G, clocks=clocks)
+
+    def run_e2e(self, steps):
+        """Pinned host q/k/v -> device, the call a user makes, output -> host, every step; no graph."""
+        from cascading_kv_cache_b200 import cascade_attention
+        hq, hk, hv = (t.cpu().pin_memory() for t in (self.qs, self.ks, self.vs))
+        hout = torch.empty_like(self.out, device="cpu").pin_memory()
+        dq, dk, dv = (torch.empty_like(t[0]) for t in (self.qs, self.ks, self.vs))
+
+        def e2e_step(i):
+            j = i % self.pool
+            dq.copy_(hq[j], non_blocking=True)
+            dk.copy_(hk[j], non_blocking=True)
+            dv.copy_(hv[j], non_blocking=True)
+            cascade_attention(dq, dk, dv, self.cache, 0, rope_theta=self.w["theta"], out=self.out,
+                              force_generic=self.force_generic)
+            hout.copy_(self.out, non_blocking=True)
+            torch.cuda.current_stream().synchronize()  # the caller reads the result
+
+        ms, _, _ = timed_steps(self.job, e2e_step, self.note_seen, steps, 3, graph=False, sample_clocks=False)
+        ms_step = ms / steps
+        world = self.job.world
+        return {"value": self.bytes_global / (ms_step * 1e-3) / 1e9, "unit": UNIT, "ms_per_step": ms_step,
+                "h2d_bytes_per_step": int(dq.numel() + dk.numel() + dv.numel()) * 2 * world,
+                "d2h_bytes_per_step": int(self.out.numel()) * 2 * world}
+
+    def host_us_per_call(self, calls=200):
+        """Host time to issue one call (marshalling + launches), measured while the GPU keeps up or not: the
+        smaller of the enqueue time and the device time bounds what the host adds per step."""
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for i in range(calls):
+            self.step(i)
+        t1 = time.perf_counter()
+        torch.cuda.synchronize()
+        return (t1 - t0) / calls * 1e6
+
+    def kernel_profile(self, n_steps):
+        from cascading_kv_cache_b200 import profiling
+        k_ms, k_n, k_name = profiling.time_dominant_kernel(self.step, n_steps=n_steps)
+        launches = profiling.last_launch_count()
+        torch.cuda.synchronize()
+        return k_ms, k_name, launches
+
+
+class PrefillCase:
+    """One rank's KV heads of the c3 chunked-prefill workload (batch 1: the lanes to split are the heads)."""
+
+    def __init__(self, job, admission, populate=True):
+        from cascading_kv_cache_b200 import CascadingKVCache
+        from cascading_kv_cache_b200.dist_utils import shard_lanes
+        from cascading_kv_cache_b200.synthetic import populate_steady_state
+        w = self.w = dict(PREFILL, admission=admission)
+        B, H, KVH, D, NS, W, C, K = (w[k] for k in ("B", "H", "KVH", "D", "NS", "W", "C", "K"))
+        h0, h1 = shard_lanes(B, KVH, job.world, job.rank)["kv_heads"]
+        self.job, self.kvh_local, G = job, h1 - h0, H // KVH
+        dt, dev = torch.bfloat16, job.dev
+        self.cache = CascadingKVCache(W, NS, B, self.kvh_local, D, W * C, device=dev, dtype=dt,
+                                      head_reduction=w["head_reduction"], layers=1, eager_fill=True,
+                                      admission=admission, verbose=False)
+        if populate:
+            populate_steady_state(self.cache, 0, seed=w["seed"], beta=w["beta"], first_kv_head=h0, global_kv_heads=KVH)
+        else:
+            self.cache.beta = w["beta"]
+        g = torch.Generator(device=dev).manual_seed(77)
+        self.pool = 3
+        full = lambda h: torch.randn(self.pool, B, h, K, D, generator=g, device=dev).to(dt)
+        self.qs = full(H)[:, :, h0 * G:h1 * G].contiguous()
+        self.ks, self.vs = (full(KVH)[:, :, h0:h1].contiguous() for _ in range(2))
+        self.out = torch.empty(B, self.kvh_local * G, K, D, device=dev, dtype=dt)
+
+    def step(self, i):
+        from cascading_kv_cache_b200 import cascade_attention
+        j = i % self.pool
+        cascade_attention(self.qs[j], self.ks[j], self.vs[j], self.cache, 0, rope_theta=self.w["theta"], out=self.out)
+
+    def note_seen(self, n):
+        self.cache.note_tokens_seen(0, n * self.w["K"])
+
+    def run_full_cache(self, chunks, warm):
+        """Chunks over the fully populated cache: ms per chunk (max over ranks), the attention kernels' share."""
+        from cascading_kv_cache_b200 import profiling
+        from cascading_kv_cache_b200.synthetic import prefill_algorithmic_flops
+        w = self.w
+        ms, clocks, _ = timed_steps(self.job, self.step, self.note_seen, chunks, warm, graph=False)
+        ms_chunk = ms / chunks
+        k_ms, _, k_name = profiling.time_dominant_kernel(self.step, n_steps=3)
+        launches = profiling.last_launch_count()
+        torch.cuda.synchronize()
+        k_ms = self.job.max_over_ranks([k_ms])[0]
+        flops = prefill_algorithmic_flops(w["B"], w["H"], w["D"], w["K"], w["NS"] + w["W"] * w["C"])   # whole job
+        peaks = measured_peaks()
+        n = self.job.world
+        return {"workload": "c3_chunked_prefill_full_cache", "admission": w["admission"], "chunk_tokens": w["K"],
+                "kv_heads_per_gpu": self.kvh_local, "tokens_per_s": w["K"] / (ms_chunk * 1e-3),
+                "ms_per_chunk": ms_chunk, "algorithmic_tflop_per_chunk": flops / 1e12,
+                "tflops": flops / (ms_chunk * 1e-3) / 1e12, "kernel": k_name, "kernel_ms": k_ms,
+                "kernel_tflops": flops / (k_ms * 1e-3) / 1e12, "peak_tflops": peaks["tf"] * n,
+                "peak_kind": peaks["kind"], "kernel_frac_of_peak": flops / (k_ms * 1e-3) / 1e12 / (peaks["tf"] * n),
+                "chunk_frac_of_peak": flops / (ms_chunk * 1e-3) / 1e12 / (peaks["tf"] * n),
+                "launches_per_chunk": launches, "clocks": clocks, "status": self.cache.kernel_status()}
+
+    def run_stream(self, chunks):
+        """The configuration as written: ``chunks`` chunks of 4096 tokens streamed from an EMPTY cache (the
+        eager-fill phase, then the steady state).  Tokens per second over the whole stream."""
+        from cascading_kv_cache_b200.synthetic import prefill_algorithmic_flops
+        w = self.w
+        self.cache.reset(verbose=False)
+        self.cache.beta = w["beta"]
+        ms, clocks, _ = timed_steps(self.job, self.step, self.note_seen, chunks, 0, graph=False)
+        S, K, NS = w["W"] * w["C"], w["K"], w["NS"]
+        flops = sum(prefill_algorithmic_flops(w["B"], w["H"], w["D"], K, min(max(K * c - NS, 0), S) + (NS if c else 0))
+                    for c in range(chunks))
+        peaks = measured_peaks()
+        n = self.job.world
+        return {"workload": "c3_chunked_prefill_stream", "admission": w["admission"], "chunks": chunks,
+                "tokens": chunks * K, "seconds": ms * 1e-3, "tokens_per_s": chunks * K / (ms * 1e-3),
+                "ms_per_chunk": ms / chunks, "algorithmic_tflop": flops / 1e12,
+                "tflops": flops / (ms * 1e-3) / 1e12,
+                "frac_of_burst_peak": flops / (ms * 1e-3) / 1e12 / (peaks["tf"] * n),
+                "frac_of_sustained_peak": flops / (ms * 1e-3) / 1e12 / (peaks["tf_sustained"] * n),
+                "clocks": clocks, "status": self.cache.kernel_status()}
+
+
+# ------------------------------------------------------------------------- CPU legs (oracle/ is the checker)
+def time_cpu_decode(w, steps, warmup, batch_sample):
     """The CPU restatement of the reference path on the host cores: `batch_sample` sequences of the
     workload per step.  Returns (seconds per step, threads, bytes per step)."""
     from oracle.cascade_oracle import OracleCascadingKVCache, cascade_attention_step
-    from cascading_kv_cache_b200.synthetic import decode_algorithmic_bytes, populate_steady_state
+    from cascading_kv_cache_b200.synthetic import populate_steady_state
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
-    S = w["W"] * w["C"]
-    dt = torch.bfloat16
+    S, dt = w["W"] * w["C"], torch.bfloat16
     cache = OracleCascadingKVCache(w["W"], w["NS"], batch_sample, w["KVH"], w["D"], S, dtype=dt,
                                    head_reduction=w["head_reduction"], layers=1, eager_fill=True, beta=w["beta"])
     populate_steady_state(cache, 0, seed=w["seed"], beta=w["beta"])
@@ -169,93 +440,74 @@ def time_cpu_port(w, steps, warmup, batch_sample=1):
         else:
             cascade_attention_step(q, k, v, cache, 0, w["theta"], w["head_reduction"], False, do_update=False)
             cache.update(k, v, 0)
-        dtm = time.perf_counter() - t0
         if it >= warmup:
-            times.append(dtm)
-    nbytes = decode_algorithmic_bytes(batch_sample, w["H"], w["KVH"], w["D"], w["NS"], S,
-                                      ema=w["admission"] == "ema")
-    return sum(times) / len(times), threads, nbytes
+            times.append(time.perf_counter() - t0)
+    return sum(times) / len(times), threads, decode_bytes(w, batch_sample)
 
 
-PREFILL = dict(B=1, H=32, KVH=8, D=128, NS=4, W=8192, C=4, K=4096, theta=500000.0, beta=0.9999,
-               admission="ema", head_reduction="max", seed=2)
-
-
-def measured_peak_tflops():
-    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    if os.path.exists(path):
-        try:
-            d = json.load(open(path))
-            return float(d["bf16_tflops"]), float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured"
-        except Exception:
-            pass
-    return 1590.0, 1400.0, "fallback"
-
-
-def run_prefill_leg(dev, chunks=6, warm=2, admission=None):
-    """Chunked prefill at the c3 shapes (batch 1, 32/8 heads, 4 sinks, 4 x 8192 slots, chunk 4096) on a full
-    cache: attention of the chunk + fused score/cache update per chunk.  ``admission`` "ema" (c3 itself: two
-    passes over the keys, because the column scores need exactly normalised probabilities) or "stride" (the
-    other admission rule at the same shapes: no column scores, one pass)."""
-    from cascading_kv_cache_b200 import CascadingKVCache, cascade_attention, profiling
-    from cascading_kv_cache_b200.synthetic import populate_steady_state, prefill_algorithmic_flops
-    w = dict(PREFILL, admission=admission or PREFILL["admission"])
-    B, H, KVH, D, NS, W, C, K = (w[k] for k in ("B", "H", "KVH", "D", "NS", "W", "C", "K"))
-    S = W * C
-    dt = torch.bfloat16
-    cache = CascadingKVCache(W, NS, B, KVH, D, S, device=dev, dtype=dt, head_reduction=w["head_reduction"],
-                             layers=1, eager_fill=True, admission=w["admission"])
+def time_cpu_prefill_head():
+    """One KV head (with its 4 query heads) of one full-cache c3 chunk on the host cores."""
+    from oracle.cascade_oracle import OracleCascadingKVCache, cascade_attention_step
+    from cascading_kv_cache_b200.synthetic import populate_steady_state
+    w = PREFILL
+    torch.set_num_threads(os.cpu_count() or 1)
+    G, dt = w["H"] // w["KVH"], torch.bfloat16
+    cache = OracleCascadingKVCache(w["W"], w["NS"], 1, 1, w["D"], w["W"] * w["C"], dtype=dt,
+                                   head_reduction=w["head_reduction"], layers=1, eager_fill=True, beta=w["beta"])
     populate_steady_state(cache, 0, seed=w["seed"], beta=w["beta"])
-    g = torch.Generator(device=dev).manual_seed(77)
-    pool = 3
-    qs = torch.randn(pool, B, H, K, D, generator=g, device=dev).to(dt)
-    ks = torch.randn(pool, B, KVH, K, D, generator=g, device=dev).to(dt)
-    vs = torch.randn(pool, B, KVH, K, D, generator=g, device=dev).to(dt)
-    out = torch.empty(B, H, K, D, device=dev, dtype=dt)
-
-    def step(i):
-        j = i % pool
-        cascade_attention(qs[j], ks[j], vs[j], cache, 0, rope_theta=w["theta"], out=out)
-
-    for i in range(warm):
-        step(i)
-    torch.cuda.synchronize()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(dev.index or 0) as clocks:
-        ev0.record()
-        for i in range(chunks):
-            step(i)
-        ev1.record()
-        torch.cuda.synchronize()
-    ms_chunk = ev0.elapsed_time(ev1) / chunks
-    k_ms, _, k_name = profiling.time_dominant_kernel(step, n_steps=3)
-    launches = profiling.last_launch_count()
-    torch.cuda.synchronize()
-    flops = prefill_algorithmic_flops(B, H, D, K, NS + S)
-    burst, sustained, kind = measured_peak_tflops()
-    return {"workload": "c3_chunked_prefill_full_cache", "admission": w["admission"], "chunk_tokens": K,
-            "tokens_per_s": K / (ms_chunk * 1e-3),
-            "ms_per_chunk": ms_chunk, "algorithmic_tflop_per_chunk": flops / 1e12,
-            "tflops": flops / (ms_chunk * 1e-3) / 1e12, "kernel": k_name, "kernel_ms": k_ms,
-            "kernel_tflops": flops / (k_ms * 1e-3) / 1e12, "peak_tflops": burst, "peak_kind": kind,
-            "kernel_frac_of_peak": flops / (k_ms * 1e-3) / 1e12 / burst, "launches_per_chunk": launches,
-            "clocks": clocks.summary(), "status": cache.kernel_status()}
+    g = torch.Generator().manual_seed(5)
+    q = torch.randn(1, G, w["K"], w["D"], generator=g).to(dt)
+    k = torch.randn(1, 1, w["K"], w["D"], generator=g).to(dt)
+    v = torch.randn(1, 1, w["K"], w["D"], generator=g).to(dt)
+    t0 = time.perf_counter()
+    cascade_attention_step(q, k, v, cache, 0, w["theta"], w["head_reduction"], False)
+    return time.perf_counter() - t0
 
 
-def run_reference(args, w, rank, world):
-    if rank != 0:
+def time_cpu_c1():
+    """The reference's own CPU-runnable configuration in full: fp32, B1 H32/KVH8 D128, 4 sinks, 4 x 512 slots,
+    stride rule, 16384 tokens in chunks of 512, then 64 decode steps."""
+    from oracle.cascade_oracle import OracleCascadingKVCache, cascade_attention_step
+    torch.set_num_threads(os.cpu_count() or 1)
+    B, H, KVH, D, NS, W, C, theta = 1, 32, 8, 128, 4, 512, 4, 5e5
+    ref = OracleCascadingKVCache(W, NS, B, KVH, D, W * C, dtype=torch.float32, layers=1, eager_fill=False)
+    g = torch.Generator().manual_seed(0)
+    t_prefill = t_decode = 0.0
+    for n in [512] * 32 + [1] * 64:
+        q = torch.randn(B, H, n, D, generator=g)
+        k = torch.randn(B, KVH, n, D, generator=g)
+        v = torch.randn(B, KVH, n, D, generator=g)
+        t0 = time.perf_counter()
+        cascade_attention_step(q, k, v, ref, 0, theta, None, False, do_update=False)
+        ref.update(k, v, 0)
+        dtm = time.perf_counter() - t0
+        if n > 1:
+            t_prefill += dtm
+        else:
+            t_decode += dtm
+    return {"prefill_tokens_per_s": 16384 / t_prefill, "decode_us_per_step": t_decode / 64 * 1e6,
+            "seconds_total": t_prefill + t_decode}
+
+
+def cpu_sample_size(w):
+    return max(1, w["B"] // 4)
+
+
+def run_reference(args, w, job):
+    if job.rank != 0:
         return
     steps, warmup = max(1, min(args.steps, 3)), max(1, min(args.warmup, 1))
-    sec, threads, nbytes = time_cpu_port(w, steps, warmup)
+    sample = cpu_sample_size(w)
+    sec, threads, nbytes = time_cpu_decode(w, steps, warmup, sample)
     gbs = nbytes / sec / 1e9
+    what = ("CPU restatement of the reference eager attention + cache update (oracle/), %d of %d sequences per step, "
+            "full cache length, %d timed steps" % (sample, w["B"], steps))
     line = {
         "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
-        "warmup": warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": args.workload, "sample": "1 of %d sequences per step" % w["B"]},
-        "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port",
-                         "sample": "CPU restatement of the reference eager attention + cache update (oracle/), "
-                                   "1 of %d sequences per step, full cache length" % w["B"]},
+        "warmup": warmup, "ms_per_step": sec * 1e3, "ms_per_step_full_batch": sec * 1e3 * w["B"] / sample,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": args.workload, "sample": "%d of %d sequences per step" % (sample, w["B"])},
+        "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port", "sample": what},
         "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -268,163 +520,131 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
     ap.add_argument("--workload", default="c2_llama8b_decode", choices=sorted(WORKLOADS))
+    ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
+                    help="N > 1: partition the global batch (strong, default) or run the whole batch on every rank")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--force-generic", action="store_true")
-    ap.add_argument("--batch", type=int, default=0, help="override the batch (smaller cases for profiler captures)")
+    ap.add_argument("--no-graph", action="store_true", help="launch every step from the host instead of replaying graphs")
+    ap.add_argument("--batch", type=int, default=0, help="override the global batch (smaller cases for profiler captures)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiler captures)")
     ap.add_argument("--no-profile", action="store_true", help="skip the per-kernel event timing")
-    ap.add_argument("--no-prefill", action="store_true", help="skip the chunked-prefill leg")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="headline only: skip sustained / c4 / prefill / stream legs (profiler captures)")
     ap.add_argument("--prefill-only", action="store_true", help="run only the chunked-prefill leg (profiler captures)")
     ap.add_argument("--prefill-chunks", type=int, default=6)
     ap.add_argument("--prefill-admission", choices=["ema", "stride"], default="ema")
+    ap.add_argument("--sustained-steps", type=int, default=1000)
+    ap.add_argument("--stream-chunks", type=int, default=256)
     args = ap.parse_args()
     w = dict(WORKLOADS[args.workload])
     if args.batch > 0:
         w["B"] = args.batch
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-
+    job = Job()
     if args.impl == "reference":
-        run_reference(args, w, rank, world)
+        run_reference(args, w, job)
         return
+    job.start()
     if args.prefill_only:
-        torch.cuda.set_device(local_rank)
-        print(json.dumps({"prefill": run_prefill_leg(torch.device("cuda", local_rank), chunks=args.prefill_chunks,
-                                                     warm=1, admission=args.prefill_admission)}), flush=True)
+        res = PrefillCase(job, args.prefill_admission).run_full_cache(args.prefill_chunks, 1)
+        if job.rank == 0:
+            print(json.dumps({"prefill": res}), flush=True)
+        job.stop()
         return
-
-    import torch.distributed as dist
-    from cascading_kv_cache_b200 import CascadingKVCache, cascade_attention
-    from cascading_kv_cache_b200.synthetic import populate_steady_state
-
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
 
     steps, warmup = args.steps, max(args.warmup, 3)
-    B, H, KVH, D, NS, W, C = (w[k] for k in ("B", "H", "KVH", "D", "NS", "W", "C"))
-    S = W * C
-    dt = torch.bfloat16
-    cache = CascadingKVCache(W, NS, B, KVH, D, S, device=dev, dtype=dt, head_reduction=w["head_reduction"],
-                             layers=1, eager_fill=True, admission=w["admission"])
-    populate_steady_state(cache, 0, seed=w["seed"] + rank, beta=w["beta"])
+    graph = not args.no_graph
+    partition = args.scaling == "strong"
+    peaks = measured_peaks()
+    case = DecodeCase(job, w, partition=partition, force_generic=args.force_generic)
+    head = case.run(steps, warmup, graph=graph)
+    e2e = None if args.no_e2e else case.run_e2e(max(3, min(steps, 50)))
 
-    # fresh N(0,1) q/k/v for every step, resident in HBM before the timed region (a pool that is cycled)
-    pool = 64
-    g = torch.Generator(device=dev).manual_seed(1000 + rank)
-    qs = torch.randn(pool, B, H, 1, D, generator=g, device=dev).to(dt)
-    ks = torch.randn(pool, B, KVH, 1, D, generator=g, device=dev).to(dt)
-    vs = torch.randn(pool, B, KVH, 1, D, generator=g, device=dev).to(dt)
-    out = torch.empty(B, H, 1, D, device=dev, dtype=dt)
+    if args.no_profile:
+        k_ms, k_name, launches = head["ms_per_step"], "whole step", 3
+    else:
+        k_ms, k_name, launches = case.kernel_profile(min(steps, 50))
+    k_ms = job.max_over_ranks([k_ms])[0]
+    k_gbs = case.bytes_local / (k_ms * 1e-3) / 1e9
+    lanes_local = case.B_local * w["KVH"]
+    line = {
+        "metric": METRIC, "value": head["gbs"], "unit": UNIT, "n_gpus": job.world, "steps": steps, "warmup": warmup,
+        "ms_per_step": head["ms_per_step"], "us_per_step": head["us_per_step"], "higher_is_better": True,
+        "scaling": args.scaling if job.world > 1 else "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": args.workload, "global_batch": case.B_global, "batch_per_gpu": case.B_local,
+                   "q_heads": w["H"], "kv_heads": w["KVH"], "head_dim": w["D"], "sinks": w["NS"],
+                   "cascades": w["C"], "window": w["W"], "admission": w["admission"],
+                   "partition": "batch over ranks, no data-path collective" if partition else "replicas",
+                   "launch": ("CUDA graphs of %d steps" % head["steps_per_graph"]) if head["steps_per_graph"] > 1
+                   else "one host call per step",
+                   "l2": "inputs larger than L2 (%.2f GB of K/V per GPU per step)" % (case.bytes_local / 1e9),
+                   "path": "generic" if args.force_generic else "tuned"},
+        "gpu_launches": launches * steps * job.world,
+        "clocks": head["clocks"],
+        "roofline": {"bound": "hbm", "achieved": k_gbs, "peak": peaks["hbm"], "unit": "GB/s",
+                     "frac": k_gbs / peaks["hbm"], "peak_kind": peaks["kind"],
+                     "traffic": recorded_dram_traffic(args.workload, k_name, lanes_local),
+                     "kernel": k_name, "kernel_ms": k_ms, "per": "GPU (rank 0's share of the batch)",
+                     "step_frac": head["gbs"] / (peaks["hbm"] * job.world),
+                     "step_frac_of_8tbs": head["gbs"] / (8000.0 * job.world)},
+    }
+    if e2e is not None:
+        line["e2e"] = e2e
+    line["host_us_per_call"] = job.max_over_ranks([case.host_us_per_call()])[0]
 
-    def step(i):
-        j = i % pool
-        cascade_attention(qs[j], ks[j], vs[j], cache, 0, rope_theta=w["theta"], out=out,
-                          force_generic=args.force_generic)
+    if not args.no_extras:
+        # the configuration as written: 1000 steps; long enough for the power cap to act and for >= 100 clock samples
+        sus = case.run(args.sustained_steps, 3, graph=graph)
+        sus["frac_of_copy_peak"] = sus["gbs"] / (peaks["hbm"] * job.world)
+        sus["frac_of_8tbs"] = sus["gbs"] / (8000.0 * job.world)
+        line["sustained"] = sus
+        del case
+        torch.cuda.empty_cache()
+        if job.world > 1 and partition:
+            rep = DecodeCase(job, w, partition=False)
+            r = rep.run(steps, warmup, graph=graph)
+            line["weak_replicas"] = {"value": r["gbs"], "unit": UNIT, "ms_per_step": r["ms_per_step"],
+                                     "batch_per_gpu": rep.B_local, "scaling": "weak"}
+            del rep
+            torch.cuda.empty_cache()
+        if args.workload != "c4_qwen2_decode":
+            w4 = dict(WORKLOADS["c4_qwen2_decode"])
+            c4 = DecodeCase(job, w4, partition=True)
+            r = c4.run(steps, warmup, graph=graph)
+            r["step_frac"] = r["gbs"] / (peaks["hbm"] * job.world)
+            r["host_us_per_call"] = job.max_over_ranks([c4.host_us_per_call()])[0]
+            r["no_graph_ms_per_step"] = c4.run(steps, 3, graph=False)["ms_per_step"]
+            r["e2e"] = c4.run_e2e(max(3, min(steps, 50)))
+            r["workload"] = "c4_qwen2_decode"
+            line["c4"] = r
+            del c4
+            torch.cuda.empty_cache()
+        pf = PrefillCase(job, "ema")
+        line["prefill"] = pf.run_full_cache(args.prefill_chunks, 2)
+        line["prefill_stream"] = pf.run_stream(args.stream_chunks)
+        del pf
+        torch.cuda.empty_cache()
+        line["prefill_stride_rule"] = PrefillCase(job, "stride").run_full_cache(args.prefill_chunks, 2)
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for i in range(warmup):
-        step(i)
-    barrier()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local_rank) as clocks:
-        barrier()
-        ev0.record()
-        for i in range(steps):
-            step(warmup + i)
-        ev1.record()
-        barrier()
-    ms_total = ev0.elapsed_time(ev1)
-
-    # end to end: pinned host inputs -> device, step, output -> host, every step
-    hq, hk, hv = (t.cpu().pin_memory() for t in (qs, ks, vs))
-    hout = torch.empty(B, H, 1, D, dtype=dt).pin_memory()
-    dq, dk, dv = (torch.empty_like(t[0]) for t in (qs, ks, vs))
-    e2e_steps = max(3, min(steps, 50))
-
-    def e2e_step(i):
-        j = i % pool
-        dq.copy_(hq[j], non_blocking=True)
-        dk.copy_(hk[j], non_blocking=True)
-        dv.copy_(hv[j], non_blocking=True)
-        cascade_attention(dq, dk, dv, cache, 0, rope_theta=w["theta"], out=out, force_generic=args.force_generic)
-        hout.copy_(out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()  # the caller reads the result
-
-    ms_e2e_total = float("nan")
-    if not args.no_e2e:
-        for i in range(3):
-            e2e_step(i)
-        barrier()
-        ev2, ev3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        ev2.record()
-        for i in range(e2e_steps):
-            e2e_step(i)
-        ev3.record()
-        barrier()
-        ms_e2e_total = ev2.elapsed_time(ev3)
-
-    from cascading_kv_cache_b200.dist_utils import max_over_ranks
-    ms_total, ms_e2e_total = max_over_ranks([ms_total, ms_e2e_total], device=dev)
-
-    nbytes = algorithmic_bytes(w)
-    ms_step = ms_total / steps
-    ms_e2e = ms_e2e_total / e2e_steps
-    value = world * nbytes / (ms_step * 1e-3) / 1e9
-    e2e_value = world * nbytes / (ms_e2e * 1e-3) / 1e9
-    peak, peak_kind = measured_peak_hbm()
-
-    if rank == 0:
-        from cascading_kv_cache_b200 import profiling
-        if args.no_profile:
-            step(0)
-            k_ms, k_name = ms_step, "whole step"
-        else:
-            k_ms, k_n, k_name = profiling.time_dominant_kernel(step, n_steps=min(steps, 50))
-        launches_per_step = profiling.last_launch_count()
-        torch.cuda.synchronize()
-        prof = {"ms": k_ms, "gbs": nbytes / (k_ms * 1e-3) / 1e9, "kernel": k_name,
-                "traffic": profiling.recorded_dram_traffic(args.workload, k_name)}
-        line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
-            "ms_per_step": ms_step, "us_per_step": ms_step * 1e3, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": args.workload, "batch_per_gpu": B, "q_heads": H, "kv_heads": KVH, "head_dim": D,
-                       "sinks": NS, "cascades": C, "window": W, "admission": w["admission"],
-                       "l2": "inputs larger than L2 (%.2f GB of K/V per step)" % (nbytes / 1e9),
-                       "path": "generic" if args.force_generic else "tuned"},
-            "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e,
-                    "h2d_bytes_per_step": int(dq.numel() + dk.numel() + dv.numel()) * 2,
-                    "d2h_bytes_per_step": int(out.numel()) * 2},
-            "gpu_launches": launches_per_step * steps,
-            "clocks": clocks.summary(),
-            "roofline": {"bound": "hbm", "achieved": prof["gbs"], "peak": peak, "unit": "GB/s",
-                         "frac": prof["gbs"] / peak, "peak_kind": peak_kind, "traffic": prof.get("traffic"),
-                         "kernel": prof["kernel"], "kernel_ms": prof["ms"],
-                         "step_frac": (nbytes / (ms_step * 1e-3) / 1e9) / peak},
-        }
-        if not args.no_prefill:
-            del qs, ks, vs
-            line["prefill"] = run_prefill_leg(dev)
-            line["prefill_stride_rule"] = run_prefill_leg(dev, admission="stride")
-        if not args.no_cpu_baseline:
-            sec, threads, cpu_bytes = time_cpu_port(w, steps=2, warmup=1)
+    if job.rank == 0:
+        if not args.no_cpu_baseline and job.world == 1:
+            sample = cpu_sample_size(w)
+            sec, threads, cpu_bytes = time_cpu_decode(w, steps=2, warmup=1, batch_sample=sample)
             line["cpu_baseline"] = {
                 "value": cpu_bytes / sec / 1e9, "unit": UNIT, "cores": threads, "kind": "port",
-                "ms_per_step_full_batch": sec * 1e3 * B,
-                "sample": "CPU restatement of the reference path (oracle/), 1 of %d sequences per step, "
-                          "2 timed steps after 1 warm-up; full-batch time is the sample x %d" % (B, B)}
+                "ms_per_step_full_batch": sec * 1e3 * w["B"] / sample,
+                "sample": "CPU restatement of the reference path (oracle/), %d of %d sequences per step, 2 timed "
+                          "steps after 1 warm-up; full-batch time is the sample x %g" % (sample, w["B"], w["B"] / sample)}
+            if not args.no_extras:
+                sec_head = time_cpu_prefill_head()
+                line["cpu_baseline"]["prefill"] = {
+                    "tokens_per_s": PREFILL["K"] / (sec_head * PREFILL["KVH"]), "unit": "tokens/s",
+                    "sample": "one KV head (4 query heads) of one full-cache 4096-token chunk: %.2f s; the chunk has "
+                              "8 such heads, so the figure divides by 8 x that time" % sec_head}
+                line["cpu_baseline"]["c1_fp32_stride_stream_in_full"] = time_cpu_c1()
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    job.stop()
 
 
 if __name__ == "__main__":

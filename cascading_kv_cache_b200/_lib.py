@@ -19,12 +19,14 @@ CKV_REDUCE = {"mean": 0, "max": 1, "median": 2}
 CKV_ADMIT = {"stride": 0, "ema": 1}
 CKV_ATTN_UPDATE = 1
 CKV_ATTN_FORCE_GENERIC = 2
+CKV_DENSE_SCORES_FLASH, CKV_DENSE_SCORES_EAGER = 0, 1
 DTYPE_CODE = {torch.float32: CKV_F32, torch.float16: CKV_F16, torch.bfloat16: CKV_BF16}
 
 EXPORTS = ("ckv_abi_version", "ckv_last_error", "ckv_cascade_update", "ckv_update_workspace_bytes",
            "ckv_attention_workspace_bytes", "ckv_attention_workspace_bytes_for",
            "ckv_attention", "ckv_last_launch_count", "ckv_profile_enable", "ckv_profile_read", "ckv_read_status",
-           "ckv_static_scratch_bytes", "ckv_attention_static")
+           "ckv_static_scratch_bytes", "ckv_attention_static", "ckv_static_status", "ckv_advance_counters_host",
+           "ckv_dense_attention_workspace_bytes", "ckv_dense_attention")
 
 
 class CkvConfig(ctypes.Structure):
@@ -60,6 +62,9 @@ def load():
     lib.ckv_last_error.restype = ctypes.c_char_p
     lib.ckv_cascade_update.restype = ctypes.c_int
     lib.ckv_cascade_update.argtypes = [cfgp, stp, vp, vp, i64, i64, i64, vp, i64, i64, i64, i32, vp, sz, vp]
+    lib.ckv_advance_counters_host.restype = ctypes.c_int
+    lib.ckv_advance_counters_host.argtypes = [cfgp, ctypes.POINTER(i64), i64, i64, ctypes.POINTER(i64),
+                                              ctypes.POINTER(i64), ctypes.POINTER(i64)]
     lib.ckv_update_workspace_bytes.restype = sz
     lib.ckv_update_workspace_bytes.argtypes = [cfgp, i32]
     lib.ckv_attention_workspace_bytes.restype = sz
@@ -73,6 +78,14 @@ def load():
     lib.ckv_attention_static.restype = ctypes.c_int
     lib.ckv_attention_static.argtypes = [cfgp, stp, vp, i64, i64, i64, vp, vp, i64, i64, i64, i32, vp, i64, vp, vp,
                                          vp, i64, i64, i64, i32, vp]
+    lib.ckv_dense_attention_workspace_bytes.restype = sz
+    lib.ckv_dense_attention_workspace_bytes.argtypes = [i32, i32, i32]
+    lib.ckv_dense_attention.restype = ctypes.c_int
+    lib.ckv_dense_attention.argtypes = [vp, i64, i64, i64, vp, i64, i64, i64, vp, i64, i64, i64, vp,
+                                        i32, i32, i32, i32, i32, i32, i32, ctypes.c_double, ctypes.c_double, i32,
+                                        vp, vp, vp, i64, i64, i64, vp, vp, sz, vp]
+    lib.ckv_static_status.restype = ctypes.c_int
+    lib.ckv_static_status.argtypes = [ctypes.POINTER(i32)]
     lib.ckv_last_launch_count.restype = ctypes.c_int
     lib.ckv_profile_enable.restype = ctypes.c_int
     lib.ckv_profile_enable.argtypes = [ctypes.c_int]

@@ -20,6 +20,7 @@ Memory layout differences (values are identical to the reference's):
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 from typing import List, Optional, Union
 
@@ -50,6 +51,101 @@ def cascade_every_n(cascade_func: str, cascades: int) -> List[int]:
     return table[cascade_func]()
 
 
+def _one_row(t: torch.Tensor, lead_dims: int):
+    """Pointer source for a lane-invariant state tensor given with the reference's ``[B, H, ...]`` shape.
+    Returns ``(row, broadcast)``: ``row`` is the single row the kernels read and write; ``broadcast`` says
+    whether the tensor really stores one row per lane, in which case the caller copies the row back to
+    every lane after the launch (the views this package's cache exposes have stride 0 and need no copy)."""
+    row = t[(0,) * lead_dims]
+    shared = all(t.stride(i) == 0 or t.size(i) == 1 for i in range(lead_dims))
+    return row, not shared
+
+
+def sink_cache(k, v, s, sink_k, sink_v, sink_mask, sink_pos, cache_k, cache_v, cache_s, mask, pos, og_pos,
+               do_cache, do_cache_every_n, stored_tokens, start_indices, stored_sinks, num_sink, window_size,
+               real_token_idx, max_seq_len, eager_fill, BENCHMARK: bool = False):
+    """The reference's functional update, ``sink_cache(...)`` (cascade/models/cascading_cache.py:962-1028),
+    with the same 23 positional arguments, served by one ``ckv_cascade_update`` call.
+
+    Tensors keep the reference's shapes: ``k, v [N,H,K,D]``, ``s [N,>=H,K]``, sinks ``[N,H,NS,D]``, cache
+    ``[N,H,S,D]``, ``cache_s [N,H,S]``, ``mask/pos/og_pos [N,H,S]``, ``sink_mask/sink_pos [N,H,NS]``, counters
+    ``[N,H,C]`` / ``[N,H]``; ``real_token_idx`` is the device scalar holding the tokens seen so far and is
+    left as it is (the reference's caller advances it, :1346).  ``do_cache`` is accepted and unused, as in
+    the reference kernel.  Lane-invariant tensors (masks, positions, counters) may be the stride-0 views of
+    this package's cache or real per-lane tensors; the latter are updated on lane (0, 0) and copied to the
+    other lanes.  With ``BENCHMARK`` the launch is timed with CUDA events and the time printed (:986-1026).
+    Returns ``(k, v)``."""
+    N, H, K, D = k.shape
+    if v.shape != k.shape:
+        raise ValueError("k and v must have the same shape")
+    if k.device.type != "cuda":
+        raise RuntimeError("sink_cache runs on a CUDA device only (there is no CPU path)")
+    if k.dtype not in _lib.DTYPE_CODE:
+        raise ValueError(f"unsupported dtype {k.dtype}")
+    for name, t in (("cache_k", cache_k), ("cache_v", cache_v), ("cache_s", cache_s), ("og_pos", og_pos)):
+        if not t.is_contiguous():
+            raise ValueError(f"{name} must be contiguous")
+    for name, t in (("sink_k", sink_k), ("sink_v", sink_v)):
+        if t.numel() and not (t.stride(3) == 1 and t.stride(2) == D and t.stride(1) == num_sink * D
+                               and t.stride(0) == H * num_sink * D):
+            raise ValueError(f"{name} must be laid out as [N, H, {num_sink}, {D}] rows")
+    C = stored_tokens.size(-1)
+    if max_seq_len != C * window_size or cache_k.size(2) != max_seq_len:
+        raise ValueError("max_seq_len must equal cascades * window_size and the cache length")
+    lib = _lib.load()
+    dt, dev = k.dtype, k.device
+    conv = lambda t: t if (t.dtype == dt and t.device == dev) else t.to(device=dev, dtype=dt)
+    k2, v2 = conv(k), conv(v)
+    rows16 = lambda t: (t.stride(3) == 1 and t.data_ptr() % 16 == 0
+                        and all((t.stride(i) * t.element_size()) % 16 == 0 for i in range(3)))
+    if not (rows16(k2) and rows16(v2) and k2.stride() == v2.stride()):
+        k2, v2 = k2.contiguous(), v2.contiguous()
+    s_ptr, ss = None, (0, 0, 0)
+    if s is not None:
+        s2 = conv(s)
+        s_ptr, ss = s2.data_ptr(), s2.stride()
+    m8 = mask.view(torch.uint8) if mask.dtype == torch.bool else mask
+    sm8 = sink_mask.view(torch.uint8) if sink_mask.dtype == torch.bool else sink_mask
+    shared = {}
+    for name, t, lead in (("mask", m8, 2), ("sink_mask", sm8, 2), ("pos", pos, 2), ("sink_pos", sink_pos, 2),
+                          ("stored_tokens", stored_tokens, 2), ("start_indices", start_indices, 2),
+                          ("stored_sinks", stored_sinks, 2)):
+        shared[name] = (t,) + _one_row(t, lead)
+    seen = real_token_idx.reshape(-1)[:1].clone()     # the kernel advances its counter; the caller's stays
+    every = do_cache_every_n.to(device=dev, dtype=torch.long).contiguous()
+    cfg = _lib.CkvConfig(batch=N, kv_heads=H, q_heads=H, head_dim=D, num_sinks=int(num_sink), window=int(window_size),
+                         cascades=C, dtype=_lib.DTYPE_CODE[dt], eager_fill=int(bool(eager_fill)), head_reduction=0,
+                         homogeneous_heads=0, admission=_lib.CKV_ADMIT["ema"], beta=1.0)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    st = _lib.CkvLayerState(
+        key_cache=p(cache_k), value_cache=p(cache_v), score_cache=p(cache_s), sink_keys=p(sink_k),
+        sink_values=p(sink_v), mask=p(shared["mask"][1]), sink_mask=p(shared["sink_mask"][1]),
+        pos=p(shared["pos"][1]), og_pos=p(og_pos), sink_pos=p(shared["sink_pos"][1]),
+        stored_tokens=p(shared["stored_tokens"][1]), start_indices=p(shared["start_indices"][1]),
+        stored_sinks=p(shared["stored_sinks"][1]), seen_tokens=p(seen), every_n=p(every))
+    ws, ws_ptr, ws_bytes = None, None, 0
+    if K >= 2:
+        ws_bytes = lib.ckv_update_workspace_bytes(ctypes.byref(cfg), K)
+        ws = torch.empty(ws_bytes + 256, device=dev, dtype=torch.uint8)
+        ws_ptr = (ws.data_ptr() + 255) & ~255
+    if BENCHMARK:
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+    with torch.cuda.device(dev):
+        rc = lib.ckv_cascade_update(ctypes.byref(cfg), ctypes.byref(st), k2.data_ptr(), v2.data_ptr(), k2.stride(0),
+                                    k2.stride(1), k2.stride(2), s_ptr, ss[0], ss[1], ss[2], K, ws_ptr, ws_bytes,
+                                    _lib.current_stream_ptr(dev))
+    _lib.check(rc, "ckv_cascade_update")
+    for name, (t, row, broadcast) in shared.items():
+        if broadcast:
+            t.copy_(row.expand_as(t))
+    if BENCHMARK:
+        ev1.record()
+        torch.cuda.synchronize()
+        print(ev0.elapsed_time(ev1))
+    return k, v
+
+
 class CascadingKVCache(Cache):
     # transformers >= 5 declares these as read-only properties on Cache; the
     # reference assigns them as plain attributes, so shadow them here.
@@ -67,13 +163,13 @@ class CascadingKVCache(Cache):
         heads: int = 16,
         dim: int = 128,
         max_seq_len: Union[int, List[int]] = 32,
-        device: torch.device = "cuda",
+        device: torch.device = "cpu",
         dtype: torch.dtype = torch.float16,
         cascade_func: str = "pow2",
         head_reduction: str = "mean",
         layers: int = 32,
         eager_fill: bool = True,
-        verbose: bool = False,
+        verbose: bool = True,
         admission: str = "ema",
     ) -> None:
         # Cache.__init__ of transformers >= 5 wants layer objects; this cache owns its tensors.
@@ -185,12 +281,17 @@ class CascadingKVCache(Cache):
         self._rope_tables = {}
         self._ema_weights = {}
         self._cfg_cache = {}
+        self._state_cache = [None for _ in range(L)]
+        # host mirror of the lane-invariant counters (sinks, stored[C], start[C]) and the token count
+        # they are valid for; None = unknown, read from the device on first use
+        self._host_counters = [((0, [0] * self.cascades[l], [0] * self.cascades[l]), 0) for l in range(L)]
 
     def reset(self, verbose=True):
         if verbose and self.verbose:
             print(f"RESET CASCADE CACHE {self.cascade_func=}")
         self._seen_tokens = 0
         self._seen_host = [0 for _ in range(self.layers)]
+        self._host_counters = [((0, [0] * self.cascades[l], [0] * self.cascades[l]), 0) for l in range(self.layers)]
         self.seen_tokens_by_layer.zero_()
         for group in (self._stored_tokens, self._start_indices, self._stored_sinks, self._pos, self._sink_pos,
                       self.og_pos, self.key_cache, self.value_cache, self.score_cache, self.sink_keys,
@@ -216,20 +317,34 @@ class CascadingKVCache(Cache):
                 cascades=self.cascades[layer_idx], dtype=_lib.DTYPE_CODE[self.dtype],
                 eager_fill=int(self.eager_fill), head_reduction=_lib.CKV_REDUCE[key[3]],
                 homogeneous_heads=int(homogeneous_heads), admission=_lib.CKV_ADMIT[key[4]], beta=float(self.beta))
+            cfg.ref = ctypes.byref(cfg)     # made once: a decode call then builds no ctypes objects
+            cfg.ws_bytes = {}
             self._cfg_cache[key] = cfg
         return cfg
 
+    def attention_workspace_bytes(self, cfg: _lib.CkvConfig, n_tokens: int, flags: int) -> int:
+        """``ckv_attention_workspace_bytes_for`` with the answer remembered per (config, tokens, flags)."""
+        n = cfg.ws_bytes.get((n_tokens, flags))
+        if n is None:
+            n = cfg.ws_bytes[(n_tokens, flags)] = self._lib.ckv_attention_workspace_bytes_for(cfg.ref, n_tokens, flags)
+        return n
+
     def ckv_state(self, layer_idx: int) -> _lib.CkvLayerState:
+        """The layer's device pointers as the ABI struct, built once per layer and reused while the
+        tensors it points at are the same objects."""
         l = layer_idx
         # score_cache[l] may have been re-assigned from Python (the reference's attention does); re-read pointers
         sc = self.score_cache[l]
+        cached = self._state_cache[l]
+        if cached is not None and cached[1] is sc and cached[2] is self.key_cache[l]:
+            return cached[0]
         if (sc.dtype != self.dtype or not sc.is_contiguous() or sc.device != self.device
                 or tuple(sc.shape) != (self.max_batch_size, self.heads, self.max_seq_len[l])):
             sc = sc.to(device=self.device, dtype=self.dtype).expand(
                 self.max_batch_size, self.heads, self.max_seq_len[l]).contiguous()
             self.score_cache[l] = sc
         p = lambda t: ctypes.c_void_p(t.data_ptr())
-        return _lib.CkvLayerState(
+        st = _lib.CkvLayerState(
             key_cache=p(self.key_cache[l]), value_cache=p(self.value_cache[l]), score_cache=p(sc),
             sink_keys=p(self.sink_keys[l]), sink_values=p(self.sink_values[l]),
             mask=p(self._mask[l]), sink_mask=p(self._sink_mask[l]), pos=p(self._pos[l]), og_pos=p(self.og_pos[l]),
@@ -237,6 +352,16 @@ class CascadingKVCache(Cache):
             start_indices=p(self._start_indices[l]), stored_sinks=p(self._stored_sinks[l]),
             seen_tokens=ctypes.c_void_p(self.seen_tokens_by_layer.data_ptr() + 8 * l),
             every_n=p(self.do_cache_every_n[l]))
+        st.ref = ctypes.byref(st)
+        self._state_cache[l] = (st, sc, self.key_cache[l])
+        return st
+
+    def device_guard(self):
+        """Context that makes the cache's device current: the library launches on the calling
+        thread's current device.  Free when it already is."""
+        if torch.cuda.current_device() == self.device.index:
+            return contextlib.nullcontext()
+        return torch.cuda.device(self.device)
 
     def workspace(self, nbytes: int) -> torch.Tensor:
         if self._workspace is None or self._workspace.numel() < nbytes:
@@ -255,7 +380,8 @@ class CascadingKVCache(Cache):
         if self._workspace is None:
             return 0
         status = ctypes.c_int32(0)
-        _lib.check(self._lib.ckv_read_status(self.workspace_ptr(), ctypes.byref(status)), "ckv_read_status")
+        with self.device_guard():
+            _lib.check(self._lib.ckv_read_status(self.workspace_ptr(), ctypes.byref(status)), "ckv_read_status")
         return int(status.value)
 
     def rope_table(self, theta: float, rows: int) -> torch.Tensor:
@@ -287,8 +413,41 @@ class CascadingKVCache(Cache):
         return w
 
     # --------------------------------------------------------------- interface
+    def invalidate_host_counters(self, layer_idx: Optional[int] = None):
+        """Call after writing the counter tensors directly (tests, synthetic set-ups): the host
+        mirror is re-read from the device the next time it is needed."""
+        for l in (range(self.layers) if layer_idx is None else [layer_idx]):
+            self._host_counters[l] = None
+
+    def host_counters(self, layer_idx: int):
+        """(stored_sinks, stored_tokens[C], start_indices[C]) of a layer without touching the device:
+        the counters depend only on how many tokens the layer has seen, so a host copy is advanced
+        by the same state machine the kernels run (cascading_cache.py:381-726 of the reference, the
+        branches that never look at scores)."""
+        l = layer_idx
+        C = self.cascades[l]
+        entry = self._host_counters[l]
+        if entry is None:       # written from outside: one device read, then tracked on the host again
+            sinks = int(self._stored_sinks[l].item())
+            entry = ((sinks, self._stored_tokens[l].tolist(), self._start_indices[l].tolist()), self._seen_host[l])
+        (sinks, stored, start), at = entry
+        todo = self._seen_host[l] - at
+        if todo > 0:
+            arr = ctypes.c_int64 * C
+            c_stored, c_start, c_sinks = arr(*stored), arr(*start), ctypes.c_int64(sinks)
+            every = arr(*cascade_every_n(self.cascade_func, C))
+            cfg = self.ckv_config(l)
+            _lib.check(self._lib.ckv_advance_counters_host(ctypes.byref(cfg), every, at, todo, c_stored, c_start,
+                                                           ctypes.byref(c_sinks)), "ckv_advance_counters_host")
+            sinks, stored, start = int(c_sinks.value), list(c_stored), list(c_start)
+        self._host_counters[l] = ((sinks, stored, start), self._seen_host[l])
+        return sinks, stored, start
+
     def get_seq_length(self, layer_idx: Optional[int] = 0, cascade_idx: Optional[int] = -1) -> int:
-        return int(self._stored_sinks[layer_idx].item()) + int(self._stored_tokens[layer_idx].sum().item())
+        """Tokens held by the layer (sinks + every cascade), reference cascading_cache.py:1129-1132,
+        from the host mirror of the counters: no device synchronisation."""
+        sinks, stored, _ = self.host_counters(layer_idx)
+        return sinks + sum(stored)
 
     def get_max_length(self) -> Optional[int]:
         return self.max_seq_len[0]
@@ -348,11 +507,13 @@ class CascadingKVCache(Cache):
         ws_ptr, ws_bytes = None, 0
         if K >= 2 and not self.force_serial_update:
             ws_bytes = self._lib.ckv_update_workspace_bytes(ctypes.byref(cfg), K)
-            self.workspace(ws_bytes)
-            ws_ptr = self.workspace_ptr()
-        rc = self._lib.ckv_cascade_update(
-            ctypes.byref(cfg), ctypes.byref(st), k.data_ptr(), v.data_ptr(), k.stride(0), k.stride(1), k.stride(2),
-            s_ptr, ss[0], ss[1], ss[2], K, ws_ptr, ws_bytes, _lib.current_stream_ptr(self.device))
+            # the first 256 bytes of the shared workspace stay the attention calls' status word
+            self.workspace(ws_bytes + 256)
+            ws_ptr = self.workspace_ptr() + 256
+        with self.device_guard():
+            rc = self._lib.ckv_cascade_update(
+                ctypes.byref(cfg), ctypes.byref(st), k.data_ptr(), v.data_ptr(), k.stride(0), k.stride(1),
+                k.stride(2), s_ptr, ss[0], ss[1], ss[2], K, ws_ptr, ws_bytes, _lib.current_stream_ptr(self.device))
         _lib.check(rc, "ckv_cascade_update")
         self.note_tokens_seen(layer_idx, K)
         return self.get_vals(layer_idx)

@@ -47,12 +47,43 @@ void ProfileHook::after(cudaStream_t stream) {
 ProfileHook *active_profile_hook() { return g_profile_on ? &g_hook : nullptr; }
 
 void note_launches(int n) { g_launches += n; }
+void reset_launch_count() { g_launches = 0; }
 
 static int check_state(const ckv_layer_state *st) {
     if (!st) return fail(CKV_E_ARG, "layer state is null");
     if (!st->key_cache || !st->value_cache || !st->score_cache || !st->mask || !st->pos || !st->og_pos ||
         !st->stored_tokens || !st->start_indices || !st->stored_sinks || !st->seen_tokens || !st->every_n)
         return fail(CKV_E_ARG, "layer state has a null pointer");
+    return CKV_OK;
+}
+
+// Every launch goes to the calling thread's current device.  A cache that lives on another device
+// (a process that drives several GPUs and forgot to make the cache's device current) would hand
+// this device pointers it cannot reach: refuse on the host instead of faulting on the GPU.
+static int check_device(const void *device_ptr, const char *what, void *cuda_stream) {
+    // not while the stream is being captured into a graph: the call was checked when it was first made
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing((cudaStream_t)cuda_stream, &capturing) != cudaSuccess) cudaGetLastError();
+    if (capturing != cudaStreamCaptureStatusNone) return CKV_OK;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess) {
+        cudaGetLastError();
+        return CKV_OK;  // no usable device: the first launch reports it
+    }
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, device_ptr) != cudaSuccess) {
+        cudaGetLastError();
+        return CKV_OK;
+    }
+    if (attr.type == cudaMemoryTypeDevice && attr.device != dev)
+        return fail(CKV_E_ARG, "%s lives on device %d but device %d is current: make the cache's device current "
+                               "before the call", what, attr.device, dev);
+    return CKV_OK;
+}
+
+static int check_sinks(const Dims &d, const ckv_layer_state *st) {
+    if (d.NS > 0 && (!st->sink_keys || !st->sink_values || !st->sink_mask || !st->sink_pos))
+        return fail(CKV_E_ARG, "sink buffers are null");
     return CKV_OK;
 }
 
@@ -75,8 +106,8 @@ extern "C" int ckv_cascade_update(const ckv_config *cfg, const ckv_layer_state *
     if (rc != CKV_OK) return rc;
     if (!key || !value) return fail(CKV_E_ARG, "key/value is null");
     if (n_tokens < 1) return fail(CKV_E_ARG, "n_tokens must be at least 1, got %d", n_tokens);
-    if (d.NS > 0 && (!st->sink_keys || !st->sink_values || !st->sink_mask || !st->sink_pos))
-        return fail(CKV_E_ARG, "sink buffers are null");
+    if ((rc = check_sinks(d, st)) != CKV_OK) return rc;
+    if ((rc = check_device(st->key_cache, "key_cache", cuda_stream)) != CKV_OK) return rc;
     g_launches = 0;
     return launch_update(d, st, key, value, kv_stride_b, kv_stride_h, kv_stride_t, scores, s_stride_b, s_stride_h,
                          s_stride_t, n_tokens, workspace, workspace_bytes, (cudaStream_t)cuda_stream);
@@ -102,6 +133,44 @@ extern "C" size_t ckv_attention_workspace_bytes(const ckv_config *cfg, int32_t n
     const size_t a = ckv_attention_workspace_bytes_for(cfg, n_tokens, 0);
     const size_t b = ckv_attention_workspace_bytes_for(cfg, n_tokens, CKV_ATTN_FORCE_GENERIC);
     return a > b ? a : b;
+}
+
+// Host-only: the score-free part of the update state machine (which cascade accepts, which evicts)
+// on host copies of the counters, so that a caller can know them without reading the device.
+extern "C" int ckv_advance_counters_host(const ckv_config *cfg, const int64_t *every_n, int64_t seen_tokens,
+                                         int64_t n_tokens, int64_t *stored_tokens, int64_t *start_indices,
+                                         int64_t *stored_sinks) {
+    Dims d;
+    int rc = make_dims(cfg, &d);
+    if (rc != CKV_OK) return rc;
+    if (!every_n || !stored_tokens || !start_indices || !stored_sinks) return fail(CKV_E_ARG, "null pointer");
+    if (seen_tokens < 0 || n_tokens < 0) return fail(CKV_E_ARG, "negative token count");
+    for (int i = 0; i < d.C; ++i)
+        if (every_n[i] < 1) return fail(CKV_E_ARG, "every_n[%d] must be at least 1", i);
+    int64_t sinks = *stored_sinks;
+    for (int64_t j = 0; j < n_tokens; ++j) {
+        const int64_t rti = seen_tokens + j + 1;
+        if (sinks < d.NS) {
+            sinks += 1;
+            continue;
+        }
+        const bool eager = d.eager_fill && (rti - 1 <= (int64_t)d.S + d.NS);
+        int i = 0;
+        while (i < d.C) {
+            const bool do_i = eager || ((rti - 1 - d.NS) % every_n[i] == 0);   // rti - 1 >= NS here
+            if ((do_i && stored_tokens[i] < d.W) || (!do_i && stored_tokens[i] == 0)) {
+                stored_tokens[i] += 1;
+                break;
+            } else if (do_i) {
+                start_indices[i] = (start_indices[i] + 1) % d.W;
+                i += 1;
+            } else {
+                break;
+            }
+        }
+    }
+    *stored_sinks = sinks;
+    return CKV_OK;
 }
 
 extern "C" int ckv_last_launch_count(void) { return g_launches; }
@@ -154,6 +223,8 @@ extern "C" int ckv_attention(const ckv_config *cfg, const ckv_layer_state *st, c
     if (!q || !key || !value || !out || !rope) return fail(CKV_E_ARG, "q/key/value/out/rope is null");
     if (n_tokens < 1) return fail(CKV_E_ARG, "n_tokens must be at least 1, got %d", n_tokens);
     if (d.NS < 1) return fail(CKV_E_UNSUPPORTED, "attention needs at least one sink token");
+    if ((rc = check_sinks(d, st)) != CKV_OK) return rc;
+    if ((rc = check_device(st->key_cache, "key_cache", cuda_stream)) != CKV_OK) return rc;
     g_launches = 0;
     if (!(flags & CKV_ATTN_FORCE_GENERIC) && decode_tuned_supported(d, n_tokens))
         return launch_decode_tuned(d, st, q, q_stride_b, q_stride_h, key, value, kv_stride_b, kv_stride_h, rope,

@@ -4,13 +4,8 @@
 from __future__ import annotations
 
 import ctypes
-import json
-import os
 
 from . import _lib
-
-_TRAFFIC_FILE = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "profiles",
-                             "dram_traffic.json")
 
 
 def time_dominant_kernel(run_step, n_steps: int = 20):
@@ -31,12 +26,3 @@ def time_dominant_kernel(run_step, n_steps: int = 20):
 
 def last_launch_count() -> int:
     return int(_lib.load().ckv_last_launch_count())
-
-
-def recorded_dram_traffic(workload: str, kernel: str):
-    """DRAM bytes per launch of ``kernel`` on ``workload`` from the committed ncu summary, or None."""
-    try:
-        table = json.load(open(_TRAFFIC_FILE))
-        return table.get(workload, {}).get(kernel)
-    except Exception:
-        return None

@@ -28,8 +28,14 @@ def steady_state_layout(W: int, C: int, NS: int, seed: int):
     return start, stored, pos, og, seen
 
 
-def populate_steady_state(cache, layer: int = 0, seed: int = 1, beta: float = 0.9999):
-    """Fill ``cache`` in place (works for CUDA and CPU tensor lists alike)."""
+def populate_steady_state(cache, layer: int = 0, seed: int = 1, beta: float = 0.9999, first_sequence: int = 0,
+                          first_kv_head: int = 0, global_kv_heads: int = 0):
+    """Fill ``cache`` in place (works for CUDA and CPU tensor lists alike).
+
+    Every lane (sequence, KV head) draws its keys, values and prior scores from its own generator, seeded by
+    ``seed`` and the lane's GLOBAL index.  A rank that owns sequences ``first_sequence ...`` or KV heads
+    ``first_kv_head ...`` of a larger job (``global_kv_heads`` heads per sequence) therefore holds exactly the
+    slice of the data that a single-GPU run holds for those lanes."""
     l = layer
     W = cache.window_length[l] if isinstance(cache.window_length, (list, tuple)) else cache.window_length
     S = cache.max_seq_len[l] if isinstance(cache.max_seq_len, (list, tuple)) else cache.max_seq_len
@@ -37,13 +43,16 @@ def populate_steady_state(cache, layer: int = 0, seed: int = 1, beta: float = 0.
     start, stored, pos, og, seen = steady_state_layout(W, C, NS, seed)
     kc = cache.key_cache[l]
     dev, dt = kc.device, kc.dtype
-    g = torch.Generator(device=dev).manual_seed(seed)
-    # generate lane by lane to bound the fp32 temporaries
-    for t in (cache.key_cache[l], cache.value_cache[l], cache.sink_keys[l], cache.sink_values[l]):
-        for b in range(t.size(0)):
-            t[b].copy_(torch.randn(t[b].shape, generator=g, device=dev, dtype=torch.float32))
+    g = torch.Generator(device=dev)
+    kvh_global = global_kv_heads or kc.size(1)
     sc = cache.score_cache[l]
-    sc.copy_(torch.rand(sc.shape, generator=g, device=dev, dtype=torch.float32) * (1 - beta))
+    # lane by lane: bounds the fp32 temporaries and makes the data independent of how lanes are sharded
+    for b in range(kc.size(0)):
+        for h in range(kc.size(1)):
+            g.manual_seed(seed * 1000003 + (first_sequence + b) * kvh_global + first_kv_head + h)
+            for t in (cache.key_cache[l], cache.value_cache[l], cache.sink_keys[l], cache.sink_values[l]):
+                t[b, h].copy_(torch.randn(t[b, h].shape, generator=g, device=dev, dtype=torch.float32))
+            sc[b, h].copy_(torch.rand(sc[b, h].shape, generator=g, device=dev, dtype=torch.float32) * (1 - beta))
 
     def base(name):
         return getattr(cache, "_" + name)[l] if hasattr(cache, "_" + name) else None
@@ -70,6 +79,7 @@ def populate_steady_state(cache, layer: int = 0, seed: int = 1, beta: float = 0.
     if isinstance(cache.seen_tokens_by_layer, torch.Tensor):
         cache.seen_tokens_by_layer[l] = seen
         cache._seen_host[l] = seen
+        cache.invalidate_host_counters(l)   # the counters were written directly
     else:
         cache.seen_tokens_by_layer[l] = seen
     cache.beta = beta

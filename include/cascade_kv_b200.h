@@ -124,6 +124,18 @@ int ckv_cascade_update(const ckv_config *cfg, const ckv_layer_state *st,
                        const void *scores, int64_t s_stride_b, int64_t s_stride_h, int64_t s_stride_t,
                        int32_t n_tokens, void *workspace, size_t workspace_bytes, void *cuda_stream);
 
+/*
+ * Host-only helper (no device work): advance HOST copies of the lane-invariant counters by n_tokens
+ * tokens, starting from a layer that has seen seen_tokens tokens.  Which cascade accepts or evicts a
+ * token depends only on the token's index and the counters, never on scores, so a caller can mirror
+ * them and answer CascadingKVCache.get_seq_length() (cascade/models/cascading_cache.py:1129-1132,
+ * two .item() synchronisations per call in the reference) without reading the device.
+ *   every_n, stored_tokens, start_indices  [cascades] host int64;  stored_sinks  [1] host int64
+ */
+int ckv_advance_counters_host(const ckv_config *cfg, const int64_t *every_n /* host */, int64_t seen_tokens,
+                              int64_t n_tokens, int64_t *stored_tokens /* host */,
+                              int64_t *start_indices /* host */, int64_t *stored_sinks /* host */);
+
 /* Bytes of scratch ckv_attention needs for calls of up to n_tokens query tokens, whatever their
  * flags: the larger of the tuned path's need and the generic path's.  (The reference has no
  * counterpart: its eager path allocates the logits and the concatenated, repeated and rotated
@@ -178,6 +190,39 @@ int ckv_attention(const ckv_config *cfg, const ckv_layer_state *st,
                   int32_t flags, void *cuda_stream);
 
 /*
+ * Attention over keys and values that the caller has already rotated and laid out as one dense key
+ * axis, with per-column attention scores.  Replaces the reference's functional
+ * attention(q, k, v, causal, sm_scale, mask, beta) -> (o, scores)
+ * (cascade/models/flash_attention.py:540-652, :713), and serves CascadeAttention.cascade_attn_flash /
+ * cascade_attn_eager when they are called with materialised tensors
+ * (cascade/models/cascade_attention.py:202-229, :250-340).
+ *
+ *   q      [B, H, n_ctx, D], k, v [B, kv_heads, n_kv, D] (kv_heads divides H; element strides for b/h/t)
+ *   mask   [n_kv - n_ctx] uint8, 1 = column masked.  The first n_kv - n_ctx columns obey `mask`, the
+ *          last n_ctx columns are causal (column i visible to query rows >= i), as in the reference
+ *          kernel (flash_attention.py:54-61), whatever its `causal` argument says.
+ *   out    [B, H, n_ctx, D] with element strides; scores [B, H, n_kv] contiguous in the same dtype, or NULL
+ *   score_mode CKV_DENSE_SCORES_FLASH: scores[col] = sum_q p[q,col] (1-beta) beta^(n_ctx-1-q), logits
+ *          q.k*sm_scale in fp32 (flash_attention.py:63-100; the reference approximates the row
+ *          normaliser while it streams, this kernel uses the exact one).
+ *          CKV_DENSE_SCORES_EAGER: the eager path's definition and rounding points
+ *          (cascade_attention.py:284-323): logits and probabilities rounded to the tensor dtype, masked
+ *          columns weighted by ema_w_cache[q] (fp32 [n_ctx]), causal columns by ema_w_new[q - i]
+ *          (dtype [n_ctx]) with every product rounded.
+ *   workspace  ckv_dense_attention_workspace_bytes(B, H, n_ctx) bytes, 256-byte aligned
+ */
+enum { CKV_DENSE_SCORES_FLASH = 0, CKV_DENSE_SCORES_EAGER = 1 };
+size_t ckv_dense_attention_workspace_bytes(int32_t batch, int32_t q_heads, int32_t n_ctx);
+int ckv_dense_attention(const void *q, int64_t q_stride_b, int64_t q_stride_h, int64_t q_stride_t,
+                        const void *k, int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_t,
+                        const void *v, int64_t v_stride_b, int64_t v_stride_h, int64_t v_stride_t,
+                        const uint8_t *mask, int32_t batch, int32_t q_heads, int32_t kv_heads,
+                        int32_t n_ctx, int32_t n_kv, int32_t head_dim, int32_t dtype, double sm_scale,
+                        double beta, int32_t score_mode, const float *ema_w_cache, const void *ema_w_new,
+                        void *out, int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_t,
+                        void *scores, void *workspace, size_t workspace_bytes, void *cuda_stream);
+
+/*
  * ckv_attention for callers that may not allocate device memory.
  * (No counterpart in the reference, whose Python layer allocates freely through torch.)
  *
@@ -209,6 +254,10 @@ int ckv_attention_static(const ckv_config *cfg, const ckv_layer_state *st,
                          const float *ema_w_cache, const void *ema_w_new,
                          void *out, int64_t o_stride_b, int64_t o_stride_h, int64_t o_stride_t,
                          int32_t flags, void *cuda_stream);
+/* ckv_read_status for the built-in array of the current device: a caller of ckv_attention_static has
+ * no workspace pointer to pass.  Copies four bytes to the host (synchronises); allocates nothing.
+ * (No counterpart in the reference.) */
+int ckv_static_status(int32_t *status /* host */);
 
 /* Number of kernels the calling thread's last ckv_attention / ckv_cascade_update call launched. */
 int ckv_last_launch_count(void);
@@ -229,7 +278,8 @@ int ckv_profile_read(double *total_ms /* host */, int32_t *launches /* host */, 
  * the last call gave up on a bounded wait; non-zero = a pipeline wait ran out and the results of
  * that call are invalid: low byte 1 (decode kernels) or 2 (prefill kernels, bits 8 and up then hold
  * the source line of the wait that gave up), 3 = the prefill kernel found its shared-memory window
- * misaligned.  (No counterpart in the reference: its kernels have no waits.)
+ * misaligned.  (No counterpart in the reference: its kernels have no waits.)  Callers of
+ * ckv_attention_static, who hold no workspace pointer, use ckv_static_status instead.
  */
 int ckv_read_status(const void *workspace, int32_t *status /* host */);
 

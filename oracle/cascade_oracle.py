@@ -202,6 +202,15 @@ def apply_rope(x: torch.Tensor, pos: torch.Tensor, theta: float) -> torch.Tensor
     return (x * cos[None, None]) + (rotate_half(x) * sin[None, None])
 
 
+def apply_rope_per_lane(x: torch.Tensor, pos: torch.Tensor, theta: float) -> torch.Tensor:
+    """x [B,h,len,D] rotated at ``pos`` [B,h,len]: every lane at its own positions (the
+    ``do_og_pos`` branch, cascade_attention.py:161-164)."""
+    B, h, n, D = x.shape
+    cos, sin = rope_cos_sin(pos.reshape(-1), D, theta, x.dtype)
+    cos, sin = cos.view(B, h, n, D), sin.view(B, h, n, D)
+    return (x * cos) + (rotate_half(x) * sin)
+
+
 # ---------------------------------------------------------------------- attention
 
 def _reduce_heads(x: torch.Tensor, how: str, dim: int, keepdim: bool = False) -> torch.Tensor:
@@ -216,7 +225,7 @@ def _reduce_heads(x: torch.Tensor, how: str, dim: int, keepdim: bool = False) ->
 
 def cascade_attention_step(q, k, v, cache: OracleCascadingKVCache, layer_idx: int = 0, theta: float = 500000.0,
                            head_reduction: Optional[str] = None, homogeneous_heads: bool = False,
-                           do_update: bool = True):
+                           do_update: bool = True, do_og_pos: bool = False):
     """One attention call over the cascading cache plus the cache update.
 
     q [B,H,K,D]; k,v [B,KVH,K,D] (un-rotated), all in the cache dtype.  Returns
@@ -232,16 +241,18 @@ def cascade_attention_step(q, k, v, cache: OracleCascadingKVCache, layer_idx: in
     beta = cache.beta
 
     first_it = cache.seen_tokens_by_layer[layer_idx] == 0
-    sink_k, sink_v, sink_pos, sink_mask, ck, cv, key_pos, key_mask, _ = cache.get_vals(layer_idx)
+    sink_k, sink_v, sink_pos, sink_mask, ck, cv, key_pos, key_mask, og_pos = cache.get_vals(layer_idx)
     max_pos = 0
     if not first_it:
-        max_pos = int(max(sink_pos.amax().item(), key_pos.amax().item())) + 1
+        # :141-148: with do_og_pos the keys keep the stream index they arrived with
+        top = og_pos.amax().item() if do_og_pos else key_pos.amax().item()
+        max_pos = int(max(sink_pos.amax().item() if sink_pos.numel() else 0, top)) + 1
     query_pos = torch.arange(K, dtype=torch.long) + max_pos
 
     q_r = apply_rope(q, query_pos, theta)
     k_r = apply_rope(k, query_pos, theta)
     sk_r = apply_rope(sink_k, sink_pos.reshape(-1), theta)
-    ck_r = apply_rope(ck, key_pos.reshape(-1), theta)
+    ck_r = apply_rope_per_lane(ck, og_pos, theta) if do_og_pos else apply_rope(ck, key_pos.reshape(-1), theta)
 
     rep = lambda t: t.repeat_interleave(G, dim=1) if G > 1 else t
     scale = 1.0 / math.sqrt(D)

@@ -76,3 +76,52 @@ def test_cache_refuses_cpu_device_and_bad_configs():
     with pytest.raises(ValueError):
         CascadingKVCache(8, 4, 1, 2, 16, 32, device="cuda", dtype=torch.float32, layers=1, cascade_func="nope")
     assert cascade_every_n("pow2", 4) == [1, 2, 4, 8]
+
+
+def test_host_counters_follow_the_update_state_machine():
+    """ckv_advance_counters_host (what get_seq_length reads instead of the device) against the oracle's
+    counters on streams fed in ragged calls, with and without eager fill, several admission schedules."""
+    import numpy as np
+    from cascading_kv_cache_b200 import _lib
+    from oracle.cascade_oracle import OracleCascadingKVCache, cascade_every_n
+    lib = _lib.load()
+    rng = np.random.default_rng(3)
+    for (W, C, NS, func, eager) in [(4, 4, 2, "pow2", False), (8, 3, 3, "pow2", True), (4, 4, 0, "pow3", False),
+                                    (8, 4, 1, "iplus1", True), (16, 2, 5, "1-then-2", False)]:
+        ref = OracleCascadingKVCache(W, NS, 1, 1, 4, W * C, dtype=torch.float32, cascade_func=func, layers=1,
+                                     eager_fill=eager)
+        cfg = _lib.CkvConfig(batch=1, kv_heads=1, q_heads=1, head_dim=4, num_sinks=NS, window=W, cascades=C, dtype=0,
+                             eager_fill=int(eager))
+        arr = ctypes.c_int64 * C
+        stored, start, sinks = arr(), arr(), ctypes.c_int64(0)
+        every = arr(*cascade_every_n(func, C))
+        seen = 0
+        for _ in range(12):
+            n = int(rng.integers(1, 40))
+            x = torch.randn(1, 1, n, 4)
+            ref.update(x, x, 0)
+            assert lib.ckv_advance_counters_host(ctypes.byref(cfg), every, seen, n, stored, start,
+                                                 ctypes.byref(sinks)) == 0
+            seen += n
+            assert list(stored) == ref.stored_tokens[0][0, 0].tolist()
+            assert list(start) == ref.start_indices[0][0, 0].tolist()
+            assert sinks.value == int(ref.stored_sinks[0][0, 0])
+
+
+def test_attention_refuses_null_sink_buffers():
+    from cascading_kv_cache_b200 import _lib
+    lib = _lib.load()
+    cfg = _lib.CkvConfig(batch=1, kv_heads=1, q_heads=1, head_dim=8, num_sinks=2, window=4, cascades=2, dtype=0)
+    one = ctypes.c_void_p(16)       # any non-null value: the call must stop at the argument checks
+    st = _lib.CkvLayerState(**{n: one for n, _ in _lib.CkvLayerState._fields_})
+    st.sink_keys = None
+    rc = lib.ckv_attention(ctypes.byref(cfg), ctypes.byref(st), one, 0, 0, 0, one, one, 0, 0, 0, 1, one, 100, None, None,
+                           one, 0, 0, 0, None, 0, 0, None)
+    assert rc == -1 and b"sink" in lib.ckv_last_error()
+    cfg.num_sinks = 0
+    rc = lib.ckv_attention(ctypes.byref(cfg), ctypes.byref(st), one, 0, 0, 0, one, one, 0, 0, 0, 1, one, 100, None, None,
+                           one, 0, 0, 0, None, 0, 0, None)
+    assert rc == -2 and b"sink" in lib.ckv_last_error()
+    assert lib.ckv_dense_attention_workspace_bytes(1, 2, 16) > 0
+    status = ctypes.c_int32(0)
+    assert lib.ckv_static_status(None) == -1

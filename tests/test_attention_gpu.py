@@ -35,14 +35,32 @@ def _gpu_cache(rule):
 
 
 def close_enough(got, want, is16):
+    """16-bit outputs: max-abs error <= 2e-2, and "1e-2 relative" read two ways -- the error's norm over the
+    output's norm <= 1e-2, and element by element on the entries that are not tiny (|want| > 0.1), where
+    one unit in the last place of bf16 is already up to 0.8 %: at least 99 % of them within 1e-2."""
     err = (got - want).abs()
     if not is16:
         return err.max().item() <= TOL_F32, err.max().item()
     rel = err.norm().item() / max(want.norm().item(), 1e-12)
-    return (err.max().item() <= TOL_16["max_abs"] and rel <= TOL_16["rel"]), (err.max().item(), rel)
+    big = want.abs() > 0.1
+    within = ((err[big] / want.abs()[big]) <= TOL_16["rel"]).float().mean().item() if bool(big.any()) else 1.0
+    return (err.max().item() <= TOL_16["max_abs"] and rel <= TOL_16["rel"] and within >= 0.99), \
+        (err.max().item(), rel, within)
 
 
-@pytest.mark.parametrize("name", sorted(ATTN))
+def slot_report(got_og, want_og, got_sc, want_sc, valid, limit=20):
+    """Slots (lane, slot) that hold different tokens, each with the two competing scores: the token the
+    GPU kept, its score there, the token the reference kept, its score there."""
+    diff = ((got_og != want_og) & valid).nonzero()
+    rows = []
+    for idx in diff[:limit]:
+        i = tuple(int(x) for x in idx)
+        rows.append(dict(slot=i, gpu_token=int(got_og[i]), gpu_score=float(got_sc[i]), ref_token=int(want_og[i]),
+                         ref_score=float(want_sc[i])))
+    return dict(divergent=int(diff.size(0)), of=int(valid.sum()), first=rows)
+
+
+@pytest.mark.parametrize("name", [n for n in sorted(ATTN) if not bool(ATTN[n]["do_og_pos"])])
 @pytest.mark.parametrize("force_generic", [True, False], ids=["generic", "tuned"])
 def test_golden_reference_outputs(name, force_generic):
     st = ATTN[name]
@@ -60,6 +78,12 @@ def test_golden_reference_outputs(name, force_generic):
         if rule == "ema":
             assert np.allclose(cache.score_cache[0].cpu().numpy()[:, :, valid], st["score_cache"][:, :, valid],
                                rtol=2e-3, atol=1e-7)
+    else:
+        # 16 bits, free-running against the reference's own stream: the same tokens in at least 99.9 % of
+        # the valid slots (a slot holds the same token when it holds the same key row)
+        got_k = cache.key_cache[0].float().cpu().numpy()[:, :, valid]
+        same = np.all(got_k == st["key_cache"][:, :, valid], axis=-1)
+        assert same.mean() >= 0.999, (same.mean(), np.argwhere(~same)[:20].tolist())
 
 
 STREAMS = [
@@ -120,7 +144,7 @@ def test_streams_against_oracle(spec, force_generic):
     # starts from the oracle's state, outputs and admissions of that step are compared, then the GPU
     # cache is re-synchronised.  Everything else is compared free-running.
     teacher = is16 and rule == "ema"
-    step_agree, score_bits = [], []
+    step_agree, score_bits, divergent = [], [], []
     for n in steps:
         q = torch.randn(B, H, n, D, generator=g).to(dtype)
         k = torch.randn(B, KVH, n, D, generator=g).to(dtype)
@@ -139,6 +163,9 @@ def test_streams_against_oracle(spec, force_generic):
             assert torch.equal(cache.pos[0].cpu()[valid], ref.pos[0][valid])
             if bool(valid.any()):      # a first chunk shorter than the sink count leaves the cascades empty
                 step_agree.append((cache.og_pos[0].cpu()[valid] == ref.og_pos[0][valid]).float().mean().item())
+                if step_agree[-1] < 1.0:
+                    divergent.append(slot_report(cache.og_pos[0].cpu(), ref.og_pos[0], cache.score_cache[0].float().cpu(),
+                                                 ref.score_cache[0].float(), valid))
                 same = (cache.og_pos[0].cpu() == ref.og_pos[0]) & valid
                 score_bits.append((cache.score_cache[0].cpu()[same] == ref.score_cache[0][same]).float().mean().item())
             copy_state_to_gpu(ref, cache)
@@ -152,7 +179,7 @@ def test_streams_against_oracle(spec, force_generic):
         # per step, the tokens admitted / kept agree on (almost) every slot, and the EMA scores of the
         # slots that hold the same token are the same 16 bits (what is left differs by one rounding)
         if step_agree:
-            assert min(step_agree) >= 0.998 and sum(step_agree) / len(step_agree) >= 0.9995, step_agree
+            assert min(step_agree) >= 0.999, (step_agree, divergent)
             assert min(score_bits) >= 0.99, score_bits
         return
     if not bool(valid.any()):       # a stream shorter than the sink count never reaches the cascades
@@ -161,7 +188,44 @@ def test_streams_against_oracle(spec, force_generic):
     if rule == "stride":
         assert agree == 1.0
     else:
-        assert agree >= 0.999, agree
+        assert agree >= 0.999, (agree, slot_report(cache.og_pos[0].cpu(), ref.og_pos[0],
+                                                   cache.score_cache[0].float().cpu(), ref.score_cache[0].float(), valid))
+
+
+FREE_RUNNING_16 = [
+    # B,H,KVH, NS,W,C, steps, dtype, red, beta: EMA rule, 16 bits, never re-synchronised
+    (1, 8, 2, 4, 64, 4, [64] * 6 + [1] * 6, torch.bfloat16, "max", 0.999),
+    (2, 8, 2, 4, 128, 2, [100] * 4 + [1] * 4, torch.bfloat16, "mean", 0.99),
+    (1, 4, 2, 8, 256, 2, [300, 300, 1, 1, 1], torch.float16, "max", 0.999),
+]
+
+
+@pytest.mark.parametrize("spec", FREE_RUNNING_16, ids=lambda s: f"B{s[0]}H{s[1]}W{s[4]}C{s[5]}-{str(s[7])[6:]}-{s[8]}")
+def test_free_running_ema_streams_in_16_bits(spec):
+    """EMA rule in 16 bits without re-synchronisation: at the end the GPU cache and the oracle hold the same
+    token in at least 99.9 % of the valid slots; every divergent slot is reported with its two scores."""
+    from cascading_kv_cache_b200 import CascadingKVCache, cascade_attention
+    B, H, KVH, NS, W, C, steps, dtype, red, beta = spec
+    D, theta = 128, 5e5
+    g = torch.Generator().manual_seed(W + H)
+    cache = CascadingKVCache(W, NS, B, KVH, D, W * C, device="cuda:0", dtype=dtype, head_reduction=red, layers=1,
+                             eager_fill=True, verbose=False)
+    ref = OracleCascadingKVCache(W, NS, B, KVH, D, W * C, dtype=dtype, head_reduction=red, layers=1, eager_fill=True,
+                                 beta=beta)
+    cache.beta = beta
+    for n in steps:
+        q = torch.randn(B, H, n, D, generator=g).to(dtype)
+        k = torch.randn(B, KVH, n, D, generator=g).to(dtype)
+        v = torch.randn(B, KVH, n, D, generator=g).to(dtype)
+        want = cascade_attention_step(q, k, v, ref, 0, theta, red, False)
+        got = cascade_attention(q.cuda(), k.cuda(), v.cuda(), cache, 0, rope_theta=theta).float().cpu()
+        ok, err = close_enough(got, want.float(), True)
+        assert ok, (n, err)
+    valid = ~ref.mask[0]
+    report = slot_report(cache.og_pos[0].cpu(), ref.og_pos[0], cache.score_cache[0].float().cpu(),
+                         ref.score_cache[0].float(), valid)
+    assert report["divergent"] <= 1e-3 * report["of"], report
+    assert cache.kernel_status() == 0
 
 
 def test_attention_without_update_leaves_state_untouched():
@@ -192,6 +256,7 @@ def copy_state_to_gpu(ref, cache, l=0):
     cache._sink_mask[l].copy_(ref.sink_mask[l][0, 0])
     cache.seen_tokens_by_layer[l] = ref.seen_tokens_by_layer[l]
     cache._seen_host[l] = ref.seen_tokens_by_layer[l]
+    cache.invalidate_host_counters(l)
     cache.beta = ref.beta
 
 

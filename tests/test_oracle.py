@@ -17,6 +17,7 @@ def _cases(npz):
 
 UPDATE = _cases(np.load(os.path.join(GOLD, "update_stride_slow.npz")))
 ATTN = _cases(np.load(os.path.join(GOLD, "attention_eager_ref.npz")))
+SCORED = _cases(np.load(os.path.join(GOLD, "update_scores_kernel_source.npz")))
 
 
 def check_against_slow(cache, st, NS):
@@ -61,6 +62,57 @@ def test_update_oracle_matches_reference_slow_cache(name, mode):
     for a, b in zip(cuts[:-1], cuts[1:]):
         cache.update(k[:, :, a:b], v[:, :, a:b], 0)
     check_against_slow(cache, st, NS)
+
+
+_DT = {"torch.float32": torch.float32, "torch.float16": torch.float16, "torch.bfloat16": torch.bfloat16}
+
+
+def check_against_reference_cache(cache, st):
+    """Compare an oracle-layout cache, bit for bit, with a state dump of the reference's own
+    CascadingKVCache (whose update kernel's source produced the dump)."""
+    valid = ~st["mask"].astype(bool)
+    assert np.array_equal(~cache.mask[0].numpy(), valid)
+    assert np.array_equal(~cache.sink_mask[0].numpy(), ~st["sink_mask"].astype(bool))
+    for name in ("stored_tokens", "start_indices", "stored_sinks"):
+        assert np.array_equal(getattr(cache, name)[0].numpy(), st[name]), name
+    assert cache.seen_tokens_by_layer[0] == int(st["seen"])
+    # what a masked slot holds is undefined in both; everything else must be the same bits
+    for name in ("key_cache", "value_cache"):
+        assert np.array_equal(getattr(cache, name)[0].float().numpy()[valid], st[name][valid]), name
+    assert np.array_equal(cache.score_cache[0].float().numpy()[valid], st["score_cache"][valid])
+    assert np.array_equal(cache.og_pos[0].numpy()[valid], st["og_pos"][valid])
+    assert np.array_equal(cache.pos[0].numpy()[valid], st["pos"][valid])
+    sv = ~st["sink_mask"].astype(bool)
+    assert np.array_equal(cache.sink_keys[0].float().numpy()[sv], st["sink_keys"][sv])
+    assert np.array_equal(cache.sink_values[0].float().numpy()[sv], st["sink_values"][sv])
+    assert np.array_equal(cache.sink_pos[0].numpy()[sv], st["sink_pos"][sv])
+
+
+def run_scored_case(st, make_cache, mode):
+    W, C, NS, B, H, D = (int(x) for x in st["cfg"])
+    dtype = _DT[str(st["dtype"])]
+    cache = make_cache(W, NS, B, H, D, W * C, dtype, str(st["cascade_func"]), bool(st["eager_fill"]))
+    k, v, s = (torch.from_numpy(st[n]).to(dtype) for n in ("k", "v", "s"))
+    chunks = [int(x) for x in st["chunks"]] if mode == "same_calls" else [1] * k.size(2)
+    t0 = 0
+    for m in chunks:
+        cache.update(k[:, :, t0:t0 + m], v[:, :, t0:t0 + m], 0, score_states=s[:, :, t0:t0 + m])
+        t0 += m
+    return cache
+
+
+@pytest.mark.parametrize("name", sorted(SCORED))
+@pytest.mark.parametrize("mode", ["same_calls", "token"])
+def test_update_oracle_matches_reference_kernel_source_on_scored_streams(name, mode):
+    """The score-driven branch (an evictee competes with the newest slot of the next cascade,
+    cascading_cache.py:667-726) pinned to the reference's own kernel: streams with frequent score ties,
+    all dtypes, eager fill on and off, calls of one and of many tokens."""
+    st = SCORED[name]
+    make = lambda W, NS, B, H, D, S, dtype, func, eager: OracleCascadingKVCache(
+        window_length=W, num_sink_tokens=NS, max_batch_size=B, heads=H, dim=D, max_seq_len=S, dtype=dtype,
+        cascade_func=func, layers=1, eager_fill=eager)
+    cache = run_scored_case(st, make, mode)
+    check_against_reference_cache(cache, st)
 
 
 def test_known_answer_stream():
@@ -109,12 +161,13 @@ def test_cascade_functions():
 
 def run_attention_case(st, step_fn, make_cache):
     B, H, KVH, D, NS, W, C, chunk, n_chunks, n_dec = (int(x) for x in st["cfg"])
-    dtype = {"torch.float32": torch.float32, "torch.bfloat16": torch.bfloat16}[str(st["dtype"])]
+    dtype = _DT[str(st["dtype"])]
     rule, red = str(st["rule"]), str(st["reduction"])
     homog, eager_fill = bool(st["homogeneous"]), bool(st["eager_fill"])
     beta, theta = float(st["beta"]), float(st["theta"])
     cache = make_cache(W, NS, B, KVH, D, W * C, dtype, red, eager_fill, beta)
     hidden = torch.from_numpy(st["hidden"]).to(dtype)
+    og = bool(st["do_og_pos"])
     hq, hk = H * D, KVH * D
     outs = []
     steps = [(i * chunk, chunk) for i in range(n_chunks)] + [(chunk * n_chunks + i, 1) for i in range(n_dec)]
@@ -123,17 +176,17 @@ def run_attention_case(st, step_fn, make_cache):
         q = x[..., :hq].view(B, n, H, D).transpose(1, 2)
         k = x[..., hq:hq + hk].view(B, n, KVH, D).transpose(1, 2)
         v = x[..., hq + hk:].view(B, n, KVH, D).transpose(1, 2)
-        o = step_fn(q, k, v, cache, theta, red, homog, rule)
+        o = step_fn(q, k, v, cache, theta, red, homog, rule, **({"do_og_pos": True} if og else {}))
         outs.append(o.transpose(1, 2).reshape(B, n, H * D).float().cpu())
     return torch.cat(outs, dim=1), cache
 
 
-def _oracle_step(q, k, v, cache, theta, red, homog, rule):
+def _oracle_step(q, k, v, cache, theta, red, homog, rule, do_og_pos=False):
     if rule == "stride":
-        out = cascade_attention_step(q, k, v, cache, 0, theta, red, homog, do_update=False)
+        out = cascade_attention_step(q, k, v, cache, 0, theta, red, homog, do_update=False, do_og_pos=do_og_pos)
         cache.update(k, v, 0)
         return out
-    return cascade_attention_step(q, k, v, cache, 0, theta, red, homog)
+    return cascade_attention_step(q, k, v, cache, 0, theta, red, homog, do_og_pos=do_og_pos)
 
 
 def _oracle_cache(W, NS, B, KVH, D, S, dtype, red, eager_fill, beta):

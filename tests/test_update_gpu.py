@@ -175,3 +175,97 @@ def test_random_configurations_and_ragged_chunks(seed):
         ref.update(k, v, 0, score_states=s)
         total += n
         assert_same_state(cache, ref)
+
+
+def _widen(t, D, Dw):
+    """Rows must be multiples of 16 bytes on the GPU: repeat the fixture's few columns."""
+    return t if D == Dw else t.repeat(1, 1, 1, Dw // D)
+
+
+def _scored_inputs(st):
+    from tests.test_oracle import _DT
+    W, C, NS, B, H, D = (int(x) for x in st["cfg"])
+    dtype = _DT[str(st["dtype"])]
+    Dw = max(D, 16 // torch.empty(0, dtype=dtype).element_size())
+    k, v, s = (torch.from_numpy(st[n]).to(dtype) for n in ("k", "v", "s"))
+    return (W, C, NS, B, H, D, Dw, dtype), _widen(k, D, Dw).cuda(), _widen(v, D, Dw).cuda(), s.cuda()
+
+
+def _assert_matches_reference_dump(state, st, D):
+    """``state``: name -> tensor in the reference's [B,H,...] layout; ``st``: dump of the reference's cache."""
+    valid = ~st["mask"].astype(bool)
+    assert np.array_equal(~state["mask"].cpu().numpy().astype(bool), valid)
+    for name in ("stored_tokens", "start_indices", "stored_sinks"):
+        assert np.array_equal(state[name].cpu().numpy(), st[name]), name
+    for name in ("key_cache", "value_cache"):
+        assert np.array_equal(state[name].float().cpu().numpy()[..., :D][valid], st[name][valid]), name
+    assert np.array_equal(state["score_cache"].float().cpu().numpy()[valid], st["score_cache"][valid])
+    assert np.array_equal(state["og_pos"].cpu().numpy()[valid], st["og_pos"][valid])
+    assert np.array_equal(state["pos"].cpu().numpy()[valid], st["pos"][valid])
+    sv = ~st["sink_mask"].astype(bool)
+    assert np.array_equal(state["sink_keys"].float().cpu().numpy()[..., :D][sv], st["sink_keys"][sv])
+    assert np.array_equal(state["sink_pos"].cpu().numpy()[sv], st["sink_pos"][sv])
+
+
+from tests.test_oracle import SCORED  # noqa: E402
+
+
+@pytest.mark.parametrize("name", sorted(SCORED))
+@pytest.mark.parametrize("serial", [False, True], ids=["parallel", "serial"])
+def test_scored_streams_against_the_reference_kernel_source(name, serial):
+    """ckv_cascade_update on streams with incoming scores (frequent ties) against state dumps of the
+    reference's own CascadingKVCache, produced by executing its Triton kernel's source on a CPU."""
+    from cascading_kv_cache_b200 import CascadingKVCache
+    st = SCORED[name]
+    (W, C, NS, B, H, D, Dw, dtype), k, v, s = _scored_inputs(st)
+    cache = CascadingKVCache(W, NS, B, H, Dw, W * C, device="cuda:0", dtype=dtype, cascade_func=str(st["cascade_func"]),
+                             layers=1, eager_fill=bool(st["eager_fill"]), verbose=False)
+    cache.force_serial_update = serial
+    t0 = 0
+    for m in (int(x) for x in st["chunks"]):
+        cache.update(k[:, :, t0:t0 + m], v[:, :, t0:t0 + m], 0, score_states=s[:, :, t0:t0 + m])
+        t0 += m
+    state = {n: getattr(cache, n)[0] for n in ("mask", "stored_tokens", "start_indices", "stored_sinks", "key_cache",
+                                                "value_cache", "score_cache", "og_pos", "pos", "sink_keys", "sink_pos")}
+    _assert_matches_reference_dump(state, st, D)
+    assert cache.get_seq_length(0) == int(st["stored_sinks"][0, 0]) + int(st["stored_tokens"][0, 0].sum())
+    assert cache.seen_tokens_host(0) == int(st["seen"])
+
+
+@pytest.mark.parametrize("name", ["score2", "score6", "score11"])
+@pytest.mark.parametrize("per_lane", [False, True], ids=["shared_rows", "per_lane_rows"])
+def test_functional_sink_cache(name, per_lane):
+    """sink_cache(...) with the reference's 23 positional arguments (cascading_cache.py:962-987): on tensors
+    in the reference's own per-lane layout, and on the stride-0 views of this package's cache."""
+    from cascading_kv_cache_b200 import CascadingKVCache, cascade_every_n, sink_cache
+    st = SCORED[name]
+    (W, C, NS, B, H, D, Dw, dtype), k, v, s = _scored_inputs(st)
+    S, dev = W * C, "cuda:0"
+    if per_lane:   # allocate as the reference's init_cache does (cascading_cache.py:1249-1276)
+        z = lambda *shape, dt=torch.long: torch.zeros(*shape, device=dev, dtype=dt)
+        t = dict(sink_keys=z(B, H, NS, Dw, dt=dtype), sink_values=z(B, H, NS, Dw, dt=dtype),
+                 sink_mask=torch.ones(B, H, NS, device=dev, dtype=torch.bool), sink_pos=z(B, H, NS),
+                 key_cache=z(B, H, S, Dw, dt=dtype), value_cache=z(B, H, S, Dw, dt=dtype),
+                 score_cache=z(B, H, S, dt=dtype), mask=torch.ones(B, H, S, device=dev, dtype=torch.bool),
+                 pos=z(B, H, S), og_pos=z(B, H, S), stored_tokens=z(B, H, C), start_indices=z(B, H, C),
+                 stored_sinks=z(B, H))
+        every = torch.tensor(cascade_every_n(str(st["cascade_func"]), C), device=dev)
+        seen = z(1)
+    else:
+        cache = CascadingKVCache(W, NS, B, H, Dw, S, device=dev, dtype=dtype, cascade_func=str(st["cascade_func"]),
+                                 layers=1, eager_fill=bool(st["eager_fill"]), verbose=False)
+        t = {n: getattr(cache, n)[0] for n in ("sink_keys", "sink_values", "sink_mask", "sink_pos", "key_cache",
+                                                "value_cache", "score_cache", "mask", "pos", "og_pos",
+                                                "stored_tokens", "start_indices", "stored_sinks")}
+        every, seen = cache.do_cache_every_n[0], cache.seen_tokens_by_layer
+    do_cache = torch.ones(C, device=dev, dtype=torch.bool)
+    t0 = 0
+    for m in (int(x) for x in st["chunks"]):
+        rk, rv = sink_cache(k[:, :, t0:t0 + m], v[:, :, t0:t0 + m], s[:, :, t0:t0 + m], t["sink_keys"],
+                            t["sink_values"], t["sink_mask"], t["sink_pos"], t["key_cache"], t["value_cache"],
+                            t["score_cache"], t["mask"], t["pos"], t["og_pos"], do_cache, every, t["stored_tokens"],
+                            t["start_indices"], t["stored_sinks"], NS, W, seen[0], S, bool(st["eager_fill"]))
+        assert rk.data_ptr() == k[:, :, t0:t0 + m].data_ptr()
+        seen[0] += m            # the caller advances the token counter, as the reference's update() does
+        t0 += m
+    _assert_matches_reference_dump(t, st, D)

@@ -66,6 +66,10 @@ def test_static_scratch_matches_ordinary_entry_point_on_consecutive_calls():
         rel = err.norm().item() / want.norm().item()
         assert err.max().item() <= 2e-2 and rel <= 1e-2, (n, err.max().item(), rel)
     torch.cuda.synchronize()
+    # no bounded wait inside a kernel gave up: the status word of the built-in array, read without a
+    # workspace pointer
+    status = ctypes.c_int32(-1)
+    assert static._lib.ckv_static_status(ctypes.byref(status)) == 0 and status.value == 0
     assert torch.equal(static.pos[0], ordinary.pos[0])
     assert torch.equal(static.stored_tokens[0], ordinary.stored_tokens[0])
     assert torch.equal(static.start_indices[0], ordinary.start_indices[0])
