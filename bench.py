@@ -332,6 +332,7 @@ class DecodeCase:
     def kernel_profile(self, n_steps):
         from cascading_kv_cache_b200 import profiling
         k_ms, k_n, k_name = profiling.time_dominant_kernel(self.step, n_steps=n_steps)
+        self.breakdown = {name: ms for name, ms, _ in profiling.kernel_breakdown()}
         launches = profiling.last_launch_count()
         torch.cuda.synchronize()
         return k_ms, k_name, launches
@@ -586,6 +587,7 @@ def main():
                      "frac": k_gbs / peaks["hbm"], "peak_kind": peaks["kind"],
                      "traffic": recorded_dram_traffic(args.workload, k_name, lanes_local),
                      "kernel": k_name, "kernel_ms": k_ms, "per": "GPU (rank 0's share of the batch)",
+                     "kernels_ms": getattr(case, "breakdown", None),
                      "step_frac": head["gbs"] / (peaks["hbm"] * job.world),
                      "step_frac_of_8tbs": head["gbs"] / (8000.0 * job.world)},
     }

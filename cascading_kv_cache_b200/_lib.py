@@ -24,7 +24,7 @@ DTYPE_CODE = {torch.float32: CKV_F32, torch.float16: CKV_F16, torch.bfloat16: CK
 
 EXPORTS = ("ckv_abi_version", "ckv_last_error", "ckv_cascade_update", "ckv_update_workspace_bytes",
            "ckv_attention_workspace_bytes", "ckv_attention_workspace_bytes_for",
-           "ckv_attention", "ckv_last_launch_count", "ckv_profile_enable", "ckv_profile_read", "ckv_read_status",
+           "ckv_attention", "ckv_last_launch_count", "ckv_profile_enable", "ckv_profile_read", "ckv_profile_kernel", "ckv_read_status",
            "ckv_static_scratch_bytes", "ckv_attention_static", "ckv_static_status", "ckv_advance_counters_host",
            "ckv_dense_attention_workspace_bytes", "ckv_dense_attention")
 
@@ -92,6 +92,9 @@ def load():
     lib.ckv_profile_read.restype = ctypes.c_int
     lib.ckv_profile_read.argtypes = [ctypes.POINTER(ctypes.c_double), ctypes.POINTER(i32),
                                      ctypes.POINTER(ctypes.c_char_p)]
+    lib.ckv_profile_kernel.restype = ctypes.c_int
+    lib.ckv_profile_kernel.argtypes = [i32, ctypes.POINTER(ctypes.c_char_p), ctypes.POINTER(ctypes.c_double),
+                                       ctypes.POINTER(i32)]
     lib.ckv_read_status.restype = ctypes.c_int
     lib.ckv_read_status.argtypes = [vp, ctypes.POINTER(i32)]
     if lib.ckv_abi_version() != 1:

@@ -366,6 +366,7 @@ class CascadingKVCache(Cache):
     def workspace(self, nbytes: int) -> torch.Tensor:
         if self._workspace is None or self._workspace.numel() < nbytes:
             self._workspace = torch.empty(nbytes + 256, device=self.device, dtype=torch.uint8)
+            self._workspace[:512].zero_()     # the status word reads 0 until an attention call writes it
         return self._workspace
 
     def workspace_bytes(self) -> int:

@@ -1,6 +1,7 @@
 // extern "C" entry points of libckv_b200.so: argument checks and dispatch.
 #include <stdarg.h>
 #include <stdio.h>
+#include <string.h>
 
 #include <utility>
 #include <vector>
@@ -19,27 +20,36 @@ int fail(int code, const char *fmt, ...) {
     return code;
 }
 
-// ---- profiling hook: library-owned CUDA events around the dominant kernel of each call ----------
+// ---- profiling hook: library-owned CUDA events around the kernels of each call --------------------
+struct TimedLaunch {
+    const char *name;
+    cudaEvent_t a, b;
+};
 static bool g_profile_on = false;
-static std::vector<std::pair<cudaEvent_t, cudaEvent_t>> g_events;
+static std::vector<TimedLaunch> g_events;
 static size_t g_events_used = 0;
-static const char *g_kernel_name = "";
 static ProfileHook g_hook;
 static thread_local int g_launches = 0;
+struct KernelTotal {
+    const char *name;
+    double ms;
+    int launches;
+};
+static std::vector<KernelTotal> g_totals;   // of the last ckv_profile_read, largest total first
 
 void ProfileHook::before(cudaStream_t stream, const char *kernel_name) {
-    g_kernel_name = kernel_name;
     if (g_events_used == g_events.size()) {
         cudaEvent_t a, b;
         if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) return;
-        g_events.emplace_back(a, b);
+        g_events.push_back({kernel_name, a, b});
     }
-    cudaEventRecord(g_events[g_events_used].first, stream);
+    g_events[g_events_used].name = kernel_name;
+    cudaEventRecord(g_events[g_events_used].a, stream);
 }
 
 void ProfileHook::after(cudaStream_t stream) {
     if (g_events_used < g_events.size()) {
-        cudaEventRecord(g_events[g_events_used].second, stream);
+        cudaEventRecord(g_events[g_events_used].b, stream);
         g_events_used += 1;
     }
 }
@@ -180,8 +190,8 @@ extern "C" int ckv_profile_enable(int enable) {
     g_events_used = 0;
     if (!g_profile_on) {
         for (auto &e : g_events) {
-            cudaEventDestroy(e.first);
-            cudaEventDestroy(e.second);
+            cudaEventDestroy(e.a);
+            cudaEventDestroy(e.b);
         }
         g_events.clear();
     }
@@ -189,17 +199,32 @@ extern "C" int ckv_profile_enable(int enable) {
 }
 
 extern "C" int ckv_profile_read(double *total_ms, int32_t *launches, const char **kernel_name) {
-    double total = 0.0;
+    g_totals.clear();
     for (size_t i = 0; i < g_events_used; ++i) {
-        CKV_CUDA_CHECK(cudaEventSynchronize(g_events[i].second));
+        CKV_CUDA_CHECK(cudaEventSynchronize(g_events[i].b));
         float ms = 0.f;
-        CKV_CUDA_CHECK(cudaEventElapsedTime(&ms, g_events[i].first, g_events[i].second));
-        total += ms;
+        CKV_CUDA_CHECK(cudaEventElapsedTime(&ms, g_events[i].a, g_events[i].b));
+        size_t k = 0;
+        while (k < g_totals.size() && strcmp(g_totals[k].name, g_events[i].name) != 0) ++k;
+        if (k == g_totals.size()) g_totals.push_back({g_events[i].name, 0.0, 0});
+        g_totals[k].ms += ms;
+        g_totals[k].launches += 1;
     }
-    if (total_ms) *total_ms = total;
-    if (launches) *launches = (int32_t)g_events_used;
-    if (kernel_name) *kernel_name = g_kernel_name;
+    for (size_t i = 1; i < g_totals.size(); ++i)       // few entries: insertion sort, largest total first
+        for (size_t j = i; j > 0 && g_totals[j].ms > g_totals[j - 1].ms; --j) std::swap(g_totals[j], g_totals[j - 1]);
+    const bool any = !g_totals.empty();
+    if (total_ms) *total_ms = any ? g_totals[0].ms : 0.0;
+    if (launches) *launches = any ? g_totals[0].launches : 0;
+    if (kernel_name) *kernel_name = any ? g_totals[0].name : "";
     g_events_used = 0;
+    return CKV_OK;
+}
+
+extern "C" int ckv_profile_kernel(int32_t index, const char **kernel_name, double *total_ms, int32_t *launches) {
+    if (index < 0 || (size_t)index >= g_totals.size()) return fail(CKV_E_ARG, "no kernel %d in the last collection", index);
+    if (kernel_name) *kernel_name = g_totals[index].name;
+    if (total_ms) *total_ms = g_totals[index].ms;
+    if (launches) *launches = g_totals[index].launches;
     return CKV_OK;
 }
 

@@ -1,15 +1,22 @@
 // Single-token decode over the cascading cache for 16-bit caches with head_dim 128.
 //
 // Kernel 0, rope_slots_kernel: cache positions do not depend on the lane, so the cos|sin row of every
-//   slot is written once per step in slot order (an L2-resident image that TMA can stream).
+//   slot is written once per step in slot order (an L2-resident image that TMA can stream).  Two
+//   images alternate with the parity of the token count; the finish kernel of a step writes the image
+//   of the NEXT step and tags it with the counters it is valid for, so that this kernel returns at
+//   once when it finds the tag of its step (it writes the image itself after a prefill chunk, a
+//   reset, or any other change of the counters behind the library's back).
 //
 // Kernel 1, decode_stream_kernel (HBM-bound, persistent, one CTA per SM):
 //   The valid keys of all lanes form one flat stream of 64-key tiles; every CTA takes a
 //   contiguous range of that stream (a split of the key dimension that ignores lane borders, so
-//   all SMs stream the same number of bytes).  A producer warp moves each tile into a 4-stage
-//   shared-memory ring with six TMA boxes (cp.async.bulk.tensor, 128-byte swizzle, mbarrier
-//   completion): K lo/hi and V lo/hi from the cache (L2 evict-first) and the cos / sin rows of the
-//   tile's slots from the image (L2 evict-last).  Sixteen consumer warps in two groups take
+//   all SMs stream the same number of bytes).  Two producer warps move each tile into shared memory
+//   with TMA boxes (cp.async.bulk.tensor, 128-byte swizzle, mbarrier completion) through two rings:
+//   K lo/hi and V lo/hi from the cache (L2 evict-first) through a 5-stage ring of 32 KB stages, the
+//   cos / sin rows of the tile's slots from the image (L2 evict-last) through a 3-stage ring of
+//   16 KB stages.  The rings are separate because their sources differ: the K/V bytes come from HBM
+//   and need as many stages in flight as the memory latency asks for, the image sits in L2 and its
+//   stage is released as soon as the keys are rotated.  Sixteen consumer warps in two groups take
 //   alternate tiles; in a group, warp w owns keys [8w, 8w+8): ldmatrix of K and cos/sin fragments,
 //   RoPE in packed 16-bit arithmetic on the fragments (the same rounding points as the reference:
 //   cascade_attention.py:31-35, :284-291), QK^T on mma.sync m16n8k16 with the GQA group as the M
@@ -33,17 +40,20 @@ namespace ckv {
 namespace {
 
 constexpr int kTile = 64;                       // keys per stage
-constexpr int kStages = 4;
+constexpr int kStages = 5;                      // K/V ring
+constexpr int kStagesCS = 3;                    // cos/sin ring
 constexpr int kGroupWarps = 8;                  // warps per consumer group: each owns 8 keys of a tile
 constexpr int kGroups = 2;                      // consumer groups working on alternate tiles
 constexpr int kComputeWarps = kGroupWarps * kGroups;
-constexpr int kStreamThreads = (kComputeWarps + 1) * 32;
+constexpr int kStreamThreads = (kComputeWarps + 2) * 32;   // + the K/V producer warp + the cos/sin producer warp
 constexpr int kSubBytes = kTile * 128;          // one swizzled 64-row x 128-byte sub-tile
-constexpr int kStageBytes = 6 * kSubBytes;      // K lo | K hi | V lo | V hi | cos | sin
-constexpr int kOffK = 0, kOffV = 2 * kSubBytes, kOffCos = 4 * kSubBytes, kOffSin = 5 * kSubBytes;
+constexpr int kStageBytes = 4 * kSubBytes;      // K lo | K hi | V lo | V hi
+constexpr int kStageBytesCS = 2 * kSubBytes;    // cos | sin
+constexpr int kOffK = 0, kOffV = 2 * kSubBytes, kOffCos = 0, kOffSin = kSubBytes;
+constexpr int kRingBytes = kStages * kStageBytes + kStagesCS * kStageBytesCS;
 constexpr int kMaxG = 16;
 constexpr int kMergeBytes = (kMaxG * 128 + 2 * kComputeWarps * kMaxG) * 4;  // out[16][128] + m,l per warp
-constexpr int kStreamSmem = kStages * kStageBytes + 1024 + 256 + kMergeBytes;
+constexpr int kStreamSmem = kRingBytes + 1024 + 256 + kMergeBytes;
 constexpr int kPartialStride = 130;             // m, l, out[128] per head row
 constexpr unsigned kSpinLimit = 1u << 24;       // bounded mbarrier waits (each probe also sleeps)
 constexpr int kFinishThreads = 256;
@@ -70,7 +80,9 @@ struct DecodeParams {
     void *logits;                                // [B*H][S]
     float *partials;                             // [(grid + lanes)][G][130]: one per (CTA, lane) segment
     void *new_scores;                            // [B*KVH]
-    void *rope_slots;                            // [sink rows padded to 64 | S][128]: cos|sin per slot
+    void *rope_slots;                            // 2 x [sink rows padded to 64 | S (+ a tile)][128]: cos|sin per slot
+    long long image_bytes;                       // of one of the two images
+    long long *image_tag;                        // 2 x 4 words: what each image is valid for
     int sink_rows_pad;
     int B, KVH, H, G, NS, W, C, S;
     int ema, update, head_reduction, eager_fill, dtype;
@@ -228,11 +240,51 @@ __device__ __forceinline__ long long cta_first_tile(long long cta, long long n_t
 // ------------------------------------------------------------------------------ rope pre-pass
 // Positions depend only on the slot, never on the lane: write the cos|sin row of every sink and
 // cache slot once per step, in slot order, so that the stream kernel can fetch them with TMA.
+// What an image depends on: the counters (hence every position), the table it was taken from, the geometry.
+struct ImageTag {
+    long long seen, counters, table, geometry;
+};
+
+__device__ __forceinline__ ImageTag make_image_tag(const DecodeParams &p, long long seen, long long sinks,
+                                                   const long long *stored, const long long *start) {
+    ImageTag t;
+    t.seen = seen;
+    long long h = sinks;
+    for (int i = 0; i < p.C; ++i) h = h * 1000003LL + stored[i] * 65537LL + start[i];
+    t.counters = h;
+    // the table's address, its length, and a few of its values that differ from one RoPE base to another
+    // (sines of row 1): a table of another base at a recycled address must not pass for this one
+    t.table = (long long)(uintptr_t)p.rope ^ (p.rope_rows << 48) ^
+              *reinterpret_cast<const long long *>(reinterpret_cast<const uint8_t *>(p.rope) + 256 + 128 + 32);
+    t.geometry = ((long long)p.S << 32) ^ ((long long)p.NS << 16) ^ (long long)p.W ^ ((long long)p.dtype << 60);
+    return t;
+}
+
+__device__ __forceinline__ uint4 *image_of(const DecodeParams &p, long long seen) {
+    return reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.rope_slots) + (seen & 1) * p.image_bytes);
+}
+
 __global__ void __launch_bounds__(256) rope_slots_kernel(DecodeParams p) {
     const Schedule sc = make_schedule(p);
+    {
+        // the image of this step may already be there (written by the previous step's finish kernel).
+        // One thread per block looks: every thread of a large grid reading the same four words would
+        // queue up at one L2 bank for longer than the whole kernel otherwise takes.
+        __shared__ int s_valid;
+        if (threadIdx.x == 0) {
+            const ImageTag want = make_image_tag(p, sc.seen, sc.sinks, p.stored_tokens, p.start_indices);
+            const volatile long long *tag = p.image_tag + 4 * (sc.seen & 1);
+            s_valid = tag[0] == want.seen && tag[1] == want.counters && tag[2] == want.table && tag[3] == want.geometry;
+        }
+        __syncthreads();
+        if (s_valid) return;
+    }
+    // No block of this grid can see a matching tag from here on: the tag is only ever set by a finish
+    // kernel, and the first block marks it invalid because the image now changes under it.
+    if (blockIdx.x == 0 && threadIdx.x == 0) p.image_tag[4 * (sc.seen & 1)] = -1;
     const int n_rows = p.sink_rows_pad + p.S;
     const uint4 *rope = reinterpret_cast<const uint4 *>(p.rope);
-    uint4 *dst = reinterpret_cast<uint4 *>(p.rope_slots);
+    uint4 *dst = image_of(p, sc.seen);
     for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < (long long)n_rows * 16;
          idx += (long long)gridDim.x * blockDim.x) {
         const int row = (int)(idx >> 4), c = (int)(idx & 15);
@@ -253,11 +305,15 @@ template <typename T, int kRowHalves>
 __global__ void __launch_bounds__(kStreamThreads, 1)
 decode_stream_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                      const __grid_constant__ CUtensorMap tmSK, const __grid_constant__ CUtensorMap tmSV,
-                     const __grid_constant__ CUtensorMap tmR, DecodeParams p) {
+                     const __grid_constant__ CUtensorMap tmR0, const __grid_constant__ CUtensorMap tmR1,
+                     DecodeParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint64_t *full = reinterpret_cast<uint64_t *>(smem + kStages * kStageBytes);
+    uint8_t *smem_cs = smem + kStages * kStageBytes;
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + kRingBytes);
     uint64_t *empty = full + kStages;
+    uint64_t *full_cs = empty + kStages;
+    uint64_t *empty_cs = full_cs + kStagesCS;
     const int warp = threadIdx.x >> 5, lane_id = threadIdx.x & 31;
     const Schedule sc = make_schedule(p);
     const long long t_begin = cta_first_tile(blockIdx.x, sc.n_tiles, gridDim.x);
@@ -268,6 +324,10 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
             mbar_init(&full[s], 1);    // the producer's expect_tx arrival; TMA completes the bytes
             mbar_init(&empty[s], kGroupWarps);
         }
+        for (int s = 0; s < kStagesCS; ++s) {
+            mbar_init(&full_cs[s], 1);
+            mbar_init(&empty_cs[s], kGroupWarps);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (blockIdx.x == 0) {
@@ -277,10 +337,9 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     __syncthreads();
 
     if (warp == kComputeWarps) {
-        // ------------------------------------------------------------------ producer warp
-        // one elected lane issues six TMA boxes per tile: K lo/hi, V lo/hi and the cos / sin rows of
-        // the tile's slots from the slot-ordered image the pre-pass wrote
-        const uint64_t pol_stream = l2_policy_evict_first(), pol_keep = l2_policy_evict_last();
+        // ------------------------------------------------------------------ K/V producer warp
+        // one elected lane issues four TMA boxes per tile: K lo/hi, V lo/hi
+        const uint64_t pol_stream = l2_policy_evict_first();
         int lane = (int)(t_begin / sc.tiles_per_lane), ti = (int)(t_begin % sc.tiles_per_lane);
         const int n_it = (int)(t_end - t_begin);
         for (int it = 0; it < n_it; ++it) {
@@ -292,23 +351,44 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
             }
             uint8_t *stage = smem + s * kStageBytes;
             if (lane_id == 0) {
-                mbar_expect_tx(&full[s], 6 * kSubBytes);
+                mbar_expect_tx(&full[s], 4 * kSubBytes);
                 const int y = sink_tile ? lane * p.NS + row0 : lane * p.S + row0;
-                const int yr = sink_tile ? row0 : p.sink_rows_pad + row0;
                 const CUtensorMap *mk = sink_tile ? &tmSK : &tmK;
                 const CUtensorMap *mv = sink_tile ? &tmSV : &tmV;
                 tma_load_2d(stage + kOffK, mk, 0, y, &full[s], pol_stream);
                 tma_load_2d(stage + kOffK + kSubBytes, mk, 64, y, &full[s], pol_stream);
                 tma_load_2d(stage + kOffV, mv, 0, y, &full[s], pol_stream);
                 tma_load_2d(stage + kOffV + kSubBytes, mv, 64, y, &full[s], pol_stream);
-                tma_load_2d(stage + kOffCos, &tmR, 0, yr, &full[s], pol_keep);
-                tma_load_2d(stage + kOffSin, &tmR, 64, yr, &full[s], pol_keep);
             }
             __syncwarp();
             if (++ti == sc.tiles_per_lane) {
                 ti = 0;
                 ++lane;
             }
+        }
+    } else if (warp == kComputeWarps + 1) {
+        // ------------------------------------------------------------------ cos/sin producer warp
+        // the cos / sin rows of each tile's slots from the slot-ordered image the pre-pass wrote
+        const uint64_t pol_keep = l2_policy_evict_last();
+        const CUtensorMap *tmR = (sc.seen & 1) ? &tmR1 : &tmR0;      // the image of this step
+        int ti = (int)(t_begin % sc.tiles_per_lane);
+        const int n_it = (int)(t_end - t_begin);
+        for (int it = 0; it < n_it; ++it) {
+            const int s = it % kStagesCS;
+            const bool sink_tile = ti < sc.n_sink_tiles;
+            const int row0 = sink_tile ? ti * kTile : (ti - sc.n_sink_tiles) * kTile;
+            if (it >= kStagesCS) {
+                if (!mbar_wait(&empty_cs[s], ((it / kStagesCS) & 1) ^ 1, p.status)) break;
+            }
+            uint8_t *stage = smem_cs + s * kStageBytesCS;
+            if (lane_id == 0) {
+                mbar_expect_tx(&full_cs[s], 2 * kSubBytes);
+                const int yr = sink_tile ? row0 : p.sink_rows_pad + row0;
+                tma_load_2d(stage + kOffCos, tmR, 0, yr, &full_cs[s], pol_keep);
+                tma_load_2d(stage + kOffSin, tmR, 64, yr, &full_cs[s], pol_keep);
+            }
+            __syncwarp();
+            if (++ti == sc.tiles_per_lane) ti = 0;
         }
     } else {
         // ----------------------------------------------------------------- consumer warps
@@ -324,7 +404,7 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         int cur_lane = -1;
         T *lrow[2] = {nullptr, nullptr};
 
-        float *mg_out = reinterpret_cast<float *>(smem + kStages * kStageBytes + 256);   // [kMaxG][128]
+        float *mg_out = reinterpret_cast<float *>(smem + kRingBytes + 256);              // [kMaxG][128]
         float *mg_m = mg_out + kMaxG * 128;                                              // [warps][kMaxG]
         float *mg_l = mg_m + kComputeWarps * kMaxG;
         const int ctid = threadIdx.x;  // consumer threads are 0 .. kComputeWarps*32 - 1
@@ -394,7 +474,7 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
         const int n_it = (int)(t_end - t_begin);
         bool failed = false;
         for (int it = 0; it < n_it; ++it) {
-            const int s = it % kStages;
+            const int s = it % kStages, scs = it % kStagesCS;
             if (lane != cur_lane) {
                 if (cur_lane >= 0) flush(cur_lane);
                 cur_lane = lane;
@@ -434,7 +514,8 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
                 }
             }
             if ((it & (kGroups - 1)) == group) {
-                if (!mbar_wait(&full[s], (it / kStages) & 1, p.status)) {
+                if (!mbar_wait(&full[s], (it / kStages) & 1, p.status) ||
+                    !mbar_wait(&full_cs[scs], (it / kStagesCS) & 1, p.status)) {
                     failed = true;
                     break;
                 }
@@ -445,6 +526,7 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
                 const int key0 = 8 * wk;
                 if (key0 < nvalid) {
                     const uint32_t stage = smem_u32(smem + s * kStageBytes);
+                    const uint32_t stage_cs = smem_u32(smem_cs + scs * kStageBytesCS);
                     float sacc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
                     for (int u = 0; u < 2; ++u) {
@@ -452,8 +534,8 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
                         uint32_t kl[4], kh[4], cs[4], sn[4];
                         ldsm_x4(stage + kOffK + choff[u], kl[0], kl[1], kl[2], kl[3]);
                         ldsm_x4(stage + kOffK + kSubBytes + choff[u], kh[0], kh[1], kh[2], kh[3]);
-                        ldsm_x4(stage + kOffCos + choff[u], cs[0], cs[1], cs[2], cs[3]);
-                        ldsm_x4(stage + kOffSin + choff[u], sn[0], sn[1], sn[2], sn[3]);
+                        ldsm_x4(stage_cs + kOffCos + choff[u], cs[0], cs[1], cs[2], cs[3]);
+                        ldsm_x4(stage_cs + kOffSin + choff[u], sn[0], sn[1], sn[2], sn[3]);
 #pragma unroll
                         for (int e = 0; e < 4; ++e) rope_pair<T>(kl[e], kh[e], cs[e], sn[e], p.rs);
                         Mma<T>::run(sacc, qa[2 * u], kl[0], kl[1]);
@@ -461,6 +543,9 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
                         Mma<T>::run(sacc, qa[2 * u + 4], kh[0], kh[1]);
                         Mma<T>::run(sacc, qa[2 * u + 5], kh[2], kh[3]);
                     }
+                    // the keys are rotated: hand the cos/sin stage back before the softmax and the P V product
+                    __syncwarp();
+                    if (lane_id == 0) mbar_arrive(&empty_cs[scs]);
                     // logits rounded to T (the reference's einsum output), masked past the valid keys
                     const int kk = key0 + 2 * tq;
 #pragma unroll
@@ -532,6 +617,7 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
                         }
                     }
                 }
+                else if (lane_id == 0) mbar_arrive(&empty_cs[scs]);   // a warp without valid keys in this tile
                 __syncwarp();
                 if (lane_id == 0) mbar_arrive(&empty[s]);
             }
@@ -606,18 +692,43 @@ __device__ __forceinline__ void ema_pass_vec(const DecodeParams &p, const Schedu
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] = kMax ? -INFINITY : 0.f;
         if (any_valid) {
+            if (kMax) {
+                // max over the group: every step from the exponent to the weighted, rounded probability is
+                // monotone (exp2, the two roundings, the product with the positive weight), so the largest
+                // exponent of the group gives the group's largest value -- one exponential per slot
 #pragma unroll
-            for (int gh = 0; gh < 8; ++gh) {
-                if (gh < p.G) {
-                    const uint32_t *lw = reinterpret_cast<const uint32_t *>(&l4[gh]);
+                for (int gh = 0; gh < 8; ++gh) {
+                    if (gh < p.G) {
+                        const uint32_t *lw = reinterpret_cast<const uint32_t *>(&l4[gh]);
 #pragma unroll
-                    for (int jj = 0; jj < 4; ++jj) {
-                        const float2 l = P::to_f2(P::from_u(lw[jj]));
-                        const float2 pr = P::to_f2(P::from_f2(make_float2(ex2_approx(fmaf(l.x, kLog2e, cg[gh])),
-                                                                          ex2_approx(fmaf(l.y, kLog2e, cg[gh])))));
-                        const float2 e = P::to_f2(P::from_f2(make_float2(__fmul_rn(pr.x, w0), __fmul_rn(pr.y, w0))));
-                        acc[2 * jj] = kMax ? fmaxf(acc[2 * jj], e.x) : acc[2 * jj] + e.x;
-                        acc[2 * jj + 1] = kMax ? fmaxf(acc[2 * jj + 1], e.y) : acc[2 * jj + 1] + e.y;
+                        for (int jj = 0; jj < 4; ++jj) {
+                            const float2 l = P::to_f2(P::from_u(lw[jj]));
+                            acc[2 * jj] = fmaxf(acc[2 * jj], fmaf(l.x, kLog2e, cg[gh]));
+                            acc[2 * jj + 1] = fmaxf(acc[2 * jj + 1], fmaf(l.y, kLog2e, cg[gh]));
+                        }
+                    }
+                }
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) {
+                    const float2 pr = P::to_f2(P::from_f2(make_float2(ex2_approx(acc[2 * jj]), ex2_approx(acc[2 * jj + 1]))));
+                    const float2 e = P::to_f2(P::from_f2(make_float2(__fmul_rn(pr.x, w0), __fmul_rn(pr.y, w0))));
+                    acc[2 * jj] = e.x;
+                    acc[2 * jj + 1] = e.y;
+                }
+            } else {
+#pragma unroll
+                for (int gh = 0; gh < 8; ++gh) {
+                    if (gh < p.G) {
+                        const uint32_t *lw = reinterpret_cast<const uint32_t *>(&l4[gh]);
+#pragma unroll
+                        for (int jj = 0; jj < 4; ++jj) {
+                            const float2 l = P::to_f2(P::from_u(lw[jj]));
+                            const float2 pr = P::to_f2(P::from_f2(make_float2(ex2_approx(fmaf(l.x, kLog2e, cg[gh])),
+                                                                              ex2_approx(fmaf(l.y, kLog2e, cg[gh])))));
+                            const float2 e = P::to_f2(P::from_f2(make_float2(__fmul_rn(pr.x, w0), __fmul_rn(pr.y, w0))));
+                            acc[2 * jj] += e.x;
+                            acc[2 * jj + 1] += e.y;
+                        }
                     }
                 }
             }
@@ -642,7 +753,9 @@ __global__ void __launch_bounds__(kFinishThreads, 3) decode_finish_kernel(Decode
     __shared__ float s_m[kMaxG], s_linv[kMaxG], s_snew[kMaxG], s_pnew[kMaxG];
     __shared__ long long s_stored[CKV_MAX_CASCADES], s_start[CKV_MAX_CASCADES], s_every[CKV_MAX_CASCADES];
     __shared__ long long s_new_stored[CKV_MAX_CASCADES], s_new_start[CKV_MAX_CASCADES];
-    __shared__ long long s_new_sinks, s_new_total;
+    __shared__ long long s_new_sinks, s_new_total, s_tag[4];
+    __shared__ int s_image_there;
+    __shared__ int s_next_pos[kFinishThreads];
     __shared__ int s_is_last;
     const int lane = blockIdx.y;
     const int b = lane / p.KVH, kvh = lane % p.KVH;
@@ -767,8 +880,8 @@ __global__ void __launch_bounds__(kFinishThreads, 3) decode_finish_kernel(Decode
     //    counters, every block of the grid taking an equal share of the slots (nothing in this kernel
     //    reads them)
     if (tid < p.C) {
-        s_new_stored[tid] = p.stored_tokens[tid];
-        s_new_start[tid] = p.start_indices[tid];
+        s_stored[tid] = s_new_stored[tid] = p.stored_tokens[tid];
+        s_start[tid] = s_new_start[tid] = p.start_indices[tid];
         s_every[tid] = p.every_n[tid];
     }
     __syncthreads();
@@ -779,6 +892,10 @@ __global__ void __launch_bounds__(kFinishThreads, 3) decode_finish_kernel(Decode
         for (int i = 0; i < p.C; ++i) total += s_new_stored[i];
         s_new_sinks = sinks;
         s_new_total = total;
+        const ImageTag t = make_image_tag(p, sc.seen + 1, sinks, s_new_stored, s_new_start);
+        s_tag[0] = t.seen; s_tag[1] = t.counters; s_tag[2] = t.table; s_tag[3] = t.geometry;
+        const volatile long long *tag = p.image_tag + 4 * ((sc.seen + 1) & 1);
+        s_image_there = tag[0] == t.seen && tag[1] == t.counters && tag[2] == t.table && tag[3] == t.geometry;
     }
     __syncthreads();
     {
@@ -794,6 +911,48 @@ __global__ void __launch_bounds__(kFinishThreads, 3) decode_finish_kernel(Decode
             const int seg = stored_i < p.W ? stored_i : p.W;
             if (rewrite && ub > 0 && seg > 0) p.pos[t] = (long long)((j + seg - (int)s_new_start[i]) % seg) + ub - seg;
         }
+        // the cos|sin image of the NEXT step (positions after this token), unless an earlier call of this
+        // step -- another layer sharing the workspace -- has written it already.  256 slots at a time: a
+        // thread works out one slot's next position, then the block copies the 256 table rows with 16
+        // independent 16-byte loads per thread.
+        if (!s_image_there) {
+            const long long seen_next = sc.seen + 1;
+            const long long shift = seen_next > p.NS ? p.NS : 0;
+            const uint4 *rope = reinterpret_cast<const uint4 *>(p.rope);
+            uint4 *img = image_of(p, seen_next) + (long long)p.sink_rows_pad * 16;
+            for (int base = s_begin; base < s_end; base += kFinishThreads) {
+                const int t = base + tid;
+                long long pos = 0;
+                if (t < s_end && t < s_new_total) {
+                    pos = p.pos[t];
+                    if (rewrite) {
+                        const int i = t / p.W, j = t % p.W;
+                        const int stored_i = (int)s_new_stored[i];
+                        const long long ub = s_new_total - (long long)i * p.W;
+                        const int seg = stored_i < p.W ? stored_i : p.W;
+                        if (seg > 0 && ub > 0) pos = (long long)((j + seg - (int)s_new_start[i]) % seg) + ub - seg;
+                    }
+                    pos += shift;
+                }
+                s_next_pos[tid] = (int)(pos < 0 ? 0 : (pos >= p.rope_rows ? p.rope_rows - 1 : pos));
+                __syncthreads();
+                const int n_here = min(kFinishThreads, s_end - base);
+#pragma unroll
+                for (int r = 0; r < 16; ++r) {
+                    const int idx = r * kFinishThreads + tid, slot = idx >> 4, c = idx & 15;
+                    if (slot < n_here) img[(long long)(base + slot) * 16 + c] = rope[(long long)s_next_pos[slot] * 16 + c];
+                }
+                __syncthreads();
+            }
+            if (me == 0) {      // the sink rows: sink i sits at position i
+                uint4 *simg = image_of(p, seen_next);
+                for (int idx = tid; idx < p.sink_rows_pad * 16; idx += kFinishThreads) {
+                    const int row = idx >> 4, c = idx & 15;
+                    const long long pos = row < s_new_sinks ? row : 0;
+                    simg[idx] = rope[pos * 16 + c];
+                }
+            }
+        }
     }
 
     // 6. the last block of the lane inserts the token; the last lane advances the counters
@@ -804,14 +963,18 @@ __global__ void __launch_bounds__(kFinishThreads, 3) decode_finish_kernel(Decode
     if (!s_is_last) return;
     __threadfence();
     if (warp == 0) {
-        if (p.ema && lane_id == 0) {
+        unsigned int new_score = 0;
+        if (p.ema) {
             float e[kMaxG];
             const float w1 = Elem<T>::to_f(reinterpret_cast<const T *>(p.ema_w_new)[0]);
             for (int gh = 0; gh < p.G; ++gh) e[gh] = rnd<T>(__fmul_rn(rnd<T>(s_pnew[gh]), w1));
-            reinterpret_cast<T *>(p.new_scores)[lane] = Elem<T>::from_f(rnd<T>(reduce_group(e, p.G, p.head_reduction)));
+            const T red = Elem<T>::from_f(rnd<T>(reduce_group(e, p.G, p.head_reduction)));
+            new_score = (unsigned int)*reinterpret_cast<const unsigned short *>(&red);
+            if (lane_id == 0) reinterpret_cast<T *>(p.new_scores)[lane] = red;
         }
         __syncwarp();
-        update_lane_walk(p.upd, lane, s_stored, s_start, s_every);
+        if (p.C <= kOneTokenMaxCascades) update_lane_one_token(p.upd, lane, s_stored, s_start, s_every, sc.sinks, sc.seen, new_score);
+        else update_lane_walk(p.upd, lane, s_stored, s_start, s_every);
         __threadfence();
         __syncwarp();
         unsigned last = 0;
@@ -830,6 +993,12 @@ __global__ void __launch_bounds__(kFinishThreads, 3) decode_finish_kernel(Decode
                 }
                 *p.stored_sinks = s_new_sinks;
                 *p.seen = sc.seen + 1;
+                // every block has written its share of the next step's image (their fences precede the
+                // counters that elected this thread): say what it is valid for
+                long long *tag = p.image_tag + 4 * ((sc.seen + 1) & 1);
+                tag[1] = s_tag[1]; tag[2] = s_tag[2]; tag[3] = s_tag[3];
+                __threadfence();
+                tag[0] = s_tag[0];
             }
         }
     }
@@ -871,7 +1040,7 @@ int make_rows_map(CUtensorMap *tm, const void *base, uint64_t rows, int dtype) {
 size_t up256(size_t x) { return (x + 255) & ~(size_t)255; }
 
 struct DecodeScratch {
-    size_t status, sync, logits, partials, new_scores, rope_slots, total;
+    size_t status, sync, image_tag, logits, partials, new_scores, rope_slots, image_bytes, total;
 };
 
 int sm_count() {
@@ -892,11 +1061,13 @@ DecodeScratch decode_scratch(const Dims &d) {
     size_t off = 0;
     s.status = off; off += 256;
     s.sync = off; off += up256((1 + lanes) * 4);
+    s.image_tag = off; off += 256;
     s.logits = off; off += up256((size_t)d.B * d.H * d.S * 2);
     s.partials = off; off += up256((size_t)(sm_count() + lanes) * d.G * kPartialStride * 4);
     s.new_scores = off; off += up256(lanes * 2);
     off = (off + 1023) & ~(size_t)1023;
-    s.rope_slots = off; off += up256((size_t)(sink_rows_padded(d) + d.S + kTile) * 256);
+    s.image_bytes = ((size_t)(sink_rows_padded(d) + d.S + kTile) * 256 + 1023) & ~(size_t)1023;
+    s.rope_slots = off; off += 2 * s.image_bytes;
     s.total = off;
     return s;
 }
@@ -943,13 +1114,16 @@ int launch_decode_tuned(const Dims &d, const ckv_layer_state *st, const void *q,
                                             cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmem));
     }
     const uint64_t lanes = (uint64_t)d.B * d.KVH;
-    CUtensorMap tmK, tmV, tmSK, tmSV, tmR;
+    CUtensorMap tmK, tmV, tmSK, tmSV, tmR0, tmR1;
     int rc;
     if ((rc = make_rows_map(&tmK, st->key_cache, lanes * d.S, d.dtype)) != CKV_OK) return rc;
     if ((rc = make_rows_map(&tmV, st->value_cache, lanes * d.S, d.dtype)) != CKV_OK) return rc;
     if ((rc = make_rows_map(&tmSK, st->sink_keys, lanes * d.NS, d.dtype)) != CKV_OK) return rc;
     if ((rc = make_rows_map(&tmSV, st->sink_values, lanes * d.NS, d.dtype)) != CKV_OK) return rc;
-    if ((rc = make_rows_map(&tmR, (uint8_t *)workspace + s.rope_slots, (uint64_t)sink_rows_padded(d) + d.S, d.dtype)) != CKV_OK)
+    if ((rc = make_rows_map(&tmR0, (uint8_t *)workspace + s.rope_slots, (uint64_t)sink_rows_padded(d) + d.S, d.dtype)) != CKV_OK)
+        return rc;
+    if ((rc = make_rows_map(&tmR1, (uint8_t *)workspace + s.rope_slots + s.image_bytes,
+                            (uint64_t)sink_rows_padded(d) + d.S, d.dtype)) != CKV_OK)
         return rc;
 
     uint8_t *ws = (uint8_t *)workspace;
@@ -971,6 +1145,8 @@ int launch_decode_tuned(const Dims &d, const ckv_layer_state *st, const void *q,
     p.partials = (float *)(ws + s.partials);
     p.new_scores = ws + s.new_scores;
     p.rope_slots = ws + s.rope_slots;
+    p.image_bytes = (long long)s.image_bytes;
+    p.image_tag = (long long *)(ws + s.image_tag);
     p.sink_rows_pad = sink_rows_padded(d);
     p.B = d.B; p.KVH = d.KVH; p.H = d.H; p.G = d.G; p.NS = d.NS; p.W = d.W; p.C = d.C; p.S = d.S;
     p.ema = ema; p.update = update; p.head_reduction = d.head_reduction; p.eager_fill = d.eager_fill;
@@ -1004,23 +1180,27 @@ int launch_decode_tuned(const Dims &d, const ckv_layer_state *st, const void *q,
         const long long work = (long long)(p.sink_rows_pad + d.S) * 16;
         int blocks = (int)((work + 255) / 256);
         blocks = blocks > 8 * sm_count() ? 8 * sm_count() : blocks;
+        if (hook) hook->before(stream, "rope_slots_kernel");
         rope_slots_kernel<<<blocks, 256, 0, stream>>>(p);
+        if (hook) hook->after(stream);
         CKV_CUDA_CHECK(cudaGetLastError());
     }
     if (hook) hook->before(stream, "decode_stream_kernel");
     const bool hi = d.G > 8;
     if (d.dtype == CKV_BF16) {
-        if (hi) decode_stream_kernel<__nv_bfloat16, 2><<<p.stream_grid, kStreamThreads, kStreamSmem, stream>>>(tmK, tmV, tmSK, tmSV, tmR, p);
-        else decode_stream_kernel<__nv_bfloat16, 1><<<p.stream_grid, kStreamThreads, kStreamSmem, stream>>>(tmK, tmV, tmSK, tmSV, tmR, p);
+        if (hi) decode_stream_kernel<__nv_bfloat16, 2><<<p.stream_grid, kStreamThreads, kStreamSmem, stream>>>(tmK, tmV, tmSK, tmSV, tmR0, tmR1, p);
+        else decode_stream_kernel<__nv_bfloat16, 1><<<p.stream_grid, kStreamThreads, kStreamSmem, stream>>>(tmK, tmV, tmSK, tmSV, tmR0, tmR1, p);
     } else {
-        if (hi) decode_stream_kernel<__half, 2><<<p.stream_grid, kStreamThreads, kStreamSmem, stream>>>(tmK, tmV, tmSK, tmSV, tmR, p);
-        else decode_stream_kernel<__half, 1><<<p.stream_grid, kStreamThreads, kStreamSmem, stream>>>(tmK, tmV, tmSK, tmSV, tmR, p);
+        if (hi) decode_stream_kernel<__half, 2><<<p.stream_grid, kStreamThreads, kStreamSmem, stream>>>(tmK, tmV, tmSK, tmSV, tmR0, tmR1, p);
+        else decode_stream_kernel<__half, 1><<<p.stream_grid, kStreamThreads, kStreamSmem, stream>>>(tmK, tmV, tmSK, tmSV, tmR0, tmR1, p);
     }
     if (hook) hook->after(stream);
     CKV_CUDA_CHECK(cudaGetLastError());
     const dim3 grid(chunks, (unsigned)lanes);
+    if (hook) hook->before(stream, "decode_finish_kernel");
     if (d.dtype == CKV_BF16) decode_finish_kernel<__nv_bfloat16><<<grid, kFinishThreads, 0, stream>>>(p);
     else decode_finish_kernel<__half><<<grid, kFinishThreads, 0, stream>>>(p);
+    if (hook) hook->after(stream);
     CKV_CUDA_CHECK(cudaGetLastError());
     note_launches(3);
     return CKV_OK;

@@ -170,6 +170,110 @@ __device__ __forceinline__ void update_lane_walk(const UpdateParams &p, int lane
     }
 }
 
+constexpr int kOneTokenMaxCascades = 8;
+
+// One new token for one lane, rows of 256 bytes, at most kOneTokenMaxCascades cascades: the same
+// result as update_lane_walk with K = 1, in one round trip to memory instead of one per cascade.
+// Which slot each hop touches follows from the counters alone (the token ripples through the full
+// cascades that accept it, then appends or competes with one newest slot), so a warp first reads the
+// rows, scores and original positions of every slot on the path at once (thread t < 16 holds 16 bytes
+// of each key row, t >= 16 of each value row), then resolves the carry chain in registers and issues
+// all stores.  The slots lie in different cascades, so no store can precede a load of the same slot.
+// s_stored / s_start / s_every hold the counters BEFORE the token (the caller has them in shared
+// memory already), sinks / seen likewise; new_score is the token's incoming score (bits of the cache
+// dtype), ignored under the stride rule (p.scr == nullptr means all-zero scores).
+__device__ __forceinline__ void update_lane_one_token(const UpdateParams &p, int lane, const long long *s_stored,
+                                                      const long long *s_start, const long long *s_every,
+                                                      long long sinks, long long seen, unsigned int new_score) {
+    const int b = lane / p.KVH, h = lane % p.KVH;
+    const int tid = threadIdx.x & 31;
+    const long long rti = seen + 1;
+    const bool is_v = tid >= 16;
+    const int chunk = tid & 15;
+    const uint4 *src = reinterpret_cast<const uint4 *>((is_v ? p.val : p.key) + b * p.ksb + h * p.ksh);
+    uint4 carry = src[chunk];
+    if (sinks < p.NS) {
+        uint8_t *dst = (is_v ? p.sink_v : p.sink_k) + ((long long)lane * p.NS + sinks) * 256;
+        reinterpret_cast<uint4 *>(dst)[chunk] = carry;
+        return;
+    }
+    uint8_t *rows = (is_v ? p.cache_v : p.cache_k) + (long long)lane * p.S * 256;
+    uint8_t *cs = p.cache_s + (long long)lane * p.S * p.esz;
+    long long *og = p.og_pos + (long long)lane * p.S;
+    const bool eager = p.eager_fill && (rti - 1 <= (long long)p.S + p.NS);
+
+    // the path: slot and kind of every hop (0 = append, 1 = evict and carry on, 2 = compete with the newest slot)
+    int slot[kOneTokenMaxCascades], kind[kOneTokenMaxCascades];
+    int n_hops = 0;
+#pragma unroll
+    for (int i = 0; i < kOneTokenMaxCascades; ++i) {
+        slot[i] = 0;
+        kind[i] = -1;
+    }
+    {
+        bool done = false;
+#pragma unroll
+        for (int i = 0; i < kOneTokenMaxCascades; ++i) {
+            if (i < p.C && !done) {
+                const bool do_i = eager || (floor_mod_ll(rti - 1 - p.NS, s_every[i]) == 0);
+                const long long stored_i = s_stored[i], start_i = s_start[i], l = (long long)i * p.W;
+                if ((do_i && stored_i < p.W) || (!do_i && stored_i == 0)) {
+                    slot[i] = (int)(l + start_i + stored_i);
+                    kind[i] = 0;
+                    done = true;
+                } else if (do_i) {
+                    slot[i] = (int)(l + start_i);
+                    kind[i] = 1;
+                } else {
+                    slot[i] = (int)(l + floor_mod_ll(start_i - 1, stored_i));
+                    kind[i] = 2;
+                    done = true;
+                }
+                n_hops = i + 1;
+            }
+        }
+    }
+    // one round of loads: the rows that move on, and the score / original position of every slot on the path
+    uint4 row[kOneTokenMaxCascades];
+#pragma unroll
+    for (int i = 0; i < kOneTokenMaxCascades; ++i)
+        if (kind[i] == 1) row[i] = reinterpret_cast<const uint4 *>(rows + (long long)slot[i] * 256)[chunk];
+    unsigned int my_s = 0;
+    long long my_og = 0;
+#pragma unroll
+    for (int i = 0; i < kOneTokenMaxCascades; ++i) {
+        if (tid == i && kind[i] >= 1) {
+            my_s = load_score_bits(cs + (long long)slot[i] * p.esz, p.esz);
+            my_og = og[slot[i]];
+        }
+    }
+    unsigned int carry_s = p.scr ? new_score : 0u;
+    long long carry_og = rti;
+    // resolve the chain and store
+#pragma unroll
+    for (int i = 0; i < kOneTokenMaxCascades; ++i) {
+        if (i < n_hops) {
+            const unsigned int slot_s = __shfl_sync(0xffffffffu, my_s, i);
+            const long long slot_og = __shfl_sync(0xffffffffu, my_og, i);
+            bool write = true;
+            if (kind[i] == 2)
+                write = score_bits_to_float(carry_s, p.dtype) >= score_bits_to_float(slot_s, p.dtype);
+            if (write) {
+                reinterpret_cast<uint4 *>(rows + (long long)slot[i] * 256)[chunk] = carry;
+                if (tid == 0) {
+                    store_score_bits(cs + (long long)slot[i] * p.esz, carry_s, p.esz);
+                    og[slot[i]] = carry_og;
+                }
+            }
+            if (kind[i] == 1) {
+                carry = row[i];
+                carry_s = slot_s;
+                carry_og = slot_og;
+            }
+        }
+    }
+}
+
 // Advance the lane-invariant counters by K tokens.  The branch taken by each
 // token depends only on its stream index and the counters, never on scores.
 static __device__ void advance_counters(long long *stored, long long *start, long long &sinks, long long seen,

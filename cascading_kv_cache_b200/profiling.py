@@ -24,5 +24,18 @@ def time_dominant_kernel(run_step, n_steps: int = 20):
     return total.value / launches, n.value, (name.value or b"").decode()
 
 
+def kernel_breakdown():
+    """Per-kernel totals of the collection the last ``time_dominant_kernel`` read: a list of
+    ``(kernel name, ms per launch, launches)``, largest total first."""
+    lib = _lib.load()
+    out, i = [], 0
+    while True:
+        name, ms, n = ctypes.c_char_p(), ctypes.c_double(0), ctypes.c_int32(0)
+        if lib.ckv_profile_kernel(i, ctypes.byref(name), ctypes.byref(ms), ctypes.byref(n)) != 0:
+            return out
+        out.append(((name.value or b"").decode(), ms.value / max(n.value, 1), n.value))
+        i += 1
+
+
 def last_launch_count() -> int:
     return int(_lib.load().ckv_last_launch_count())

@@ -263,15 +263,19 @@ int ckv_static_status(int32_t *status /* host */);
 int ckv_last_launch_count(void);
 
 /*
- * Optional CUDA-event timing of the dominant (key/value streaming) kernel of every following
- * ckv_attention call, with events owned by the library.  Replaces the BENCHMARK switch of the
- * reference's sink_cache(), which brackets its launch with CUDA events and prints the time
+ * Optional CUDA-event timing of the kernels of every following ckv_attention call, with events
+ * owned by the library.  Replaces the BENCHMARK switch of the reference's sink_cache(), which
+ * brackets its launch with CUDA events and prints the time
  * (cascade/models/cascading_cache.py:986-1026).  ckv_profile_read synchronises on the recorded
- * events, returns their summed duration, how many launches were timed and the kernel's name, and
- * starts a new collection.  Not thread-safe; meant for benchmarks.
+ * events, sums them per kernel, returns the kernel with the largest total (its summed duration, how
+ * many of its launches were timed, its name) and starts a new collection; ckv_profile_kernel then
+ * gives the totals of every timed kernel of that collection, largest first (index 0 is the one
+ * ckv_profile_read returned; CKV_E_ARG past the end).  Not thread-safe; meant for benchmarks.
  */
 int ckv_profile_enable(int enable);
 int ckv_profile_read(double *total_ms /* host */, int32_t *launches /* host */, const char **kernel_name /* host */);
+int ckv_profile_kernel(int32_t index, const char **kernel_name /* host */, double *total_ms /* host */,
+                       int32_t *launches /* host */);
 
 /*
  * Copy the status word of a ckv_attention workspace to the host (synchronises).  0 = no kernel of
