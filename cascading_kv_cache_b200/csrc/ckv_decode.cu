@@ -12,8 +12,8 @@
 //   contiguous range of that stream (a split of the key dimension that ignores lane borders, so
 //   all SMs stream the same number of bytes).  Two producer warps move each tile into shared memory
 //   with TMA boxes (cp.async.bulk.tensor, 128-byte swizzle, mbarrier completion) through two rings:
-//   K lo/hi and V lo/hi from the cache (L2 evict-first) through a 5-stage ring of 32 KB stages, the
-//   cos / sin rows of the tile's slots from the image (L2 evict-last) through a 3-stage ring of
+//   K lo/hi and V lo/hi from the cache (L2 evict-first) through a 4-stage ring of 32 KB stages, the
+//   cos / sin rows of the tile's slots from the image (L2 evict-last) through a 4-stage ring of
 //   16 KB stages.  The rings are separate because their sources differ: the K/V bytes come from HBM
 //   and need as many stages in flight as the memory latency asks for, the image sits in L2 and its
 //   stage is released as soon as the keys are rotated.  Sixteen consumer warps in two groups take
@@ -40,8 +40,12 @@ namespace ckv {
 namespace {
 
 constexpr int kTile = 64;                       // keys per stage
-constexpr int kStages = 5;                      // K/V ring
-constexpr int kStagesCS = 3;                    // cos/sin ring
+// Both ring depths are powers of two on purpose: every consumer warp turns the tile index into a stage and
+// a barrier phase once per tile, and with any other depth those are integer divisions in the hot loop
+// (5 + 3 stages ran 4 % slower than 4 + 4 for that reason alone).
+constexpr int kStages = 4;                      // K/V ring
+constexpr int kStagesCS = 4;                    // cos/sin ring
+static_assert((kStages & (kStages - 1)) == 0 && (kStagesCS & (kStagesCS - 1)) == 0, "ring depths: powers of two");
 constexpr int kGroupWarps = 8;                  // warps per consumer group: each owns 8 keys of a tile
 constexpr int kGroups = 2;                      // consumer groups working on alternate tiles
 constexpr int kComputeWarps = kGroupWarps * kGroups;
@@ -57,6 +61,7 @@ constexpr int kStreamSmem = kRingBytes + 1024 + 256 + kMergeBytes;
 constexpr int kPartialStride = 130;             // m, l, out[128] per head row
 constexpr unsigned kSpinLimit = 1u << 24;       // bounded mbarrier waits (each probe also sleeps)
 constexpr int kFinishThreads = 256;
+constexpr int kMaxParts = 160;                  // partials of one lane: at most one per stream CTA (one CTA per SM)
 
 struct DecodeParams {
     const void *q;
@@ -751,6 +756,8 @@ __device__ __forceinline__ void ema_pass_vec(const DecodeParams &p, const Schedu
 template <typename T>
 __global__ void __launch_bounds__(kFinishThreads, 3) decode_finish_kernel(DecodeParams p) {
     __shared__ float s_m[kMaxG], s_linv[kMaxG], s_snew[kMaxG], s_pnew[kMaxG];
+    __shared__ int s_part[kMaxParts];
+    __shared__ float s_w[kMaxG * kMaxParts];
     __shared__ long long s_stored[CKV_MAX_CASCADES], s_start[CKV_MAX_CASCADES], s_every[CKV_MAX_CASCADES];
     __shared__ long long s_new_stored[CKV_MAX_CASCADES], s_new_start[CKV_MAX_CASCADES];
     __shared__ long long s_new_sinks, s_new_total, s_tag[4];
@@ -766,8 +773,42 @@ __global__ void __launch_bounds__(kFinishThreads, 3) decode_finish_kernel(Decode
     const T *krow = reinterpret_cast<const T *>(p.knew) + b * p.ksb + kvh * p.ksh;
     const T *vrow = reinterpret_cast<const T *>(p.vnew) + b * p.ksb + kvh * p.ksh;
 
-    // 1. the new token's own logit per head: both operands rotated at max_pos and scaled
+    // 1. which of the stream kernel's partials belong to this lane: CTAs whose tile range meets the lane's.
+    //    Partial i comes from CTA cta_lo + i; CTAs with an empty tile range wrote nothing.  Worked out once
+    //    per block (the range arithmetic is 64-bit divisions) and kept in shared memory.
+    const long long a_tile = (long long)lane * sc.tiles_per_lane, b_tile = a_tile + sc.tiles_per_lane;
+    int cta_lo = 0, cta_hi = -1;
+    if (sc.tiles_per_lane > 0) {
+        cta_lo = (int)((a_tile * p.stream_grid) / sc.n_tiles);
+        while (cta_lo > 0 && cta_first_tile(cta_lo, sc.n_tiles, p.stream_grid) > a_tile) --cta_lo;
+        while (cta_lo + 1 < p.stream_grid && cta_first_tile(cta_lo + 1, sc.n_tiles, p.stream_grid) <= a_tile) ++cta_lo;
+        cta_hi = cta_lo;
+        while (cta_hi + 1 < p.stream_grid && cta_first_tile(cta_hi + 1, sc.n_tiles, p.stream_grid) < b_tile) ++cta_hi;
+    }
+    const int n_parts = min(cta_hi - cta_lo + 1, kMaxParts);
+    for (int i = tid; i < n_parts; i += kFinishThreads) {
+        const int c = cta_lo + i;
+        const bool wrote = cta_first_tile(c, sc.n_tiles, p.stream_grid) < cta_first_tile(c + 1, sc.n_tiles, p.stream_grid);
+        s_part[i] = wrote ? c + lane : -1;
+    }
+    __syncthreads();
+
+    // 2. one warp per head: the partials' (max, sum) are fetched first, the new token's own logit (both
+    //    operands rotated at max_pos and scaled) is worked out while they travel, then everything is merged
+    constexpr int kPartsPerLane = (kMaxParts + 31) / 32;
     for (int gh = warp; gh < p.G; gh += kFinishThreads / 32) {
+        float pm[kPartsPerLane], pl[kPartsPerLane];
+#pragma unroll
+        for (int j = 0; j < kPartsPerLane; ++j) {
+            const int i = lane_id + 32 * j;
+            pm[j] = -INFINITY;
+            pl[j] = 0.f;
+            if (i < n_parts && s_part[i] >= 0) {
+                const float *pr = p.partials + ((long long)s_part[i] * p.G + gh) * kPartialStride;
+                pm[j] = pr[0];
+                pl[j] = pr[1];
+            }
+        }
         const T *qrow = reinterpret_cast<const T *>(p.q) + b * p.qsb + (long long)(kvh * p.G + gh) * p.qsh;
         float part = 0.f;
 #pragma unroll
@@ -785,49 +826,27 @@ __global__ void __launch_bounds__(kFinishThreads, 3) decode_finish_kernel(Decode
         }
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
-        if (lane_id == 0) s_snew[gh] = rnd<T>(part);
-    }
-    __syncthreads();
-
-    // 2. merge the stream kernel's partials of this lane: CTAs whose tile range meets the lane's
-    const long long a_tile = (long long)lane * sc.tiles_per_lane, b_tile = a_tile + sc.tiles_per_lane;
-    int cta_lo = 0, cta_hi = -1;
-    if (sc.tiles_per_lane > 0) {
-        cta_lo = (int)((a_tile * p.stream_grid) / sc.n_tiles);
-        while (cta_lo > 0 && cta_first_tile(cta_lo, sc.n_tiles, p.stream_grid) > a_tile) --cta_lo;
-        while (cta_lo + 1 < p.stream_grid && cta_first_tile(cta_lo + 1, sc.n_tiles, p.stream_grid) <= a_tile) ++cta_lo;
-        cta_hi = cta_lo;
-        while (cta_hi + 1 < p.stream_grid && cta_first_tile(cta_hi + 1, sc.n_tiles, p.stream_grid) < b_tile) ++cta_hi;
-    }
-    // partial i of the lane comes from CTA cta_lo + i; CTAs with an empty tile range wrote nothing
-    const int n_parts = cta_hi - cta_lo + 1;
-    auto part = [&](int i, int row) -> const float * {
-        const int c = cta_lo + i;
-        if (cta_first_tile(c, sc.n_tiles, p.stream_grid) >= cta_first_tile(c + 1, sc.n_tiles, p.stream_grid))
-            return nullptr;
-        return p.partials + (long long)(c + lane) * p.G * kPartialStride + row * kPartialStride;
-    };
-    // one warp per head: lanes stride over the partials
-    for (int gh = warp; gh < p.G; gh += kFinishThreads / 32) {
-        float m = s_snew[gh];
-        for (int i = lane_id; i < n_parts; i += 32) {
-            const float *pr = part(i, gh);
-            if (pr) m = fmaxf(m, pr[0]);
-        }
+        const float snew = rnd<T>(part);
+        float m = snew;
+#pragma unroll
+        for (int j = 0; j < kPartsPerLane; ++j) m = fmaxf(m, pm[j]);
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
         float l = 0.f;
-        for (int i = lane_id; i < n_parts; i += 32) {
-            const float *pr = part(i, gh);
-            if (pr && pr[0] != -INFINITY) l += pr[1] * __expf(pr[0] - m);
+#pragma unroll
+        for (int j = 0; j < kPartsPerLane; ++j) {
+            const float w = pm[j] == -INFINITY ? 0.f : __expf(pm[j] - m);
+            l += pl[j] * w;
+            if (lane_id + 32 * j < n_parts) s_w[gh * kMaxParts + lane_id + 32 * j] = w;   // the partial's weight in the output
         }
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
-        l += __expf(s_snew[gh] - m);
+        l += __expf(snew - m);
         if (lane_id == 0) {
+            s_snew[gh] = snew;
             s_m[gh] = m;
             s_linv[gh] = 1.f / l;
-            s_pnew[gh] = __expf(s_snew[gh] - m) / l;
+            s_pnew[gh] = __expf(snew - m) / l;
         }
     }
     __syncthreads();
@@ -839,9 +858,10 @@ __global__ void __launch_bounds__(kFinishThreads, 3) decode_finish_kernel(Decode
         for (int idx = blockIdx.x * per_out + tid; idx < o_end; idx += kFinishThreads) {
             const int gh = idx >> 7, d = idx & 127;
             float acc = __expf(s_snew[gh] - s_m[gh]) * Elem<T>::to_f(vrow[d]);
+#pragma unroll 4
             for (int i = 0; i < n_parts; ++i) {
-                const float *pr = part(i, gh);
-                if (pr && pr[0] != -INFINITY) acc = fmaf(pr[2 + d], __expf(pr[0] - s_m[gh]), acc);
+                const float w = s_w[gh * kMaxParts + i];
+                if (w != 0.f) acc = fmaf(p.partials[((long long)s_part[i] * p.G + gh) * kPartialStride + 2 + d], w, acc);
             }
             T *orow = reinterpret_cast<T *>(p.out) + b * p.osb + (long long)(kvh * p.G + gh) * p.osh;
             orow[d] = Elem<T>::from_f(acc * s_linv[gh]);
@@ -1151,10 +1171,12 @@ int launch_decode_tuned(const Dims &d, const ckv_layer_state *st, const void *q,
     p.B = d.B; p.KVH = d.KVH; p.H = d.H; p.G = d.G; p.NS = d.NS; p.W = d.W; p.C = d.C; p.S = d.S;
     p.ema = ema; p.update = update; p.head_reduction = d.head_reduction; p.eager_fill = d.eager_fill;
     p.dtype = d.dtype;
-    p.stream_grid = sm_count();
+    p.stream_grid = sm_count() < kMaxParts ? sm_count() : kMaxParts;
     int chunks = 1;
-    if (ema) {
-        chunks = (int)((3 * (uint64_t)sm_count()) / lanes);  // one wave: the kernel is built for three blocks per SM
+    if (update) {
+        // one wave: the kernel is built for three blocks per SM.  Also without the EMA pass the blocks share
+        // the rewrite of the positions and of the next step's cos|sin image.
+        chunks = (int)((3 * (uint64_t)sm_count()) / lanes);
         chunks = chunks < 1 ? 1 : (chunks > 64 ? 64 : chunks);
     }
     p.finish_chunks = chunks;
