@@ -490,6 +490,99 @@ def time_cpu_c1():
             "seconds_total": t_prefill + t_decode}
 
 
+def run_c5(job, args):
+    """End to end (``--workload c5_e2e``): the Llama-3.1-8B architecture with random-init bf16 weights (32 layers,
+    hidden 4096, 32 q / 8 KV heads, FFN 14336, vocab 128256; N(0, 0.02) from seed 4, plain RoPE base 500000), a
+    prompt of seeded uniform token ids prefilled in strides of 4096 through the cascading cache (window 32768,
+    4 cascades, 64 sinks, EMA rule), then greedy decode tokens.  One sequence per GPU (rank r: seed 4 + r); the
+    generated ids are gathered at the end, the only collective."""
+    from cascading_kv_cache_b200.dist_utils import gather_token_ids
+    from cascading_kv_cache_b200.thin_model import CascadeForCausalLM, cascade_config, get_cache
+    dev = job.dev
+    cfg = cascade_config("llama", num_hidden_layers=args.c5_layers)
+    with torch.device(dev):
+        model = CascadeForCausalLM(cfg, "llama").to(torch.bfloat16).eval()
+    model.init_weights(seed=4)
+    cache = get_cache(model)
+    cache.beta = 0.9999
+    g = torch.Generator().manual_seed(4 + job.rank)
+    prompt = torch.randint(0, cfg.vocab_size, (1, args.c5_prompt), generator=g).to(dev)
+    stride, n_new = cfg._cascade_stride, args.c5_new_tokens
+    with torch.no_grad():      # warm-up on a scratch cache: kernel attributes, cuBLAS handles, workspaces
+        warm = get_cache(model)
+        model(prompt[:, :stride], past_key_values=warm, num_logits_to_keep=1)
+        model(prompt[:, :1], past_key_values=warm, num_logits_to_keep=1)
+        del warm
+    torch.cuda.empty_cache()
+    job.barrier()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    with ClockSampler(job.local_rank) as clocks, torch.no_grad():
+        ev[0].record()
+        for i in range(0, prompt.size(1), stride):
+            out = model(prompt[:, i:i + stride], past_key_values=cache, num_logits_to_keep=1)
+        ids = [out.logits[:, -1].argmax(-1)]
+        ev[1].record()
+        # the first half of the new tokens one host-driven forward at a time, the second half by replaying a
+        # CUDA graph of one whole decode step (32 layers + lm_head + argmax; the kernels read every counter
+        # from device memory, the host only advances its mirrors)
+        n_eager = (n_new - 1) // 2 if args.c5_graph else n_new - 1
+        for _ in range(n_eager):
+            out = model(ids[-1][:, None], past_key_values=cache, num_logits_to_keep=1)
+            ids.append(out.logits[:, -1].argmax(-1))
+        ev[2].record()
+        n_graph, graph_note = n_new - 1 - n_eager, None
+        if n_graph > 0:
+            try:
+                tok_in = ids[-1][:, None].clone()
+                side = torch.cuda.Stream()
+                side.wait_stream(torch.cuda.current_stream())
+                cg = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(cg, stream=side):
+                    tok_out = model(tok_in, past_key_values=cache, num_logits_to_keep=1).logits[:, -1].argmax(-1)
+                for l in range(cfg.num_hidden_layers):
+                    cache.note_tokens_seen(l, -1)        # capturing ran the host mirrors forward, not the device
+                torch.cuda.current_stream().wait_stream(side)
+                ev.append(torch.cuda.Event(enable_timing=True))
+                ev.append(torch.cuda.Event(enable_timing=True))
+                ev[3].record()
+                for _ in range(n_graph):
+                    cg.replay()
+                    for l in range(cfg.num_hidden_layers):
+                        cache.note_tokens_seen(l, 1)
+                    ids.append(tok_out.clone())
+                    tok_in.copy_(tok_out[:, None])
+                ev[4].record()
+            except Exception as exc:                     # keep the line: finish the tokens without a graph
+                graph_note = "graph capture failed: %s" % str(exc)[:200]
+                torch.cuda.synchronize()
+                for _ in range(n_new - len(ids)):
+                    out = model(ids[-1][:, None], past_key_values=cache, num_logits_to_keep=1)
+                    ids.append(out.logits[:, -1].argmax(-1))
+        job.barrier()
+    ids = torch.stack(ids, dim=1)[0]
+    all_ids = gather_token_ids(ids)
+    ms_prefill, ms_decode = job.max_over_ranks([ev[0].elapsed_time(ev[1]), ev[1].elapsed_time(ev[2])])
+    ms_graph = job.max_over_ranks([ev[3].elapsed_time(ev[4])])[0] if len(ev) == 5 else None
+    if job.rank == 0:
+        n = job.world
+        line = {"metric": "e2e_prefill_tokens_per_s", "value": n * args.c5_prompt / (ms_prefill * 1e-3), "unit": "tokens/s",
+                "n_gpus": n, "steps": 1, "warmup": 1, "ms_per_step": ms_prefill + ms_decode, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": "c5_e2e", "layers": args.c5_layers, "prompt_tokens": args.c5_prompt,
+                           "new_tokens": n_new, "stride": stride, "sequences_per_gpu": 1,
+                           "rope": "theta 500000, no frequency scaling"},
+                "prefill_s": ms_prefill * 1e-3, "decode_s": ms_decode * 1e-3,
+                "decode_ms_per_token": ms_decode / max(n_eager, 1), "decode_tokens_timed": n_eager,
+                "decode_tokens_per_s": n * n_eager / (ms_decode * 1e-3) if n_eager > 0 else None,
+                "decode_graph_ms_per_token": ms_graph / n_graph if ms_graph else None,
+                "decode_graph_tokens_per_s": n * n_graph / (ms_graph * 1e-3) if ms_graph else None,
+                "decode_graph_tokens_timed": n_graph if ms_graph else 0, "decode_graph_note": graph_note,
+                "generated_ids_shape": list(all_ids.shape), "first_ids": all_ids[0, :8].tolist(),
+                "cache_tokens": cache.get_seq_length(0), "kernel_status": cache.kernel_status(),
+                "clocks": clocks.summary()}
+        print(json.dumps(line), flush=True)
+
+
 def cpu_sample_size(w):
     return max(1, w["B"] // 4)
 
@@ -520,7 +613,11 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
-    ap.add_argument("--workload", default="c2_llama8b_decode", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c2_llama8b_decode", choices=sorted(WORKLOADS) + ["c5_e2e"])
+    ap.add_argument("--c5-layers", type=int, default=32)
+    ap.add_argument("--c5-prompt", type=int, default=131072)
+    ap.add_argument("--c5-new-tokens", type=int, default=256)
+    ap.add_argument("--c5-graph", type=int, default=1, help="decode the second half of the new tokens from a CUDA graph")
     ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
                     help="N > 1: partition the global batch (strong, default) or run the whole batch on every rank")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -537,11 +634,20 @@ def main():
     ap.add_argument("--sustained-steps", type=int, default=1000)
     ap.add_argument("--stream-chunks", type=int, default=256)
     args = ap.parse_args()
+    job = Job()
+    if args.workload == "c5_e2e":
+        if args.impl == "reference":
+            if job.rank == 0:
+                print(json.dumps({"impl": "reference", "unavailable": "the end-to-end configuration is timed on the "
+                                  "GPU arm only; its CPU baseline is one layer-chunk (cpu_baseline.prefill of the default run)"}))
+            return
+        job.start()
+        run_c5(job, args)
+        job.stop()
+        return
     w = dict(WORKLOADS[args.workload])
     if args.batch > 0:
         w["B"] = args.batch
-
-    job = Job()
     if args.impl == "reference":
         run_reference(args, w, job)
         return

@@ -26,7 +26,7 @@ EXPORTS = ("ckv_abi_version", "ckv_last_error", "ckv_cascade_update", "ckv_updat
            "ckv_attention_workspace_bytes", "ckv_attention_workspace_bytes_for",
            "ckv_attention", "ckv_last_launch_count", "ckv_profile_enable", "ckv_profile_read", "ckv_profile_kernel", "ckv_read_status",
            "ckv_static_scratch_bytes", "ckv_attention_static", "ckv_static_status", "ckv_advance_counters_host",
-           "ckv_dense_attention_workspace_bytes", "ckv_dense_attention")
+           "ckv_dense_attention_workspace_bytes", "ckv_dense_attention", "ckv_bounds_status", "ckv_selftest_bounded_wait")
 
 
 class CkvConfig(ctypes.Structure):
@@ -84,6 +84,10 @@ def load():
     lib.ckv_dense_attention.argtypes = [vp, i64, i64, i64, vp, i64, i64, i64, vp, i64, i64, i64, vp,
                                         i32, i32, i32, i32, i32, i32, i32, ctypes.c_double, ctypes.c_double, i32,
                                         vp, vp, vp, i64, i64, i64, vp, vp, sz, vp]
+    lib.ckv_selftest_bounded_wait.restype = ctypes.c_int
+    lib.ckv_selftest_bounded_wait.argtypes = [i32, vp, vp]
+    lib.ckv_bounds_status.restype = ctypes.c_int
+    lib.ckv_bounds_status.argtypes = [ctypes.POINTER(i32)]
     lib.ckv_static_status.restype = ctypes.c_int
     lib.ckv_static_status.argtypes = [ctypes.POINTER(i32)]
     lib.ckv_last_launch_count.restype = ctypes.c_int

@@ -11,6 +11,9 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libckv_b200.so")
 OBJ_DIR = os.path.join(PKG_DIR, "build")
+# debug build with bounds checks in the update kernels (see ckv_bounds_status in the header)
+BOUNDS_LIB_PATH = os.path.join(PKG_DIR, "libckv_b200_bounds.so")
+BOUNDS_OBJ_DIR = os.path.join(PKG_DIR, "build", "bounds")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]
@@ -26,18 +29,20 @@ def _newest_source_mtime():
     return max(os.path.getmtime(f) for f in files)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile every .cu under csrc/ and link libckv_b200.so next to this file."""
-    if not force and os.path.exists(LIB_PATH) and os.path.getmtime(LIB_PATH) >= _newest_source_mtime():
-        return LIB_PATH
+def build(force: bool = False, verbose: bool = False, bounds: bool = False) -> str:
+    """Compile every .cu under csrc/ and link libckv_b200.so next to this file (``bounds``: the debug
+    build libckv_b200_bounds.so, compiled with -DCKV_BOUNDS)."""
+    lib_path, obj_dir = (BOUNDS_LIB_PATH, BOUNDS_OBJ_DIR) if bounds else (LIB_PATH, OBJ_DIR)
+    if not force and os.path.exists(lib_path) and os.path.getmtime(lib_path) >= _newest_source_mtime():
+        return lib_path
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not os.path.exists(nvcc):
         raise RuntimeError("nvcc not found: libckv_b200.so must be built where the CUDA toolkit is installed")
-    os.makedirs(OBJ_DIR, exist_ok=True)
-    extra = ["-Xptxas", "-v"] if verbose else []
+    os.makedirs(obj_dir, exist_ok=True)
+    extra = (["-Xptxas", "-v"] if verbose else []) + (["-DCKV_BOUNDS"] if bounds else [])
 
     def compile_one(src):
-        obj = os.path.join(OBJ_DIR, src[:-3] + ".o")
+        obj = os.path.join(obj_dir, src[:-3] + ".o")
         cmd = [nvcc, *NVCC_FLAGS, *extra, "-c", os.path.join(CSRC, src), "-o", obj]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
@@ -48,12 +53,12 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
     with ThreadPoolExecutor(max_workers=8) as ex:
         objs = list(ex.map(compile_one, sources()))
-    cmd = [nvcc, "-shared", "-o", LIB_PATH, *objs, "-gencode", "arch=compute_100a,code=sm_100a"]
+    cmd = [nvcc, "-shared", "-o", lib_path, *objs, "-gencode", "arch=compute_100a,code=sm_100a"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
-    return LIB_PATH
+    return lib_path
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, bounds="--bounds" in sys.argv))

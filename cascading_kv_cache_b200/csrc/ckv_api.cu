@@ -183,6 +183,31 @@ extern "C" int ckv_advance_counters_host(const ckv_config *cfg, const int64_t *e
     return CKV_OK;
 }
 
+#ifdef CKV_BOUNDS
+namespace ckv {
+int read_bounds_status_serial(int *out);
+int read_bounds_status_chunk(int *out);
+int read_bounds_status_decode(int *out);
+}  // namespace ckv
+#endif
+
+// Debug builds (-DCKV_BOUNDS) only: the first bounds violation the update kernels recorded since the last
+// call, 0 if none (4 | source line << 8 otherwise); clears the record.  Synchronises.
+extern "C" int ckv_bounds_status(int32_t *status) {
+    if (!status) return fail(CKV_E_ARG, "status is null");
+#ifdef CKV_BOUNDS
+    CKV_CUDA_CHECK(cudaDeviceSynchronize());
+    int a = 0, b = 0, c = 0;
+    if (read_bounds_status_serial(&a) || read_bounds_status_chunk(&b) || read_bounds_status_decode(&c))
+        return fail(CKV_E_CUDA, "reading the bounds status failed");
+    *status = a ? a : (b ? b : c);
+    return CKV_OK;
+#else
+    *status = 0;
+    return fail(CKV_E_UNSUPPORTED, "this library was built without CKV_BOUNDS");
+#endif
+}
+
 extern "C" int ckv_last_launch_count(void) { return g_launches; }
 
 extern "C" int ckv_profile_enable(int enable) {
@@ -226,6 +251,15 @@ extern "C" int ckv_profile_kernel(int32_t index, const char **kernel_name, doubl
     if (total_ms) *total_ms = g_totals[index].ms;
     if (launches) *launches = g_totals[index].launches;
     return CKV_OK;
+}
+
+extern "C" int ckv_selftest_bounded_wait(int32_t which, void *workspace, void *cuda_stream) {
+    if (!workspace) return fail(CKV_E_ARG, "workspace is null");
+    if (which != 1 && which != 2) return fail(CKV_E_ARG, "which must be 1 (decode kernels) or 2 (prefill kernels)");
+    cudaStream_t stream = (cudaStream_t)cuda_stream;
+    CKV_CUDA_CHECK(cudaMemsetAsync(workspace, 0, 4, stream));
+    return which == 1 ? launch_decode_wait_selftest((int *)workspace, stream)
+                      : launch_prefill_wait_selftest((int *)workspace, stream);
 }
 
 extern "C" int ckv_read_status(const void *workspace, int32_t *status) {

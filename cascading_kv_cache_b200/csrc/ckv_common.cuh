@@ -137,6 +137,11 @@ int launch_prefill_tuned(const Dims &d, const ckv_layer_state *st, const void *q
                          const void *ema_w_new, void *out, int64_t osb, int64_t osh, int64_t ost, void *workspace,
                          size_t workspace_bytes, int flags, cudaStream_t stream, ProfileHook *hook);
 
+// Self-tests of the bounded waits: a wait on a barrier phase that nothing completes must give up and raise the
+// status word (decode: code 1; prefill: 2 | line << 8).
+int launch_decode_wait_selftest(int *status, cudaStream_t stream);
+int launch_prefill_wait_selftest(int *status, cudaStream_t stream);
+
 // Kernel attributes (opt-in shared memory sizes) belong to a device's context: a process that drives
 // several GPUs has to set them once on each.  Returns true the first time it sees the current device.
 inline bool first_use_on_this_device(bool (&seen)[64]) {

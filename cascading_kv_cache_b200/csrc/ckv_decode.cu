@@ -119,8 +119,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, unsigned parity) {
 }
 // Bounded wait: gives up after kSpinLimit probes, raises the status flag and reports failure so
 // that the caller leaves its loop instead of hanging the GPU.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, unsigned parity, int *status) {
-    for (unsigned n = 0; n < kSpinLimit; ++n) {
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, unsigned parity, int *status, unsigned limit = kSpinLimit) {
+    for (unsigned n = 0; n < limit; ++n) {
         if (mbar_try_wait(bar, parity)) return true;
         if (n > 64) __nanosleep(64);
         if ((n & 1023) == 1023 && *((volatile int *)status) != 0) return false;
@@ -240,6 +240,18 @@ __device__ __forceinline__ Schedule make_schedule(const DecodeParams &p) {
 
 __device__ __forceinline__ long long cta_first_tile(long long cta, long long n_tiles, int grid) {
     return (cta * n_tiles) / grid;
+}
+
+// Self-test of the bounded wait: one thread waits, with a short limit, for a barrier phase that nothing will
+// ever complete.  The wait must give up, raise the status word and return; the kernel then ends normally.
+__global__ void decode_wait_selftest_kernel(int *status) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        const bool arrived = mbar_wait(&bar, 0, status, 1u << 12);
+        if (arrived) atomicExch(status, -1);     // cannot happen: nobody arrives on this barrier
+    }
 }
 
 // ------------------------------------------------------------------------------ rope pre-pass
@@ -910,6 +922,8 @@ __global__ void __launch_bounds__(kFinishThreads, 3) decode_finish_kernel(Decode
         advance_counters(s_new_stored, s_new_start, sinks, sc.seen, s_every, 1, p.NS, p.W, p.C, p.S, p.eager_fill);
         long long total = 0;
         for (int i = 0; i < p.C; ++i) total += s_new_stored[i];
+        for (int i = 0; i < p.C; ++i)
+            if (!CKV_COUNTERS_OK(s_new_stored[i], s_new_start[i], p.W)) s_new_stored[i] = s_new_start[i] = 0;
         s_new_sinks = sinks;
         s_new_total = total;
         const ImageTag t = make_image_tag(p, sc.seen + 1, sinks, s_new_stored, s_new_start);
@@ -1227,5 +1241,15 @@ int launch_decode_tuned(const Dims &d, const ckv_layer_state *st, const void *q,
     note_launches(3);
     return CKV_OK;
 }
+
+int launch_decode_wait_selftest(int *status, cudaStream_t stream) {
+    decode_wait_selftest_kernel<<<1, 32, 0, stream>>>(status);
+    CKV_CUDA_CHECK(cudaGetLastError());
+    return CKV_OK;
+}
+
+#ifdef CKV_BOUNDS
+int read_bounds_status_decode(int *out) { return read_bounds_status_of_this_unit(out); }
+#endif
 
 }  // namespace ckv

@@ -212,14 +212,15 @@ __device__ __forceinline__ unsigned long long global_ns() {
 }
 // Bounded wait.  On a time-out the status word becomes 2 | (source line of the wait << 8) -- the first
 // wait to give up wins -- and every other wait of the grid returns false soon after.
-__device__ __forceinline__ bool bar_wait_at(uint64_t *bar, unsigned parity, int *status, int line) {
+__device__ __forceinline__ bool bar_wait_at(uint64_t *bar, unsigned parity, int *status, int line,
+                                            unsigned long long limit_ns = kWaitLimitNs) {
     if (bar_try(bar, parity)) return true;
     const unsigned long long t_start = global_ns();
     for (unsigned n = 1;; ++n) {
         if (bar_try(bar, parity)) return true;
         if ((n & 15) == 15) {
             if (*((volatile int *)status) != 0) return false;
-            if (global_ns() - t_start > kWaitLimitNs) break;
+            if (global_ns() - t_start > limit_ns) break;
         }
     }
     atomicCAS(status, 0, 2 | (line << 8));
@@ -1501,7 +1502,24 @@ PrefillScratch prefill_scratch(const Dims &d, int K) {
     return s;
 }
 
+// Self-test of the bounded wait (see decode_wait_selftest_kernel): a 20 ms limit on a phase nobody completes.
+__global__ void prefill_wait_selftest_kernel(int *status) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        bar_init(&bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        const bool arrived = bar_wait_at(&bar, 0, status, __LINE__, 20000000ull);
+        if (arrived) atomicExch(status, -1);
+    }
+}
+
 }  // namespace
+
+int launch_prefill_wait_selftest(int *status, cudaStream_t stream) {
+    prefill_wait_selftest_kernel<<<1, 32, 0, stream>>>(status);
+    CKV_CUDA_CHECK(cudaGetLastError());
+    return CKV_OK;
+}
 
 bool prefill_tuned_supported(const Dims &d, int n_tokens) {
     return n_tokens >= 2 && (d.dtype == CKV_BF16 || d.dtype == CKV_F16) && d.D == 128 && d.G <= 16 &&

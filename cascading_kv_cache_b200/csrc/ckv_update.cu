@@ -50,6 +50,7 @@ __global__ void __launch_bounds__(256) update_finalize_kernel(FinalizeParams p) 
         advance_counters(s_stored, s_start, sinks, seen, s_every, p.K, p.NS, p.W, p.C, p.S, p.eager_fill);
         long long total = 0;
         for (int i = 0; i < p.C; ++i) {
+            if (!CKV_COUNTERS_OK(s_stored[i], s_start[i], p.W)) s_stored[i] = s_start[i] = 0;   // keep what follows in range
             p.stored_tokens[i] = s_stored[i];
             p.start_indices[i] = s_start[i];
             total += s_stored[i];
@@ -122,5 +123,9 @@ int launch_update_serial(const Dims &d, const ckv_layer_state *st, const void *k
     note_launches(2);
     return CKV_OK;
 }
+
+#ifdef CKV_BOUNDS
+int read_bounds_status_serial(int *out) { return read_bounds_status_of_this_unit(out); }
+#endif
 
 }  // namespace ckv

@@ -221,6 +221,10 @@ __device__ void load_counters(const UpdateParams &u, Shared &sh) {
         sh.start[i] = u.start_indices[i];
         sh.every[i] = u.every_n[i];
         sh.casc_cnt[i] = 0;
+        if (!CKV_COUNTERS_OK(sh.count[i], sh.start[i], u.W)) {     // debug build: report, then keep what follows in range
+            sh.count[i] = sh.count[i] < 0 ? 0 : (sh.count[i] > u.W ? u.W : sh.count[i]);
+            sh.start[i] = floor_mod_ll(sh.start[i], u.W);
+        }
     }
     if (threadIdx.x == 0) sh.casc_off[0] = 0;
     __syncthreads();
@@ -250,6 +254,7 @@ __device__ __forceinline__ void execute_moves(const UpdateParams &u, int lane, c
             if (idx < total) {
                 const int e = idx / nchunk, c = idx % nchunk;
                 const int dst = plan[2 * e], id = plan[2 * e + 1];
+                if (!CKV_IN_BOUNDS(dst >= 0 && dst < u.S && id >= 0 && id < u.K + u.S)) continue;
                 const uint4 *sk, *sv;
                 if (id < u.K) {
                     sk = reinterpret_cast<const uint4 *>(u.key + b * u.ksb + h * u.ksh + (long long)id * u.kst);
@@ -487,5 +492,9 @@ int launch_update_chunk(const Dims &d, const ckv_layer_state *st, const void *ke
     note_launches(launches);
     return CKV_OK;
 }
+
+#ifdef CKV_BOUNDS
+int read_bounds_status_chunk(int *out) { return read_bounds_status_of_this_unit(out); }
+#endif
 
 }  // namespace ckv

@@ -18,6 +18,30 @@ struct UpdateParams {
     int KVH, K, NS, W, C, S, row_bytes, esz, dtype, eager_fill;
 };
 
+// ---- debug bounds checks (-DCKV_BOUNDS) ------------------------------------------------------------
+// The stand-in for a memory checker on machines where none can be run: every slot index the update
+// computes, and the counters it computes them from, are checked before use.  A violation records
+// code 4 | (source line << 8) in a per-translation-unit status word and SKIPS the access; nothing
+// traps.  ckv_bounds_status() (C ABI) reads and clears the words of all translation units.  In the
+// ordinary build the checks compile to nothing.
+#ifdef CKV_BOUNDS
+static __device__ int g_bounds_status;
+__device__ __forceinline__ bool bounds_ok(bool ok, int line) {
+    if (!ok) atomicCAS(&g_bounds_status, 0, 4 | (line << 8));
+    return ok;
+}
+#define CKV_IN_BOUNDS(cond) ::ckv::bounds_ok((cond), __LINE__)
+static inline int read_bounds_status_of_this_unit(int *out) {
+    int zero = 0;
+    if (cudaMemcpyFromSymbol(out, g_bounds_status, sizeof(int)) != cudaSuccess) return -1;
+    return cudaMemcpyToSymbol(g_bounds_status, &zero, sizeof(int)) == cudaSuccess ? 0 : -1;
+}
+#else
+#define CKV_IN_BOUNDS(cond) true
+#endif
+// counters of one cascade: at most W tokens stored, ring start inside the window
+#define CKV_COUNTERS_OK(stored, start, W) CKV_IN_BOUNDS((stored) >= 0 && (stored) <= (W) && (start) >= 0 && (start) < (W))
+
 __device__ __forceinline__ float score_bits_to_float(unsigned int bits, int dtype) {
     if (dtype == CKV_F32) return __uint_as_float(bits);
     if (dtype == CKV_BF16) return __uint_as_float(bits << 16);
@@ -72,6 +96,7 @@ __device__ __forceinline__ void update_lane_walk(const UpdateParams &p, int lane
             }
         }
         if (sinks < p.NS) {
+            if (!CKV_IN_BOUNDS(sinks >= 0)) return;
             uint4 *dk = reinterpret_cast<uint4 *>(p.sink_k + ((long long)lane * p.NS + sinks) * row);
             uint4 *dv = reinterpret_cast<uint4 *>(p.sink_v + ((long long)lane * p.NS + sinks) * row);
 #pragma unroll
@@ -96,8 +121,10 @@ __device__ __forceinline__ void update_lane_walk(const UpdateParams &p, int lane
             const bool do_i = eager || (floor_mod_ll(rti - 1 - p.NS, s_every[i]) == 0);
             const long long stored_i = s_stored[i];
             const long long start_i = s_start[i];
+            if (!CKV_COUNTERS_OK(stored_i, start_i, p.W)) return;
             if ((do_i && stored_i < p.W) || (!do_i && stored_i == 0)) {
                 const long long t = l + start_i + stored_i;
+                if (!CKV_IN_BOUNDS(t < p.S)) return;
                 uint4 *dk = reinterpret_cast<uint4 *>(ck + t * row);
                 uint4 *dv = reinterpret_cast<uint4 *>(cv + t * row);
 #pragma unroll
@@ -193,6 +220,7 @@ __device__ __forceinline__ void update_lane_one_token(const UpdateParams &p, int
     const uint4 *src = reinterpret_cast<const uint4 *>((is_v ? p.val : p.key) + b * p.ksb + h * p.ksh);
     uint4 carry = src[chunk];
     if (sinks < p.NS) {
+        if (!CKV_IN_BOUNDS(sinks >= 0)) return;
         uint8_t *dst = (is_v ? p.sink_v : p.sink_k) + ((long long)lane * p.NS + sinks) * 256;
         reinterpret_cast<uint4 *>(dst)[chunk] = carry;
         return;
@@ -217,6 +245,7 @@ __device__ __forceinline__ void update_lane_one_token(const UpdateParams &p, int
             if (i < p.C && !done) {
                 const bool do_i = eager || (floor_mod_ll(rti - 1 - p.NS, s_every[i]) == 0);
                 const long long stored_i = s_stored[i], start_i = s_start[i], l = (long long)i * p.W;
+                if (!CKV_COUNTERS_OK(stored_i, start_i, p.W)) return;
                 if ((do_i && stored_i < p.W) || (!do_i && stored_i == 0)) {
                     slot[i] = (int)(l + start_i + stored_i);
                     kind[i] = 0;
@@ -233,6 +262,9 @@ __device__ __forceinline__ void update_lane_one_token(const UpdateParams &p, int
             }
         }
     }
+#pragma unroll
+    for (int i = 0; i < kOneTokenMaxCascades; ++i)
+        if (kind[i] >= 0 && !CKV_IN_BOUNDS(slot[i] >= 0 && slot[i] < p.S)) return;
     // one round of loads: the rows that move on, and the score / original position of every slot on the path
     uint4 row[kOneTokenMaxCascades];
 #pragma unroll

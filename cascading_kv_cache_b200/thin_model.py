@@ -1,0 +1,173 @@
+"""A thin decoder stack around the patched attention: what the end-to-end configuration needs.
+
+The reference runs its attention inside forked Hugging Face models
+(cascade/models/llama/modeling_llama.py:701-782 decoder layer, :939-1058 model, :1164-1256 causal LM;
+cascade/models/qwen2/modeling_qwen2.py likewise), which cannot be constructed under the installed
+transformers.  This module is the same computation with nothing else around it: token embedding,
+``L x [RMSNorm -> cascade attention -> residual -> RMSNorm -> SwiGLU MLP -> residual]``, final RMSNorm,
+``lm_head``.  The attention is ``LlamaCascadeAttention`` / ``Qwen2CascadeAttention`` (hand-written kernels
+behind the C ABI); the dense layers are plain ``torch.nn.Linear`` (library GEMMs), RMSNorm follows
+modeling_llama.py:113-127 (fp32 variance, weight applied after the cast back).
+
+Configuration: a Hugging Face ``LlamaConfig`` / ``Qwen2Config`` carrying the reference's private fields
+(cascade/main/llama_eval.py:143-152): ``_sinks, _cascades, _window, _cascade_func, _head_reduction,
+_cascade_stride, _homogeneous_heads, _do_og_pos``, plus ``_batch_size``.  ``get_cache(model)`` builds the
+cache from them as the reference's helper does (cascade/models/test.py:21-39).
+"""
+from __future__ import annotations
+
+import types
+from typing import Optional
+
+import torch
+from torch import nn
+
+from .cascade_attention import LlamaCascadeAttention, Qwen2CascadeAttention, sample_monkeypatch
+from .cascading_cache import CascadingKVCache
+
+
+class RMSNorm(nn.Module):
+    """modeling_llama.py:113-127 of the reference."""
+
+    def __init__(self, hidden_size: int, eps: float = 1e-6):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(hidden_size))
+        self.variance_epsilon = eps
+
+    def forward(self, hidden_states):
+        input_dtype = hidden_states.dtype
+        hidden_states = hidden_states.to(torch.float32)
+        variance = hidden_states.pow(2).mean(-1, keepdim=True)
+        hidden_states = hidden_states * torch.rsqrt(variance + self.variance_epsilon)
+        return self.weight * hidden_states.to(input_dtype)
+
+
+class SwiGLU(nn.Module):
+    """LlamaMLP / Qwen2MLP: ``down(silu(gate(x)) * up(x))`` (modeling_llama.py:282-313)."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int):
+        super().__init__()
+        self.gate_proj = nn.Linear(hidden_size, intermediate_size, bias=False)
+        self.up_proj = nn.Linear(hidden_size, intermediate_size, bias=False)
+        self.down_proj = nn.Linear(intermediate_size, hidden_size, bias=False)
+
+    def forward(self, x):
+        return self.down_proj(nn.functional.silu(self.gate_proj(x)) * self.up_proj(x))
+
+
+class DecoderLayer(nn.Module):
+    """modeling_llama.py:701-782: pre-norm attention and MLP with residuals."""
+
+    def __init__(self, config, layer_idx: int, attention_cls):
+        super().__init__()
+        self.self_attn = attention_cls(config, layer_idx)
+        self.mlp = SwiGLU(config.hidden_size, config.intermediate_size)
+        self.input_layernorm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps)
+        self.post_attention_layernorm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps)
+
+    def forward(self, hidden_states, past_key_values):
+        residual = hidden_states
+        hidden_states = self.input_layernorm(hidden_states)
+        hidden_states, _, _ = self.self_attn(hidden_states, past_key_values=past_key_values, use_cache=True)
+        hidden_states = residual + hidden_states
+        residual = hidden_states
+        hidden_states = self.post_attention_layernorm(hidden_states)
+        return residual + self.mlp(hidden_states)
+
+
+class CascadeModel(nn.Module):
+    def __init__(self, config, attention_cls):
+        super().__init__()
+        self.config = config
+        self.embed_tokens = nn.Embedding(config.vocab_size, config.hidden_size)
+        self.layers = nn.ModuleList([DecoderLayer(config, i, attention_cls) for i in range(config.num_hidden_layers)])
+        self.norm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps)
+
+    def forward(self, input_ids, past_key_values):
+        hidden_states = self.embed_tokens(input_ids)
+        for layer in self.layers:
+            hidden_states = layer(hidden_states, past_key_values)
+        return self.norm(hidden_states)
+
+
+class CascadeForCausalLM(nn.Module):
+    """``model(input_ids, past_key_values=cache)`` -> object with ``.logits`` and ``.past_key_values``
+    (modeling_llama.py:1164-1256).  ``num_logits_to_keep`` > 0 applies ``lm_head`` to the last positions only:
+    a 4096-token prefill chunk needs one row of logits, not 4096 x vocab."""
+
+    def __init__(self, config, family: str = "llama"):
+        super().__init__()
+        if family not in ("llama", "qwen2"):
+            raise ValueError(f"unknown model family {family}")
+        self.config = config
+        self.family = family
+        self.model = CascadeModel(config, LlamaCascadeAttention if family == "llama" else Qwen2CascadeAttention)
+        self.lm_head = nn.Linear(config.hidden_size, config.vocab_size, bias=False)
+        sample_monkeypatch(self)
+
+    def forward(self, input_ids, past_key_values: CascadingKVCache, num_logits_to_keep: int = 0, **_):
+        hidden_states = self.model(input_ids, past_key_values)
+        if num_logits_to_keep > 0:
+            hidden_states = hidden_states[:, -num_logits_to_keep:]
+        return types.SimpleNamespace(logits=self.lm_head(hidden_states), past_key_values=past_key_values)
+
+    @torch.no_grad()
+    def generate(self, input_ids, past_key_values: CascadingKVCache, max_new_tokens: int = 128,
+                 do_sample: bool = False, **kwargs):
+        """The reference's generation path: ``_sample`` bound by ``sample_monkeypatch`` -- the prompt in strides of
+        ``config._cascade_stride`` through the cascading cache, then one token at a time."""
+        return self._sample(input_ids, past_key_values, max_new_tokens=max_new_tokens, do_sample=do_sample,
+                            num_logits_to_keep=1, **kwargs)
+
+    @torch.no_grad()
+    def init_weights(self, seed: int, std: float = 0.02):
+        """Random N(0, std) matrices and embeddings from ``seed`` (norm weights stay 1, biases 0), drawn on the
+        parameters' device in their order of registration."""
+        dev = self.lm_head.weight.device
+        g = torch.Generator(device=dev).manual_seed(seed)
+        for name, p in self.named_parameters():
+            if p.dim() >= 2:
+                p.copy_(torch.randn(p.shape, generator=g, device=dev, dtype=torch.float32) * std)
+            elif name.endswith("bias"):
+                p.zero_()
+        return self
+
+
+def cascade_config(family: str = "llama", hidden_size: int = 4096, intermediate_size: int = 14336,
+                   num_hidden_layers: int = 32, num_attention_heads: int = 32, num_key_value_heads: int = 8,
+                   vocab_size: int = 128256, rope_theta: float = 500000.0, rms_norm_eps: float = 1e-5,
+                   sinks: int = 64, cascades: int = 4, window: int = 32768, cascade_func: str = "pow2",
+                   head_reduction: str = "max", cascade_stride: int = 4096, homogeneous_heads: bool = False,
+                   do_og_pos: bool = False, batch_size: int = 1):
+    """A Hugging Face config with the reference's private cascade fields; defaults = Llama-3.1-8B shapes with a
+    plain RoPE base (no frequency scaling)."""
+    if family == "llama":
+        from transformers import LlamaConfig
+        cfg = LlamaConfig(hidden_size=hidden_size, intermediate_size=intermediate_size,
+                          num_hidden_layers=num_hidden_layers, num_attention_heads=num_attention_heads,
+                          num_key_value_heads=num_key_value_heads, head_dim=hidden_size // num_attention_heads,
+                          vocab_size=vocab_size, rope_theta=rope_theta, rms_norm_eps=rms_norm_eps)
+    else:
+        from transformers import Qwen2Config
+        cfg = Qwen2Config(hidden_size=hidden_size, intermediate_size=intermediate_size,
+                          num_hidden_layers=num_hidden_layers, num_attention_heads=num_attention_heads,
+                          num_key_value_heads=num_key_value_heads, vocab_size=vocab_size, rope_theta=rope_theta,
+                          rms_norm_eps=rms_norm_eps)
+    cfg._method = "sink"
+    cfg._sinks, cfg._cascades, cfg._window, cfg._cascade_func = sinks, cascades, window, cascade_func
+    cfg._head_reduction, cfg._cascade_stride = head_reduction, cascade_stride
+    cfg._homogeneous_heads, cfg._do_og_pos, cfg._batch_size = homogeneous_heads, do_og_pos, batch_size
+    return cfg
+
+
+def get_cache(model: CascadeForCausalLM, dtype: Optional[torch.dtype] = None, eager_fill: bool = True,
+              admission: str = "ema") -> CascadingKVCache:
+    """The cache for ``model`` from its config's cascade fields (cascade/models/test.py:21-39)."""
+    cfg = model.config
+    param = model.lm_head.weight
+    return CascadingKVCache(
+        cfg._window // cfg._cascades, num_sink_tokens=cfg._sinks, max_batch_size=cfg._batch_size,
+        heads=cfg.num_key_value_heads, dim=cfg.hidden_size // cfg.num_attention_heads, max_seq_len=cfg._window,
+        dtype=dtype or param.dtype, device=param.device, cascade_func=cfg._cascade_func,
+        head_reduction=cfg._head_reduction, layers=cfg.num_hidden_layers, eager_fill=eager_fill, verbose=False,
+        admission=admission)

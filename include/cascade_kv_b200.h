@@ -287,6 +287,26 @@ int ckv_profile_kernel(int32_t index, const char **kernel_name /* host */, doubl
  */
 int ckv_read_status(const void *workspace, int32_t *status /* host */);
 
+/*
+ * Self-test of the bounded waits: launches one thread that waits, with a short limit, for a barrier phase
+ * that nothing completes -- through the very wait routine of the decode kernels (which = 1) or of the
+ * prefill kernels (which = 2).  The wait must give up and the kernel end normally; afterwards
+ * ckv_read_status(workspace) gives 1 (decode) or 2 | line << 8 (prefill).  This is how the error path of
+ * the waits is exercised without making a real pipeline stall.  workspace: at least 4 bytes of device
+ * memory, its first word is overwritten.  (No counterpart in the reference.)
+ */
+int ckv_selftest_bounded_wait(int32_t which, void *workspace, void *cuda_stream);
+
+/*
+ * Debug build of the library only (compiled with -DCKV_BOUNDS: `python -m cascading_kv_cache_b200.build
+ * --bounds` writes libckv_b200_bounds.so): the update kernels check every slot index and counter before
+ * they use it; a violation is recorded and the access skipped, nothing traps.  Returns the first
+ * violation since the last call (4 | source line << 8) or 0, and clears the record; synchronises the
+ * device.  The ordinary build answers CKV_E_UNSUPPORTED.  (The reference has no counterpart; this stands
+ * in for a memory checker where none can be run.)
+ */
+int ckv_bounds_status(int32_t *status /* host */);
+
 #ifdef __cplusplus
 }
 #endif
