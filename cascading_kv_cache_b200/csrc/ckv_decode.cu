@@ -61,6 +61,7 @@ constexpr int kStreamSmem = kRingBytes + 1024 + 256 + kMergeBytes;
 constexpr int kPartialStride = 130;             // m, l, out[128] per head row
 constexpr unsigned kSpinLimit = 1u << 24;       // bounded mbarrier waits (each probe also sleeps)
 constexpr int kFinishThreads = 256;
+constexpr int kMaxHomogHeads = 64;              // query heads of one sequence reduced together (homogeneous_heads)
 constexpr int kMaxParts = 160;                  // partials of one lane: at most one per stream CTA (one CTA per SM)
 
 struct DecodeParams {
@@ -91,6 +92,8 @@ struct DecodeParams {
     int sink_rows_pad;
     int B, KVH, H, G, NS, W, C, S;
     int ema, update, head_reduction, eager_fill, dtype;
+    int homog;                                   // reduce the scores over all query heads of a sequence
+    float *head_stats;                           // homog: [B*H][4] = max, 1/sum, new-token probability of every head
     int stream_grid, finish_chunks;
     float rs, beta_pow;
     UpdateParams upd;                            // the one-token cache update of the finish kernel
@@ -765,9 +768,13 @@ __device__ __forceinline__ void ema_pass_vec(const DecodeParams &p, const Schedu
     }
 }
 
-template <typename T>
+// kStatsOnly: a first, small launch of the same kernel under homogeneous_heads -- every lane leaves (max, 1/sum,
+// new-token probability) of its heads in p.head_stats and returns, so that the real launch can reduce the scores
+// of a slot over ALL heads of the sequence (cascade_attention.py:240-242), not only over its own KV group.
+template <typename T, bool kStatsOnly>
 __global__ void __launch_bounds__(kFinishThreads, 3) decode_finish_kernel(DecodeParams p) {
     __shared__ float s_m[kMaxG], s_linv[kMaxG], s_snew[kMaxG], s_pnew[kMaxG];
+    __shared__ float s_hcg[kMaxHomogHeads], s_hpnew[kMaxHomogHeads];
     __shared__ int s_part[kMaxParts];
     __shared__ float s_w[kMaxG * kMaxParts];
     __shared__ long long s_stored[CKV_MAX_CASCADES], s_start[CKV_MAX_CASCADES], s_every[CKV_MAX_CASCADES];
@@ -863,6 +870,25 @@ __global__ void __launch_bounds__(kFinishThreads, 3) decode_finish_kernel(Decode
     }
     __syncthreads();
 
+    if (kStatsOnly) {
+        if (tid < p.G) {
+            float *hs = p.head_stats + ((long long)b * p.H + kvh * p.G + tid) * 4;
+            hs[0] = s_m[tid];
+            hs[1] = s_linv[tid];
+            hs[2] = s_pnew[tid];
+        }
+        return;
+    }
+    if (p.homog && p.update && p.ema) {
+        // exponent shift and new-token probability of every head of the sequence (left by the first launch)
+        for (int h = tid; h < p.H; h += kFinishThreads) {
+            const float *hs = p.head_stats + ((long long)b * p.H + h) * 4;
+            s_hcg[h] = -hs[0] * 1.4426950408889634f + __log2f(hs[1]);
+            s_hpnew[h] = hs[2];
+        }
+        __syncthreads();
+    }
+
     // 3. output rows, shared out among the lane's blocks
     {
         const int n_out = p.G * 128, per_out = (n_out + gridDim.x - 1) / gridDim.x;
@@ -886,7 +912,28 @@ __global__ void __launch_bounds__(kFinishThreads, 3) decode_finish_kernel(Decode
         const float w0 = p.ema_w_cache[0];
         const T *lg = reinterpret_cast<const T *>(p.logits) + ((long long)b * p.H + kvh * p.G) * p.S;
         T *scr = reinterpret_cast<T *>(p.score_cache) + (long long)lane * p.S;
-        if (p.S % 8 == 0 && p.head_reduction != CKV_REDUCE_MEDIAN && p.G <= 8) {
+        if (p.homog) {
+            // every KV head of the sequence computes the same reduction over all H heads and applies it to its own
+            // score row: H / G times the logit reads of the per-group rule, no exchange between blocks
+            const T *lgb = reinterpret_cast<const T *>(p.logits) + (long long)b * p.H * p.S;
+            const int per_block = (p.S + p.finish_chunks - 1) / p.finish_chunks;
+            const int s_end = min(p.S, (int)(blockIdx.x + 1) * per_block);
+            constexpr float kL2e = 1.4426950408889634f;
+            for (int slot = blockIdx.x * per_block + tid; slot < s_end; slot += kFinishThreads) {
+                float red = 0.f;
+                if (slot < sc.total) {
+                    float e[kMaxHomogHeads];
+#pragma unroll 4
+                    for (int h = 0; h < p.H; ++h) {
+                        const float pr = rnd<T>(ex2_approx(fmaf(Elem<T>::to_f(lgb[(long long)h * p.S + slot]), kL2e, s_hcg[h])));
+                        e[h] = rnd<T>(__fmul_rn(pr, w0));
+                    }
+                    red = rnd<T>(reduce_group(e, p.H, p.head_reduction));
+                }
+                const float decayed = rnd<T>(__fmul_rn(Elem<T>::to_f(scr[slot]), p.beta_pow));
+                scr[slot] = Elem<T>::from_f(__fadd_rn(decayed, red));
+            }
+        } else if (p.S % 8 == 0 && p.head_reduction != CKV_REDUCE_MEDIAN && p.G <= 8) {
             if (p.head_reduction == CKV_REDUCE_MAX) ema_pass_vec<T, true>(p, sc, lg, scr, s_m, s_linv, w0, tid);
             else ema_pass_vec<T, false>(p, sc, lg, scr, s_m, s_linv, w0, tid);
         } else {
@@ -999,10 +1046,12 @@ __global__ void __launch_bounds__(kFinishThreads, 3) decode_finish_kernel(Decode
     if (warp == 0) {
         unsigned int new_score = 0;
         if (p.ema) {
-            float e[kMaxG];
+            float e[kMaxHomogHeads];
             const float w1 = Elem<T>::to_f(reinterpret_cast<const T *>(p.ema_w_new)[0]);
-            for (int gh = 0; gh < p.G; ++gh) e[gh] = rnd<T>(__fmul_rn(rnd<T>(s_pnew[gh]), w1));
-            const T red = Elem<T>::from_f(rnd<T>(reduce_group(e, p.G, p.head_reduction)));
+            const int n_red = p.homog ? p.H : p.G;
+            const float *pn = p.homog ? s_hpnew : s_pnew;
+            for (int gh = 0; gh < n_red; ++gh) e[gh] = rnd<T>(__fmul_rn(rnd<T>(pn[gh]), w1));
+            const T red = Elem<T>::from_f(rnd<T>(reduce_group(e, n_red, p.head_reduction)));
             new_score = (unsigned int)*reinterpret_cast<const unsigned short *>(&red);
             if (lane_id == 0) reinterpret_cast<T *>(p.new_scores)[lane] = red;
         }
@@ -1074,7 +1123,7 @@ int make_rows_map(CUtensorMap *tm, const void *base, uint64_t rows, int dtype) {
 size_t up256(size_t x) { return (x + 255) & ~(size_t)255; }
 
 struct DecodeScratch {
-    size_t status, sync, image_tag, logits, partials, new_scores, rope_slots, image_bytes, total;
+    size_t status, sync, image_tag, head_stats, logits, partials, new_scores, rope_slots, image_bytes, total;
 };
 
 int sm_count() {
@@ -1096,6 +1145,7 @@ DecodeScratch decode_scratch(const Dims &d) {
     s.status = off; off += 256;
     s.sync = off; off += up256((1 + lanes) * 4);
     s.image_tag = off; off += 256;
+    s.head_stats = off; off += up256((size_t)d.B * d.H * 4 * sizeof(float));
     s.logits = off; off += up256((size_t)d.B * d.H * d.S * 2);
     s.partials = off; off += up256((size_t)(sm_count() + lanes) * d.G * kPartialStride * 4);
     s.new_scores = off; off += up256(lanes * 2);
@@ -1110,7 +1160,7 @@ DecodeScratch decode_scratch(const Dims &d) {
 
 bool decode_tuned_supported(const Dims &d, int n_tokens) {
     return n_tokens == 1 && (d.dtype == CKV_BF16 || d.dtype == CKV_F16) && d.D == 128 && d.G <= kMaxG &&
-           !d.homogeneous && d.S % 2 == 0 && d.NS >= 1;
+           (!d.homogeneous || d.H <= kMaxHomogHeads) && d.S % 2 == 0 && d.NS >= 1;
 }
 
 size_t decode_workspace_bytes(const Dims &d) { return decode_scratch(d).total; }
@@ -1181,6 +1231,8 @@ int launch_decode_tuned(const Dims &d, const ckv_layer_state *st, const void *q,
     p.rope_slots = ws + s.rope_slots;
     p.image_bytes = (long long)s.image_bytes;
     p.image_tag = (long long *)(ws + s.image_tag);
+    p.head_stats = (float *)(ws + s.head_stats);
+    p.homog = d.homogeneous ? 1 : 0;
     p.sink_rows_pad = sink_rows_padded(d);
     p.B = d.B; p.KVH = d.KVH; p.H = d.H; p.G = d.G; p.NS = d.NS; p.W = d.W; p.C = d.C; p.S = d.S;
     p.ema = ema; p.update = update; p.head_reduction = d.head_reduction; p.eager_fill = d.eager_fill;
@@ -1233,12 +1285,19 @@ int launch_decode_tuned(const Dims &d, const ckv_layer_state *st, const void *q,
     if (hook) hook->after(stream);
     CKV_CUDA_CHECK(cudaGetLastError());
     const dim3 grid(chunks, (unsigned)lanes);
+    const bool two_launches = p.homog && ema;
+    if (two_launches) {   // homogeneous heads: every lane first publishes its heads' statistics
+        const dim3 sgrid(1, (unsigned)lanes);
+        if (d.dtype == CKV_BF16) decode_finish_kernel<__nv_bfloat16, true><<<sgrid, kFinishThreads, 0, stream>>>(p);
+        else decode_finish_kernel<__half, true><<<sgrid, kFinishThreads, 0, stream>>>(p);
+        CKV_CUDA_CHECK(cudaGetLastError());
+    }
     if (hook) hook->before(stream, "decode_finish_kernel");
-    if (d.dtype == CKV_BF16) decode_finish_kernel<__nv_bfloat16><<<grid, kFinishThreads, 0, stream>>>(p);
-    else decode_finish_kernel<__half><<<grid, kFinishThreads, 0, stream>>>(p);
+    if (d.dtype == CKV_BF16) decode_finish_kernel<__nv_bfloat16, false><<<grid, kFinishThreads, 0, stream>>>(p);
+    else decode_finish_kernel<__half, false><<<grid, kFinishThreads, 0, stream>>>(p);
     if (hook) hook->after(stream);
     CKV_CUDA_CHECK(cudaGetLastError());
-    note_launches(3);
+    note_launches(two_launches ? 4 : 3);
     return CKV_OK;
 }
 

@@ -78,7 +78,7 @@ struct PrefillParams {
     int nSplit;
     void *new_scores;  // [B*KVH][K]
     int B, KVH, H, G, NS, S, C, K, Kpad, Rpad, nQT;
-    int ema, head_reduction;
+    int ema, head_reduction, homogeneous;
     float rs, beta_pow, beta;
 };
 
@@ -1351,6 +1351,8 @@ __global__ void __launch_bounds__(256) prefill_combine_single_kernel(PrefillPara
 }
 
 // ----------------------------------------------------------------------------------- score reduce
+constexpr int kMaxHomogeneousHeads = 64;     // heads of one sequence reduced together (homogeneous_heads)
+
 __device__ __forceinline__ float reduce_heads_pf(const float *v, int n, int how) {
     if (how == CKV_REDUCE_MAX) {
         float m = v[0];
@@ -1379,34 +1381,42 @@ template <typename T>
 __global__ void __launch_bounds__(256) prefill_scores_kernel(PrefillParams p) {
     const Extents e = make_extents(p);
     const int ncol = p.S + p.K;
-    const long long n = (long long)p.B * p.KVH * ncol;
+    // one thread per (lane, column); with homogeneous heads one per (sequence, column): the reduction then
+    // runs over ALL query heads of the sequence and its result goes to every KV head (cascade_attention.py:240-242)
+    const int lanes_in = p.homogeneous ? p.B : p.B * p.KVH;
+    const long long n = (long long)lanes_in * ncol;
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= n) return;
     const int col = (int)(idx % ncol);
-    const int lane = (int)(idx / ncol);
-    const int b = lane / p.KVH, kvh = lane % p.KVH;
-    float v[16];
+    const int li = (int)(idx / ncol);
+    const int b = p.homogeneous ? li : li / p.KVH, kvh = p.homogeneous ? 0 : li % p.KVH;
+    const int n_heads = p.homogeneous ? p.H : p.G, h0 = p.homogeneous ? 0 : kvh * p.G;
+    float v[kMaxHomogeneousHeads];
     float red = 0.f;
     const bool is_new = col >= p.S;
     if (is_new || col < e.total) {
         const int r = is_new ? e.n_cached + (col - p.S) : (int)e.sinks + col;      // row of the compacted key matrix
         const int qt0 = is_new ? (col - p.S) / kBM : 0;                            // first query tile that sees it
-        for (int gh = 0; gh < p.G; ++gh) {
-            const float *part = p.colpart + ((long long)(b * p.H + kvh * p.G + gh) * p.nQT) * 2 * p.Rpad + r;
+        for (int gh = 0; gh < n_heads; ++gh) {
+            const float *part = p.colpart + ((long long)(b * p.H + h0 + gh) * p.nQT) * 2 * p.Rpad + r;
             float s = 0.f;
             // same order of additions, eight loads in flight
 #pragma unroll 8
             for (int i = 2 * qt0; i < 2 * p.nQT; ++i) s += part[(long long)i * p.Rpad];
             v[gh] = rnd<T>(s);
         }
-        red = rnd<T>(reduce_heads_pf(v, p.G, p.head_reduction));
+        red = rnd<T>(reduce_heads_pf(v, n_heads, p.head_reduction));
     }
-    if (!is_new) {
-        T *sc = reinterpret_cast<T *>(p.cache_s) + (long long)lane * p.S + col;
-        const float decayed = rnd<T>(__fmul_rn(Elem<T>::to_f(*sc), p.beta_pow));
-        *sc = Elem<T>::from_f(__fadd_rn(decayed, red));
-    } else {
-        reinterpret_cast<T *>(p.new_scores)[(long long)lane * p.K + (col - p.S)] = Elem<T>::from_f(red);
+    const int kv0 = p.homogeneous ? 0 : kvh, kv1 = p.homogeneous ? p.KVH : kvh + 1;
+    for (int kv = kv0; kv < kv1; ++kv) {
+        const long long lane = (long long)b * p.KVH + kv;
+        if (!is_new) {
+            T *sc = reinterpret_cast<T *>(p.cache_s) + lane * p.S + col;
+            const float decayed = rnd<T>(__fmul_rn(Elem<T>::to_f(*sc), p.beta_pow));
+            *sc = Elem<T>::from_f(__fadd_rn(decayed, red));
+        } else {
+            reinterpret_cast<T *>(p.new_scores)[lane * p.K + (col - p.S)] = Elem<T>::from_f(red);
+        }
     }
 }
 
@@ -1523,7 +1533,7 @@ int launch_prefill_wait_selftest(int *status, cudaStream_t stream) {
 
 bool prefill_tuned_supported(const Dims &d, int n_tokens) {
     return n_tokens >= 2 && (d.dtype == CKV_BF16 || d.dtype == CKV_F16) && d.D == 128 && d.G <= 16 &&
-           !d.homogeneous && d.NS >= 1;
+           (!d.homogeneous || d.H <= kMaxHomogeneousHeads) && d.NS >= 1;
 }
 
 size_t prefill_workspace_bytes(const Dims &d, int n_tokens) { return prefill_scratch(d, n_tokens).total; }
@@ -1582,7 +1592,7 @@ int launch_prefill_tuned(const Dims &d, const ckv_layer_state *st, const void *q
     p.stats = (float2 *)(ws + s.stats); p.opart = (float *)(ws + s.opart);
     p.B = d.B; p.KVH = d.KVH; p.H = d.H; p.G = d.G; p.NS = d.NS; p.S = d.S; p.C = d.C;
     p.K = n_tokens; p.Kpad = s.Kpad; p.Rpad = s.Rpad; p.nQT = s.nQT;
-    p.ema = ema; p.head_reduction = d.head_reduction;
+    p.ema = ema; p.head_reduction = d.head_reduction; p.homogeneous = d.homogeneous;
     p.rs = (float)sqrt(1.0 / sqrt((double)d.D));
     p.beta_pow = (float)pow(d.beta, (double)n_tokens);
     p.beta = (float)d.beta;
@@ -1641,7 +1651,7 @@ int launch_prefill_tuned(const Dims &d, const ckv_layer_state *st, const void *q
     CKV_CUDA_CHECK(cudaGetLastError());
     int launches = ((ema || two_pass_always) ? 3 : 2) + (p.nSplit > 1 ? 1 : 0);
     if (ema) {
-        const long long n = (long long)d.B * d.KVH * (d.S + n_tokens);
+        const long long n = (long long)(d.homogeneous ? d.B : d.B * d.KVH) * (d.S + n_tokens);
         if (d.dtype == CKV_BF16) prefill_scores_kernel<__nv_bfloat16><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(p);
         else prefill_scores_kernel<__half><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(p);
         CKV_CUDA_CHECK(cudaGetLastError());

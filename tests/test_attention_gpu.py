@@ -101,6 +101,10 @@ STREAMS = [
     (1, 4, 4, 128, 4, 256, 4, 300, 6, 3, torch.float16, "ema", "mean", False, True, 0.999, 5e5),
     (1, 6, 2, 128, 8, 512, 2, 333, 5, 2, torch.bfloat16, "ema", "mean", False, False, 0.9999, 1e6),
     (1, 8, 2, 128, 4, 128, 8, 257, 6, 2, torch.bfloat16, "stride", "mean", False, True, 0.9999, 5e5),
+    # homogeneous heads on the tuned kernels: scores reduced over all query heads of a sequence
+    (2, 8, 2, 128, 4, 64, 4, 150, 5, 6, torch.bfloat16, "ema", "max", True, True, 0.999, 5e5),
+    (1, 12, 4, 128, 8, 128, 2, 200, 4, 5, torch.float16, "ema", "mean", True, False, 0.999, 1e6),
+    (1, 6, 2, 128, 4, 64, 4, 70, 6, 4, torch.bfloat16, "ema", "median", True, True, 0.999, 5e5),
 ]
 
 
@@ -273,13 +277,15 @@ DECODE = [
 ]
 
 
-@pytest.mark.parametrize("spec", DECODE, ids=lambda s: f"B{s[0]}H{s[1]}kv{s[2]}NS{s[3]}W{s[4]}C{s[5]}-{str(s[6])[6:]}-{s[7]}-{s[8]}")
+@pytest.mark.parametrize("spec", DECODE + [s + (True,) for s in DECODE if s[7] == "ema"],
+                         ids=lambda s: f"B{s[0]}H{s[1]}kv{s[2]}NS{s[3]}W{s[4]}C{s[5]}-{str(s[6])[6:]}-{s[7]}-{s[8]}" + ("-homog" if len(s) > 10 else ""))
 def test_decode_on_full_cache(spec):
     """Decode steps on a fully populated cache (the benchmark's regime): the streaming kernel's
     split of the key stream crosses lanes and CTAs hold several tiles."""
     from cascading_kv_cache_b200 import CascadingKVCache, cascade_attention
     from cascading_kv_cache_b200.synthetic import populate_steady_state
-    B, H, KVH, NS, W, C, dtype, rule, red, steps = spec
+    B, H, KVH, NS, W, C, dtype, rule, red, steps = spec[:10]
+    homog = len(spec) > 10      # scores reduced over all query heads of a sequence (two finish launches)
     D, S = 128, W * C
     ref = OracleCascadingKVCache(W, NS, B, KVH, D, S, dtype=dtype, head_reduction=red, layers=1, eager_fill=True)
     populate_steady_state(ref, 0, seed=5, beta=0.999)
@@ -295,8 +301,9 @@ def test_decode_on_full_cache(spec):
             want = cascade_attention_step(q, k, v, ref, 0, 5e5, red, False, do_update=False)
             ref.update(k, v, 0)
         else:
-            want = cascade_attention_step(q, k, v, ref, 0, 5e5, red, False)
-        got = cascade_attention(q.cuda(), k.cuda(), v.cuda(), cache, 0, rope_theta=5e5).float().cpu()
+            want = cascade_attention_step(q, k, v, ref, 0, 5e5, red, homog)
+        got = cascade_attention(q.cuda(), k.cuda(), v.cuda(), cache, 0, rope_theta=5e5,
+                                homogeneous_heads=homog).float().cpu()
         ok, err = close_enough(got, want.float(), True)
         assert ok, err
     assert cache.kernel_status() == 0
