@@ -18,10 +18,13 @@ replace.  Only tests/, ``__graft_entry__.smoke()`` and the CPU-baseline legs of
   (:250-340, the three-segment softmax, EMA scores and score-cache decay) and
   ``calc_scores`` (:231-248, head reduction).
 
-Parity status: pinned for the update (stride rule) against
-``CascadingKVCacheSlow`` and for attention against the reference's own
-``forward_cascade``/``cascade_attn_eager`` run on CPU; the vectors and the
-script that produced them are under tests/golden/.
+Parity status: pinned.  The update is checked against ``CascadingKVCacheSlow``
+(stride rule) and against state dumps of the reference's own ``CascadingKVCache``
+whose Triton kernel's source was executed on the CPU (score-driven rule, every
+dtype); attention against the reference's own ``forward_cascade`` /
+``cascade_attn_eager`` run on CPU over that cache (default positions and
+``do_og_pos``).  The vectors and the scripts that produced them are under
+tests/golden/.
 """
 from __future__ import annotations
 
