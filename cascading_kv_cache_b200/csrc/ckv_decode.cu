@@ -286,6 +286,7 @@ __device__ __forceinline__ uint4 *image_of(const DecodeParams &p, long long seen
 
 __global__ void __launch_bounds__(256) rope_slots_kernel(DecodeParams p) {
     const Schedule sc = make_schedule(p);
+    if (blockIdx.x == 0 && threadIdx.x == 0) *p.status = 0;     // first kernel of the step: clear the status word
     {
         // the image of this step may already be there (written by the previous step's finish kernel).
         // One thread per block looks: every thread of a large grid reading the same four words would
@@ -1263,7 +1264,6 @@ int launch_decode_tuned(const Dims &d, const ckv_layer_state *st, const void *q,
     u.KVH = d.KVH; u.K = 1; u.NS = d.NS; u.W = d.W; u.C = d.C; u.S = d.S;
     u.row_bytes = 256; u.esz = 2; u.dtype = d.dtype; u.eager_fill = d.eager_fill;
 
-    CKV_CUDA_CHECK(cudaMemsetAsync(p.status, 0, 4, stream));
     {
         const long long work = (long long)(p.sink_rows_pad + d.S) * 16;
         // Two blocks per SM: in steady state the kernel only compares the tag and returns, and a small grid returns
