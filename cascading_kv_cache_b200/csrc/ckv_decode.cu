@@ -25,11 +25,13 @@
 //   (max, sum, out) in shared memory into one partial per (CTA, lane); under the EMA rule the
 //   logits of every cached slot are also stored (the rounding point of the reference's einsum).
 //
-// Kernel 2, decode_finish_kernel: merges the partials with the new token's own logit, writes the
-//   output, turns logits into probabilities, reduces them over the GQA group, applies
-//   score_cache = beta*score_cache + ema (cascade_attention.py:315-330), then the last block of
-//   each lane inserts the new token (the cascade update state machine) and the last block of all
-//   advances the lane-invariant counters.  No host synchronisation anywhere.
+// Kernel 2, decode_finish_kernel: the blocks of a lane have roles.  Work blocks merge the partials with
+//   the new token's own logit, write the output, turn logits into probabilities, reduce them over
+//   the GQA group and apply score_cache = beta*score_cache + ema (cascade_attention.py:315-330);
+//   the last of them to finish inserts the new token (the cascade update state machine).  Under the
+//   stride rule the insert depends on nothing else and has a block of its own.  Image blocks rewrite
+//   the lane-invariant positions / masks and the next step's cos|sin image.  The last block of the
+//   whole grid advances the lane-invariant counters.  No host synchronisation anywhere.
 #include <cuda.h>
 
 #include "ckv_common.cuh"
@@ -94,7 +96,8 @@ struct DecodeParams {
     int ema, update, head_reduction, eager_fill, dtype;
     int homog;                                   // reduce the scores over all query heads of a sequence
     float *head_stats;                           // homog: [B*H][4] = max, 1/sum, new-token probability of every head
-    int stream_grid, finish_chunks;
+    int stream_grid;
+    int finish_chunks, finish_upd, finish_img;   // blocks of a lane in the finish kernel, by role
     float rs, beta_pow;
     UpdateParams upd;                            // the one-token cache update of the finish kernel
 };
@@ -793,6 +796,144 @@ __global__ void __launch_bounds__(kFinishThreads, 3) decode_finish_kernel(Decode
     const T *krow = reinterpret_cast<const T *>(p.knew) + b * p.ksb + kvh * p.ksh;
     const T *vrow = reinterpret_cast<const T *>(p.vnew) + b * p.ksb + kvh * p.ksh;
 
+    // Blocks of a lane by role (blockIdx.x): [0, finish_chunks) merge the partials, write the output rows and run
+    // the EMA pass; under the stride rule one further block inserts the token (nothing it touches depends on the
+    // others); the last finish_img blocks rewrite the lane-invariant positions / masks and the next step's cos|sin
+    // image.  Nothing on one role's path waits for another role: they meet only in the count that elects the
+    // block which publishes the advanced counters.
+    const int upd_base = p.finish_chunks, img_base = p.finish_chunks + p.finish_upd;
+    const bool work_block = (int)blockIdx.x < upd_base;
+
+    // 0. the counters after this token (every block may turn out to be the one that publishes them)
+    if (!kStatsOnly && p.update) {
+        if (tid < p.C) {
+            s_stored[tid] = s_new_stored[tid] = p.stored_tokens[tid];
+            s_start[tid] = s_new_start[tid] = p.start_indices[tid];
+            s_every[tid] = p.every_n[tid];
+        }
+        __syncthreads();
+        if (tid == 0) {
+            long long sinks = sc.sinks;
+            advance_counters(s_new_stored, s_new_start, sinks, sc.seen, s_every, 1, p.NS, p.W, p.C, p.S, p.eager_fill);
+            long long total = 0;
+            for (int i = 0; i < p.C; ++i) total += s_new_stored[i];
+            for (int i = 0; i < p.C; ++i)
+                if (!CKV_COUNTERS_OK(s_new_stored[i], s_new_start[i], p.W)) s_new_stored[i] = s_new_start[i] = 0;
+            s_new_sinks = sinks;
+            s_new_total = total;
+            const ImageTag t = make_image_tag(p, sc.seen + 1, sinks, s_new_stored, s_new_start);
+            s_tag[0] = t.seen; s_tag[1] = t.counters; s_tag[2] = t.table; s_tag[3] = t.geometry;
+            const volatile long long *tag = p.image_tag + 4 * ((sc.seen + 1) & 1);
+            s_image_there = tag[0] == t.seen && tag[1] == t.counters && tag[2] == t.table && tag[3] == t.geometry;
+        }
+        __syncthreads();
+    }
+    auto arrive_and_publish = [&]() {
+        // every block that changed state counts itself once its writes are fenced; the last one of the grid
+        // publishes the new counters
+        __threadfence();
+        __syncthreads();
+        if (warp != 0) return;
+        unsigned last = 0;
+        const unsigned expected = gridDim.y * (unsigned)(p.finish_img + p.finish_upd + (p.ema ? 1 : p.finish_chunks));
+        if (lane_id == 0) last = (atomicAdd(&p.sync[0], 1u) == expected - 1);
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (!last) return;
+        __threadfence();
+        // every lane has read the old counters and finished its insert: publish the new ones
+        for (int i = lane_id; i < p.C; i += 32) {
+            p.stored_tokens[i] = s_new_stored[i];
+            p.start_indices[i] = s_new_start[i];
+        }
+        if (lane_id == 0) {
+            if (s_new_sinks > sc.sinks) {
+                p.sink_pos[sc.sinks] = sc.sinks;
+                p.sink_mask[sc.sinks] = 0;
+            }
+            *p.stored_sinks = s_new_sinks;
+            *p.seen = sc.seen + 1;
+            // every image block has written its share of the next step's image (their fences precede the
+            // count that elected this thread): say what it is valid for
+            long long *tag = p.image_tag + 4 * ((sc.seen + 1) & 1);
+            tag[1] = s_tag[1]; tag[2] = s_tag[2]; tag[3] = s_tag[3];
+            __threadfence();
+            tag[0] = s_tag[0];
+        }
+    };
+
+    if (!kStatsOnly && p.update && (int)blockIdx.x >= img_base) {
+        // ---- image blocks: positions / masks from the advanced counters, every image block of the grid taking
+        //      an equal share of the slots (nothing in this kernel reads them)
+        {
+            const int n_blocks = gridDim.y * p.finish_img, me = lane * p.finish_img + ((int)blockIdx.x - img_base);
+            const int per_block = (p.S + n_blocks - 1) / n_blocks;
+            const int s_begin = me * per_block, s_end = min(p.S, s_begin + per_block);
+            const bool rewrite = sc.seen + 1 > p.NS;
+            for (int t = s_begin + tid; t < s_end; t += kFinishThreads) {
+                const int i = t / p.W, j = t % p.W;
+                const int stored_i = (int)s_new_stored[i];                  // counters are at most W
+                if (j < stored_i) p.mask[t] = 0;
+                const long long ub = s_new_total - (long long)i * p.W;
+                const int seg = stored_i < p.W ? stored_i : p.W;
+                if (rewrite && ub > 0 && seg > 0) p.pos[t] = (long long)((j + seg - (int)s_new_start[i]) % seg) + ub - seg;
+            }
+            // the cos|sin image of the NEXT step (positions after this token), unless an earlier call of this
+            // step -- another layer sharing the workspace -- has written it already.  256 slots at a time: a
+            // thread works out one slot's next position, then the block copies the 256 table rows with 16
+            // independent 16-byte loads per thread.
+            if (!s_image_there) {
+                const long long seen_next = sc.seen + 1;
+                const long long shift = seen_next > p.NS ? p.NS : 0;
+                const uint4 *rope = reinterpret_cast<const uint4 *>(p.rope);
+                uint4 *img = image_of(p, seen_next) + (long long)p.sink_rows_pad * 16;
+                for (int base = s_begin; base < s_end; base += kFinishThreads) {
+                    const int t = base + tid;
+                    long long pos = 0;
+                    if (t < s_end && t < s_new_total) {
+                        pos = p.pos[t];
+                        if (rewrite) {
+                            const int i = t / p.W, j = t % p.W;
+                            const int stored_i = (int)s_new_stored[i];
+                            const long long ub = s_new_total - (long long)i * p.W;
+                            const int seg = stored_i < p.W ? stored_i : p.W;
+                            if (seg > 0 && ub > 0) pos = (long long)((j + seg - (int)s_new_start[i]) % seg) + ub - seg;
+                        }
+                        pos += shift;
+                    }
+                    s_next_pos[tid] = (int)(pos < 0 ? 0 : (pos >= p.rope_rows ? p.rope_rows - 1 : pos));
+                    __syncthreads();
+                    const int n_here = min(kFinishThreads, s_end - base);
+#pragma unroll
+                    for (int r = 0; r < 16; ++r) {
+                        const int idx = r * kFinishThreads + tid, slot = idx >> 4, c = idx & 15;
+                        if (slot < n_here) img[(long long)(base + slot) * 16 + c] = rope[(long long)s_next_pos[slot] * 16 + c];
+                    }
+                    __syncthreads();
+                }
+                if (me == 0) {      // the sink rows: sink i sits at position i
+                    uint4 *simg = image_of(p, seen_next);
+                    for (int idx = tid; idx < p.sink_rows_pad * 16; idx += kFinishThreads) {
+                        const int row = idx >> 4, c = idx & 15;
+                        const long long pos = row < s_new_sinks ? row : 0;
+                        simg[idx] = rope[pos * 16 + c];
+                    }
+                }
+            }
+        }
+        arrive_and_publish();
+        return;
+    }
+    if (!kStatsOnly && p.update && p.finish_upd && (int)blockIdx.x == upd_base) {
+        // ---- stride rule: the token goes in at once
+        if (warp == 0) {
+            if (p.C <= kOneTokenMaxCascades) update_lane_one_token(p.upd, lane, s_stored, s_start, s_every, sc.sinks, sc.seen, 0u);
+            else update_lane_walk(p.upd, lane, s_stored, s_start, s_every);
+        }
+        arrive_and_publish();
+        return;
+    }
+    if (!work_block) return;
+
     // 1. which of the stream kernel's partials belong to this lane: CTAs whose tile range meets the lane's.
     //    Partial i comes from CTA cta_lo + i; CTAs with an empty tile range wrote nothing.  Worked out once
     //    per block (the range arithmetic is 64-bit divisions) and kept in shared memory.
@@ -892,7 +1033,7 @@ __global__ void __launch_bounds__(kFinishThreads, 3) decode_finish_kernel(Decode
 
     // 3. output rows, shared out among the lane's blocks
     {
-        const int n_out = p.G * 128, per_out = (n_out + gridDim.x - 1) / gridDim.x;
+        const int n_out = p.G * 128, per_out = (n_out + p.finish_chunks - 1) / p.finish_chunks;
         const int o_end = min(n_out, (int)(blockIdx.x + 1) * per_out);
         for (int idx = blockIdx.x * per_out + tid; idx < o_end; idx += kFinishThreads) {
             const int gh = idx >> 7, d = idx & 127;
@@ -956,136 +1097,32 @@ __global__ void __launch_bounds__(kFinishThreads, 3) decode_finish_kernel(Decode
         }
     }
 
-    // 5. lane-invariant state after this token: positions / masks are rewritten from the advanced
-    //    counters, every block of the grid taking an equal share of the slots (nothing in this kernel
-    //    reads them)
-    if (tid < p.C) {
-        s_stored[tid] = s_new_stored[tid] = p.stored_tokens[tid];
-        s_start[tid] = s_new_start[tid] = p.start_indices[tid];
-        s_every[tid] = p.every_n[tid];
-    }
-    __syncthreads();
-    if (tid == 0) {
-        long long sinks = sc.sinks;
-        advance_counters(s_new_stored, s_new_start, sinks, sc.seen, s_every, 1, p.NS, p.W, p.C, p.S, p.eager_fill);
-        long long total = 0;
-        for (int i = 0; i < p.C; ++i) total += s_new_stored[i];
-        for (int i = 0; i < p.C; ++i)
-            if (!CKV_COUNTERS_OK(s_new_stored[i], s_new_start[i], p.W)) s_new_stored[i] = s_new_start[i] = 0;
-        s_new_sinks = sinks;
-        s_new_total = total;
-        const ImageTag t = make_image_tag(p, sc.seen + 1, sinks, s_new_stored, s_new_start);
-        s_tag[0] = t.seen; s_tag[1] = t.counters; s_tag[2] = t.table; s_tag[3] = t.geometry;
-        const volatile long long *tag = p.image_tag + 4 * ((sc.seen + 1) & 1);
-        s_image_there = tag[0] == t.seen && tag[1] == t.counters && tag[2] == t.table && tag[3] == t.geometry;
-    }
-    __syncthreads();
-    {
-        const int n_blocks = gridDim.x * gridDim.y, me = blockIdx.y * gridDim.x + blockIdx.x;
-        const int per_block = (p.S + n_blocks - 1) / n_blocks;
-        const int s_begin = me * per_block, s_end = min(p.S, s_begin + per_block);
-        const bool rewrite = sc.seen + 1 > p.NS;
-        for (int t = s_begin + tid; t < s_end; t += kFinishThreads) {
-            const int i = t / p.W, j = t % p.W;
-            const int stored_i = (int)s_new_stored[i];                  // counters are at most W
-            if (j < stored_i) p.mask[t] = 0;
-            const long long ub = s_new_total - (long long)i * p.W;
-            const int seg = stored_i < p.W ? stored_i : p.W;
-            if (rewrite && ub > 0 && seg > 0) p.pos[t] = (long long)((j + seg - (int)s_new_start[i]) % seg) + ub - seg;
-        }
-        // the cos|sin image of the NEXT step (positions after this token), unless an earlier call of this
-        // step -- another layer sharing the workspace -- has written it already.  256 slots at a time: a
-        // thread works out one slot's next position, then the block copies the 256 table rows with 16
-        // independent 16-byte loads per thread.
-        if (!s_image_there) {
-            const long long seen_next = sc.seen + 1;
-            const long long shift = seen_next > p.NS ? p.NS : 0;
-            const uint4 *rope = reinterpret_cast<const uint4 *>(p.rope);
-            uint4 *img = image_of(p, seen_next) + (long long)p.sink_rows_pad * 16;
-            for (int base = s_begin; base < s_end; base += kFinishThreads) {
-                const int t = base + tid;
-                long long pos = 0;
-                if (t < s_end && t < s_new_total) {
-                    pos = p.pos[t];
-                    if (rewrite) {
-                        const int i = t / p.W, j = t % p.W;
-                        const int stored_i = (int)s_new_stored[i];
-                        const long long ub = s_new_total - (long long)i * p.W;
-                        const int seg = stored_i < p.W ? stored_i : p.W;
-                        if (seg > 0 && ub > 0) pos = (long long)((j + seg - (int)s_new_start[i]) % seg) + ub - seg;
-                    }
-                    pos += shift;
-                }
-                s_next_pos[tid] = (int)(pos < 0 ? 0 : (pos >= p.rope_rows ? p.rope_rows - 1 : pos));
-                __syncthreads();
-                const int n_here = min(kFinishThreads, s_end - base);
-#pragma unroll
-                for (int r = 0; r < 16; ++r) {
-                    const int idx = r * kFinishThreads + tid, slot = idx >> 4, c = idx & 15;
-                    if (slot < n_here) img[(long long)(base + slot) * 16 + c] = rope[(long long)s_next_pos[slot] * 16 + c];
-                }
-                __syncthreads();
-            }
-            if (me == 0) {      // the sink rows: sink i sits at position i
-                uint4 *simg = image_of(p, seen_next);
-                for (int idx = tid; idx < p.sink_rows_pad * 16; idx += kFinishThreads) {
-                    const int row = idx >> 4, c = idx & 15;
-                    const long long pos = row < s_new_sinks ? row : 0;
-                    simg[idx] = rope[pos * 16 + c];
-                }
-            }
-        }
-    }
-
-    // 6. the last block of the lane inserts the token; the last lane advances the counters
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) s_is_last = (atomicAdd(&p.sync[1 + lane], 1u) == (unsigned)(gridDim.x - 1));
-    __syncthreads();
-    if (!s_is_last) return;
-    __threadfence();
-    if (warp == 0) {
-        unsigned int new_score = 0;
-        if (p.ema) {
-            float e[kMaxHomogHeads];
-            const float w1 = Elem<T>::to_f(reinterpret_cast<const T *>(p.ema_w_new)[0]);
-            const int n_red = p.homog ? p.H : p.G;
-            const float *pn = p.homog ? s_hpnew : s_pnew;
-            for (int gh = 0; gh < n_red; ++gh) e[gh] = rnd<T>(__fmul_rn(rnd<T>(pn[gh]), w1));
-            const T red = Elem<T>::from_f(rnd<T>(reduce_group(e, n_red, p.head_reduction)));
-            new_score = (unsigned int)*reinterpret_cast<const unsigned short *>(&red);
-            if (lane_id == 0) reinterpret_cast<T *>(p.new_scores)[lane] = red;
-        }
-        __syncwarp();
-        if (p.C <= kOneTokenMaxCascades) update_lane_one_token(p.upd, lane, s_stored, s_start, s_every, sc.sinks, sc.seen, new_score);
-        else update_lane_walk(p.upd, lane, s_stored, s_start, s_every);
+    if (p.ema) {
+        // the last work block of the lane inserts the token: the scores of every slot must be final
         __threadfence();
-        __syncwarp();
-        unsigned last = 0;
-        if (lane_id == 0) last = (atomicAdd(&p.sync[0], 1u) == (unsigned)(gridDim.y - 1));
-        last = __shfl_sync(0xffffffffu, last, 0);
-        if (last) {
-            // every lane has read the old counters and finished its insert: publish the new ones
-            for (int i = lane_id; i < p.C; i += 32) {
-                p.stored_tokens[i] = s_new_stored[i];
-                p.start_indices[i] = s_new_start[i];
+        __syncthreads();
+        if (tid == 0) s_is_last = (atomicAdd(&p.sync[1 + lane], 1u) == (unsigned)(p.finish_chunks - 1));
+        __syncthreads();
+        if (!s_is_last) return;
+        __threadfence();
+        if (warp == 0) {
+            unsigned int new_score = 0;
+            {
+                float e[kMaxHomogHeads];
+                const float w1 = Elem<T>::to_f(reinterpret_cast<const T *>(p.ema_w_new)[0]);
+                const int n_red = p.homog ? p.H : p.G;
+                const float *pn = p.homog ? s_hpnew : s_pnew;
+                for (int gh = 0; gh < n_red; ++gh) e[gh] = rnd<T>(__fmul_rn(rnd<T>(pn[gh]), w1));
+                const T red = Elem<T>::from_f(rnd<T>(reduce_group(e, n_red, p.head_reduction)));
+                new_score = (unsigned int)*reinterpret_cast<const unsigned short *>(&red);
+                if (lane_id == 0) reinterpret_cast<T *>(p.new_scores)[lane] = red;
             }
-            if (lane_id == 0) {
-                if (s_new_sinks > sc.sinks) {
-                    p.sink_pos[sc.sinks] = sc.sinks;
-                    p.sink_mask[sc.sinks] = 0;
-                }
-                *p.stored_sinks = s_new_sinks;
-                *p.seen = sc.seen + 1;
-                // every block has written its share of the next step's image (their fences precede the
-                // counters that elected this thread): say what it is valid for
-                long long *tag = p.image_tag + 4 * ((sc.seen + 1) & 1);
-                tag[1] = s_tag[1]; tag[2] = s_tag[2]; tag[3] = s_tag[3];
-                __threadfence();
-                tag[0] = s_tag[0];
-            }
+            __syncwarp();
+            if (p.C <= kOneTokenMaxCascades) update_lane_one_token(p.upd, lane, s_stored, s_start, s_every, sc.sinks, sc.seen, new_score);
+            else update_lane_walk(p.upd, lane, s_stored, s_start, s_every);
         }
     }
+    arrive_and_publish();
 }
 
 // ------------------------------------------------------------------------------------ host side
@@ -1239,14 +1276,22 @@ int launch_decode_tuned(const Dims &d, const ckv_layer_state *st, const void *q,
     p.ema = ema; p.update = update; p.head_reduction = d.head_reduction; p.eager_fill = d.eager_fill;
     p.dtype = d.dtype;
     p.stream_grid = sm_count() < kMaxParts ? sm_count() : kMaxParts;
-    int chunks = 1;
+    // Blocks per lane in the finish kernel: `chunks` work blocks (merge, output, EMA pass; one is enough without
+    // the EMA pass), one block that inserts the token under the stride rule, `img` blocks for the lane-invariant
+    // state -- about one image block per SM over the whole grid, the work blocks filling the rest of one wave of
+    // three blocks per SM.
+    int chunks = 1, upd = 0, img = 0;
     if (update) {
-        // one wave: the kernel is built for three blocks per SM.  Also without the EMA pass the blocks share
-        // the rewrite of the positions and of the next step's cos|sin image.
-        chunks = (int)((3 * (uint64_t)sm_count()) / lanes);
-        chunks = chunks < 1 ? 1 : (chunks > 64 ? 64 : chunks);
+        img = (int)((uint64_t)sm_count() / lanes);
+        img = img < 1 ? 1 : (img > 32 ? 32 : img);
+        if (ema) {
+            chunks = (int)((3 * (uint64_t)sm_count()) / lanes) - img;
+            chunks = chunks < 1 ? 1 : (chunks > 64 ? 64 : chunks);
+        } else {
+            upd = 1;
+        }
     }
-    p.finish_chunks = chunks;
+    p.finish_chunks = chunks; p.finish_upd = upd; p.finish_img = img;
     p.rs = (float)sqrt(1.0 / sqrt((double)d.D));
     p.beta_pow = (float)d.beta;
     UpdateParams &u = p.upd;
@@ -1286,7 +1331,7 @@ int launch_decode_tuned(const Dims &d, const ckv_layer_state *st, const void *q,
     }
     if (hook) hook->after(stream);
     CKV_CUDA_CHECK(cudaGetLastError());
-    const dim3 grid(chunks, (unsigned)lanes);
+    const dim3 grid(chunks + upd + img, (unsigned)lanes);
     const bool two_launches = p.homog && ema;
     if (two_launches) {   // homogeneous heads: every lane first publishes its heads' statistics
         const dim3 sgrid(1, (unsigned)lanes);
