@@ -804,8 +804,9 @@ __global__ void __launch_bounds__(kFinishThreads, 3) decode_finish_kernel(Decode
     const int upd_base = p.finish_chunks, img_base = p.finish_chunks + p.finish_upd;
     const bool work_block = (int)blockIdx.x < upd_base;
 
-    // 0. the counters after this token (every block may turn out to be the one that publishes them)
-    if (!kStatsOnly && p.update) {
+    // the counters after this token: needed by whoever inserts the token (the old ones) and by whoever turns out
+    // to publish (the new ones); the work blocks fetch them after their EMA pass, off their critical path
+    auto load_counters = [&]() {
         if (tid < p.C) {
             s_stored[tid] = s_new_stored[tid] = p.stored_tokens[tid];
             s_start[tid] = s_new_start[tid] = p.start_indices[tid];
@@ -827,7 +828,7 @@ __global__ void __launch_bounds__(kFinishThreads, 3) decode_finish_kernel(Decode
             s_image_there = tag[0] == t.seen && tag[1] == t.counters && tag[2] == t.table && tag[3] == t.geometry;
         }
         __syncthreads();
-    }
+    };
     auto arrive_and_publish = [&]() {
         // every block that changed state counts itself once its writes are fenced; the last one of the grid
         // publishes the new counters
@@ -861,6 +862,7 @@ __global__ void __launch_bounds__(kFinishThreads, 3) decode_finish_kernel(Decode
         }
     };
 
+    if (!kStatsOnly && p.update && !work_block) load_counters();
     if (!kStatsOnly && p.update && (int)blockIdx.x >= img_base) {
         // ---- image blocks: positions / masks from the advanced counters, every image block of the grid taking
         //      an equal share of the slots (nothing in this kernel reads them)
@@ -1097,6 +1099,7 @@ __global__ void __launch_bounds__(kFinishThreads, 3) decode_finish_kernel(Decode
         }
     }
 
+    load_counters();
     if (p.ema) {
         // the last work block of the lane inserts the token: the scores of every slot must be final
         __threadfence();
