@@ -18,7 +18,8 @@ Reported metric: achieved HBM GB/s = algorithmic bytes of the whole job per step
 cache read+written once, q/out/new k,v once) / step time (max over ranks); ``ms_per_step`` carries the latency.
 The timed loop replays CUDA graphs of several consecutive steps (the kernels take every counter from device
 memory, so a step needs nothing from the host).  ``e2e`` is the same metric through the Python call a user
-makes, with the step's q/k/v copied from pinned host memory and the output copied back inside the timed region.
+makes, one synchronous host round trip per step: the step's q|k|v copied from pinned host memory, the call, the
+output copied back and waited for, all inside the timed region (a one-step graph; the eager figure beside it).
 
 Further keys of the same JSON line: ``sustained`` (1000 steps, as the configuration is written), ``c4`` (the
 Qwen2-7B decode configuration, batch 32 split over the ranks), ``prefill`` / ``prefill_stride_rule`` (a
