@@ -113,5 +113,14 @@ def check(rc: int, what: str):
         raise RuntimeError(f"{what} failed (code {rc}): {msg}")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def current_stream_ptr(device) -> int:
+    """The current CUDA stream of ``device`` as an integer handle (no Stream object is built when torch
+    exposes the raw accessor)."""
+    if _raw_stream is not None:
+        index = getattr(device, "index", device)
+        if isinstance(index, int):
+            return _raw_stream(index)
     return torch.cuda.current_stream(device).cuda_stream

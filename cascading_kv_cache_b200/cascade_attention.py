@@ -35,12 +35,16 @@ from .cascading_cache import CascadingKVCache
 from .flash_attention import attention, dense_attention
 
 
-def _rows(t: torch.Tensor, dtype, device) -> torch.Tensor:
+def _rows(t: torch.Tensor, dtype, device):
+    """The tensor as the ABI wants it (last dimension contiguous, rows 16-byte aligned) and its strides."""
     if t.dtype != dtype or t.device != device:
         t = t.to(device=device, dtype=dtype)
-    esz = t.element_size()
-    ok = t.stride(3) == 1 and t.data_ptr() % 16 == 0 and all((t.stride(i) * esz) % 16 == 0 for i in range(3))
-    return t if ok else t.contiguous()
+    st = t.stride()
+    # every outer stride a multiple of 16 bytes <=> their bitwise OR is (element sizes are powers of two)
+    if st[3] == 1 and not (((st[0] | st[1] | st[2]) * t.element_size()) & 15) and not (t.data_ptr() & 15):
+        return t, st
+    t = t.contiguous()
+    return t, t.stride()
 
 
 def cascade_attention(
@@ -71,13 +75,15 @@ def cascade_attention(
         raise ValueError(f"shape mismatch: q {tuple(query_states.shape)} k {tuple(key_states.shape)} "
                          f"v {tuple(value_states.shape)} cache ({cache.max_batch_size}, {cache.heads}, K, {cache.dim})")
     dev, dt = cache.device, cache.dtype
-    q = _rows(query_states, dt, dev)
-    k = _rows(key_states, dt, dev)
-    v = _rows(value_states, dt, dev)
-    if k.stride() != v.stride():
+    q, qs = _rows(query_states, dt, dev)
+    k, ks = _rows(key_states, dt, dev)
+    v, vs = _rows(value_states, dt, dev)
+    if ks != vs:
         k, v = k.contiguous(), v.contiguous()
+        ks = k.stride()
     if out is None:
         out = torch.empty(B, H, K, D, device=dev, dtype=dt)
+    os_ = out.stride()
     lib = cache._lib
     cfg = cache.ckv_config(layer_idx, q_heads=H, homogeneous_heads=homogeneous_heads, head_reduction=head_reduction)
     st = cache.ckv_state(layer_idx)
@@ -95,10 +101,10 @@ def cascade_attention(
     with cache.device_guard():
         rc = lib.ckv_attention(
             cfg.ref, st.ref,
-            q.data_ptr(), q.stride(0), q.stride(1), q.stride(2),
-            k.data_ptr(), v.data_ptr(), k.stride(0), k.stride(1), k.stride(2),
+            q.data_ptr(), qs[0], qs[1], qs[2],
+            k.data_ptr(), v.data_ptr(), ks[0], ks[1], ks[2],
             K, rope.data_ptr(), rope.size(0), w_cache_ptr, w_new_ptr,
-            out.data_ptr(), out.stride(0), out.stride(1), out.stride(2),
+            out.data_ptr(), os_[0], os_[1], os_[2],
             ws_ptr, nbytes, flags, _lib.current_stream_ptr(dev))
     _lib.check(rc, "ckv_attention")
     if update:

@@ -1161,6 +1161,34 @@ int make_rows_map(CUtensorMap *tm, const void *base, uint64_t rows, int dtype) {
     return CKV_OK;
 }
 
+// The six maps of a decode call describe the same tensors step after step: keep the last few encodings per
+// host thread (a map depends only on base address, row count and element type) and copy instead of encoding.
+int cached_rows_map(CUtensorMap *tm, const void *base, uint64_t rows, int dtype) {
+    struct Entry {
+        const void *base;
+        uint64_t rows;
+        int dtype;
+        CUtensorMap map;
+    };
+    constexpr int kEntries = 32;
+    static thread_local Entry entries[kEntries];
+    static thread_local int n_entries = 0, next = 0;
+    for (int i = 0; i < n_entries; ++i) {
+        const Entry &e = entries[i];
+        if (e.base == base && e.rows == rows && e.dtype == dtype) {
+            *tm = e.map;
+            return CKV_OK;
+        }
+    }
+    const int rc = make_rows_map(tm, base, rows, dtype);
+    if (rc != CKV_OK) return rc;
+    Entry &e = entries[next];
+    e.base = base; e.rows = rows; e.dtype = dtype; e.map = *tm;
+    next = (next + 1) % kEntries;
+    if (n_entries < kEntries) ++n_entries;
+    return CKV_OK;
+}
+
 size_t up256(size_t x) { return (x + 255) & ~(size_t)255; }
 
 struct DecodeScratch {
@@ -1241,13 +1269,13 @@ int launch_decode_tuned(const Dims &d, const ckv_layer_state *st, const void *q,
     const uint64_t lanes = (uint64_t)d.B * d.KVH;
     CUtensorMap tmK, tmV, tmSK, tmSV, tmR0, tmR1;
     int rc;
-    if ((rc = make_rows_map(&tmK, st->key_cache, lanes * d.S, d.dtype)) != CKV_OK) return rc;
-    if ((rc = make_rows_map(&tmV, st->value_cache, lanes * d.S, d.dtype)) != CKV_OK) return rc;
-    if ((rc = make_rows_map(&tmSK, st->sink_keys, lanes * d.NS, d.dtype)) != CKV_OK) return rc;
-    if ((rc = make_rows_map(&tmSV, st->sink_values, lanes * d.NS, d.dtype)) != CKV_OK) return rc;
-    if ((rc = make_rows_map(&tmR0, (uint8_t *)workspace + s.rope_slots, (uint64_t)sink_rows_padded(d) + d.S, d.dtype)) != CKV_OK)
+    if ((rc = cached_rows_map(&tmK, st->key_cache, lanes * d.S, d.dtype)) != CKV_OK) return rc;
+    if ((rc = cached_rows_map(&tmV, st->value_cache, lanes * d.S, d.dtype)) != CKV_OK) return rc;
+    if ((rc = cached_rows_map(&tmSK, st->sink_keys, lanes * d.NS, d.dtype)) != CKV_OK) return rc;
+    if ((rc = cached_rows_map(&tmSV, st->sink_values, lanes * d.NS, d.dtype)) != CKV_OK) return rc;
+    if ((rc = cached_rows_map(&tmR0, (uint8_t *)workspace + s.rope_slots, (uint64_t)sink_rows_padded(d) + d.S, d.dtype)) != CKV_OK)
         return rc;
-    if ((rc = make_rows_map(&tmR1, (uint8_t *)workspace + s.rope_slots + s.image_bytes,
+    if ((rc = cached_rows_map(&tmR1, (uint8_t *)workspace + s.rope_slots + s.image_bytes,
                             (uint64_t)sink_rows_padded(d) + d.S, d.dtype)) != CKV_OK)
         return rc;
 
