@@ -26,7 +26,8 @@ EXPORTS = ("ckv_abi_version", "ckv_last_error", "ckv_cascade_update", "ckv_updat
            "ckv_attention_workspace_bytes", "ckv_attention_workspace_bytes_for",
            "ckv_attention", "ckv_last_launch_count", "ckv_profile_enable", "ckv_profile_read", "ckv_profile_kernel", "ckv_read_status",
            "ckv_static_scratch_bytes", "ckv_attention_static", "ckv_static_status", "ckv_advance_counters_host",
-           "ckv_dense_attention_workspace_bytes", "ckv_dense_attention", "ckv_bounds_status", "ckv_selftest_bounded_wait")
+           "ckv_dense_attention_workspace_bytes", "ckv_dense_attention", "ckv_bounds_status", "ckv_selftest_bounded_wait",
+           "ckv_add_rmsnorm", "ckv_silu_mul")
 
 
 class CkvConfig(ctypes.Structure):
@@ -80,6 +81,10 @@ def load():
                                          vp, i64, i64, i64, i32, vp]
     lib.ckv_dense_attention_workspace_bytes.restype = sz
     lib.ckv_dense_attention_workspace_bytes.argtypes = [i32, i32, i32]
+    lib.ckv_add_rmsnorm.restype = ctypes.c_int
+    lib.ckv_add_rmsnorm.argtypes = [vp, vp, vp, vp, vp, i64, i32, ctypes.c_double, i32, vp]
+    lib.ckv_silu_mul.restype = ctypes.c_int
+    lib.ckv_silu_mul.argtypes = [vp, vp, vp, i64, i32, i64, i64, i32, vp]
     lib.ckv_dense_attention.restype = ctypes.c_int
     lib.ckv_dense_attention.argtypes = [vp, i64, i64, i64, vp, i64, i64, i64, vp, i64, i64, i64, vp,
                                         i32, i32, i32, i32, i32, i32, i32, ctypes.c_double, ctypes.c_double, i32,

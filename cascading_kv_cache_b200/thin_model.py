@@ -6,8 +6,10 @@ cascade/models/qwen2/modeling_qwen2.py likewise), which cannot be constructed un
 transformers.  This module is the same computation with nothing else around it: token embedding,
 ``L x [RMSNorm -> cascade attention -> residual -> RMSNorm -> SwiGLU MLP -> residual]``, final RMSNorm,
 ``lm_head``.  The attention is ``LlamaCascadeAttention`` / ``Qwen2CascadeAttention`` (hand-written kernels
-behind the C ABI); the dense layers are plain ``torch.nn.Linear`` (library GEMMs), RMSNorm follows
-modeling_llama.py:113-127 (fp32 variance, weight applied after the cast back).
+behind the C ABI); the dense layers are plain ``torch.nn.Linear`` (library GEMMs); RMSNorm follows
+modeling_llama.py:113-127 (fp32 variance, weight applied after the cast back) and is fused with the residual
+add before it, the SwiGLU gate is one kernel too (``ckv_add_rmsnorm`` / ``ckv_silu_mul`` on 16-bit CUDA
+tensors, the same torch operations as the reference elsewhere).
 
 Configuration: a Hugging Face ``LlamaConfig`` / ``Qwen2Config`` carrying the reference's private fields
 (cascade/main/llama_eval.py:143-152): ``_sinks, _cascades, _window, _cascade_func, _head_reduction,
@@ -22,8 +24,51 @@ from typing import Optional
 import torch
 from torch import nn
 
+from . import _lib
 from .cascade_attention import LlamaCascadeAttention, Qwen2CascadeAttention, sample_monkeypatch
 from .cascading_cache import CascadingKVCache
+
+
+def _fusable(x: torch.Tensor) -> bool:
+    """The element-wise kernels of the library take contiguous 16-bit CUDA rows of a multiple of 8 elements."""
+    return x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and x.size(-1) % 8 == 0 and x.is_contiguous()
+
+
+def add_rmsnorm(x: torch.Tensor, residual: Optional[torch.Tensor], weight: torch.Tensor, eps: float):
+    """``s = x + residual`` (``s = x`` without a residual) and ``weight * rmsnorm(s)``: the residual add of a
+    decoder layer and the norm that follows it (modeling_llama.py:113-127, :745-770), one kernel on 16-bit CUDA
+    tensors (``ckv_add_rmsnorm``), the reference's own sequence of torch operations otherwise.
+    Returns ``(normed, s)``."""
+    if _fusable(x) and (residual is None or (_fusable(residual) and residual.shape == x.shape)) \
+            and weight.dtype == x.dtype and weight.is_contiguous():
+        lib = _lib.load()
+        normed = torch.empty_like(x)
+        s = x if residual is None else torch.empty_like(x)
+        hidden = x.size(-1)
+        with torch.cuda.device(x.device):
+            rc = lib.ckv_add_rmsnorm(x.data_ptr(), None if residual is None else residual.data_ptr(), weight.data_ptr(),
+                                     normed.data_ptr(), None if residual is None else s.data_ptr(), x.numel() // hidden,
+                                     hidden, float(eps), _lib.DTYPE_CODE[x.dtype], _lib.current_stream_ptr(x.device))
+        _lib.check(rc, "ckv_add_rmsnorm")
+        return normed, s
+    s = x if residual is None else residual + x
+    h = s.to(torch.float32)
+    h = h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + eps)
+    return weight * h.to(s.dtype), s
+
+
+def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """``silu(gate) * up`` (modeling_llama.py:282-313), one kernel on 16-bit CUDA tensors (``ckv_silu_mul``)."""
+    if _fusable(gate) and _fusable(up) and gate.shape == up.shape and gate.dtype == up.dtype:
+        lib = _lib.load()
+        out = torch.empty_like(gate)
+        cols = gate.size(-1)
+        with torch.cuda.device(gate.device):
+            rc = lib.ckv_silu_mul(gate.data_ptr(), up.data_ptr(), out.data_ptr(), gate.numel() // cols, cols, cols, cols,
+                                  _lib.DTYPE_CODE[gate.dtype], _lib.current_stream_ptr(gate.device))
+        _lib.check(rc, "ckv_silu_mul")
+        return out
+    return nn.functional.silu(gate) * up
 
 
 class RMSNorm(nn.Module):
@@ -34,12 +79,11 @@ class RMSNorm(nn.Module):
         self.weight = nn.Parameter(torch.ones(hidden_size))
         self.variance_epsilon = eps
 
-    def forward(self, hidden_states):
-        input_dtype = hidden_states.dtype
-        hidden_states = hidden_states.to(torch.float32)
-        variance = hidden_states.pow(2).mean(-1, keepdim=True)
-        hidden_states = hidden_states * torch.rsqrt(variance + self.variance_epsilon)
-        return self.weight * hidden_states.to(input_dtype)
+    def forward(self, hidden_states, residual: Optional[torch.Tensor] = None):
+        """Without ``residual``: the norm of ``hidden_states``.  With it: ``(norm(hidden_states + residual),
+        hidden_states + residual)`` -- the add that precedes every norm of the stack but the first."""
+        normed, s = add_rmsnorm(hidden_states, residual, self.weight, self.variance_epsilon)
+        return normed if residual is None else (normed, s)
 
 
 class SwiGLU(nn.Module):
@@ -52,11 +96,13 @@ class SwiGLU(nn.Module):
         self.down_proj = nn.Linear(intermediate_size, hidden_size, bias=False)
 
     def forward(self, x):
-        return self.down_proj(nn.functional.silu(self.gate_proj(x)) * self.up_proj(x))
+        return self.down_proj(silu_mul(self.gate_proj(x), self.up_proj(x)))
 
 
 class DecoderLayer(nn.Module):
-    """modeling_llama.py:701-782: pre-norm attention and MLP with residuals."""
+    """modeling_llama.py:701-782: pre-norm attention and MLP with residuals.  The layer hands its MLP output and
+    the running residual to the next layer separately, so that every residual add is done by the norm that
+    consumes its result (same values, same rounding points, one kernel instead of two)."""
 
     def __init__(self, config, layer_idx: int, attention_cls):
         super().__init__()
@@ -65,14 +111,14 @@ class DecoderLayer(nn.Module):
         self.input_layernorm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps)
         self.post_attention_layernorm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps)
 
-    def forward(self, hidden_states, past_key_values):
-        residual = hidden_states
-        hidden_states = self.input_layernorm(hidden_states)
+    def forward(self, hidden_states, residual, past_key_values):
+        if residual is None:
+            residual, hidden_states = hidden_states, self.input_layernorm(hidden_states)
+        else:
+            hidden_states, residual = self.input_layernorm(hidden_states, residual)
         hidden_states, _, _ = self.self_attn(hidden_states, past_key_values=past_key_values, use_cache=True)
-        hidden_states = residual + hidden_states
-        residual = hidden_states
-        hidden_states = self.post_attention_layernorm(hidden_states)
-        return residual + self.mlp(hidden_states)
+        hidden_states, residual = self.post_attention_layernorm(hidden_states, residual)
+        return self.mlp(hidden_states), residual
 
 
 class CascadeModel(nn.Module):
@@ -84,10 +130,12 @@ class CascadeModel(nn.Module):
         self.norm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps)
 
     def forward(self, input_ids, past_key_values):
-        hidden_states = self.embed_tokens(input_ids)
+        hidden_states, residual = self.embed_tokens(input_ids), None
         for layer in self.layers:
-            hidden_states = layer(hidden_states, past_key_values)
-        return self.norm(hidden_states)
+            hidden_states, residual = layer(hidden_states, residual, past_key_values)
+        if residual is None:
+            return self.norm(hidden_states)
+        return self.norm(hidden_states, residual)[0]
 
 
 class CascadeForCausalLM(nn.Module):

@@ -223,6 +223,25 @@ int ckv_dense_attention(const void *q, int64_t q_stride_b, int64_t q_stride_h, i
                         void *scores, void *workspace, size_t workspace_bytes, void *cuda_stream);
 
 /*
+ * The two element-wise operators of the decoder layer around the attention, for the end-to-end configuration
+ * (the reference runs them as chains of framework kernels inside its forked models:
+ * cascade/models/llama/modeling_llama.py:113-127 LlamaRMSNorm, :745-770 the residual adds of the decoder layer,
+ * :282-313 the SwiGLU gate of LlamaMLP; cascade/models/qwen2/modeling_qwen2.py likewise).  16-bit rows,
+ * contiguous, 16-byte aligned, `hidden` / `cols` multiples of 8.
+ *
+ * ckv_add_rmsnorm: s = x + residual (rounded to the dtype; residual may be null: s = x), written to sum_out
+ *   when that is not null; normed = weight * T(s * rsqrt(mean(s^2) + eps)) with the variance in fp32 and the
+ *   normalised row rounded to the dtype before the weight is applied, as the reference does.  x, residual,
+ *   normed, sum_out: [rows, hidden]; weight: [hidden].  sum_out may alias residual, normed may alias x.
+ * ckv_silu_mul: out = T(T(silu(gate)) * up); gate / up: [rows, cols] with row strides ld_gate / ld_up in
+ *   elements (the two halves of one fused projection are fine), out: [rows, cols] contiguous.
+ */
+int ckv_add_rmsnorm(const void *x, const void *residual, const void *weight, void *normed, void *sum_out,
+                    int64_t rows, int32_t hidden, double eps, int32_t dtype, void *cuda_stream);
+int ckv_silu_mul(const void *gate, const void *up, void *out, int64_t rows, int32_t cols, int64_t ld_gate,
+                 int64_t ld_up, int32_t dtype, void *cuda_stream);
+
+/*
  * ckv_attention for callers that may not allocate device memory.
  * (No counterpart in the reference, whose Python layer allocates freely through torch.)
  *

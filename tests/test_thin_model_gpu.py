@@ -140,3 +140,35 @@ def test_stack_and_generation_against_cpu_replica(family, dtype):
     assert torch.equal(out.cpu(), ids), (out.cpu()[0, 150:].tolist(), ids[0, 150:].tolist())
     for lyr in model.model.layers:
         assert lyr.self_attn.last_it is True        # raised for the prompt's final stride, as the reference does
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "fp16"])
+@pytest.mark.parametrize("shape", [(2, 7, 4096), (5, 256), (1, 1, 14336)])
+def test_fused_layer_operators_against_torch(dtype, shape):
+    """``ckv_add_rmsnorm`` and ``ckv_silu_mul`` against the sequence of torch operations they replace
+    (modeling_llama.py:113-127, :282-313 of the reference): the residual sum is the same bits, the normalised
+    rows agree except where the block's summation order moves the variance by an fp32 ulp, the gate is the same
+    arithmetic."""
+    from cascading_kv_cache_b200.thin_model import add_rmsnorm, silu_mul
+    g = torch.Generator().manual_seed(shape[-1])
+    x = (torch.randn(shape, generator=g) * 1.5).to(dtype).to(DEV)
+    r = torch.randn(shape, generator=g).to(dtype).to(DEV)
+    w = (1 + 0.1 * torch.randn(shape[-1], generator=g)).to(dtype).to(DEV)
+    eps = 1e-5
+
+    def torch_norm(s):
+        h = s.float()
+        h = h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + eps)
+        return w * h.to(dtype)
+
+    for residual in (r, None):
+        normed, s = add_rmsnorm(x, residual, w, eps)
+        want_s = x if residual is None else residual + x
+        assert torch.equal(s, want_s)
+        want = torch_norm(want_s)
+        assert torch.allclose(normed.float(), want.float(), rtol=2 ** -7 if dtype == torch.bfloat16 else 2 ** -10, atol=1e-6)
+        assert (normed == want).float().mean().item() >= 0.99
+    got = silu_mul(x, r)
+    want = torch.nn.functional.silu(x) * r
+    assert torch.allclose(got.float(), want.float(), rtol=2 ** -7 if dtype == torch.bfloat16 else 2 ** -10, atol=1e-6)
+    assert (got == want).float().mean().item() >= 0.999
