@@ -532,6 +532,8 @@ def run_c5(job, args):
     with torch.device(dev):
         model = CascadeForCausalLM(cfg, "llama").to(torch.bfloat16).eval()
     model.init_weights(seed=4)
+    if args.c5_fuse:
+        model.fuse_projections()       # q|k|v and gate|up as one projection each
     cache = get_cache(model)
     cache.beta = 0.9999
     g = torch.Generator().manual_seed(4 + job.rank)
@@ -646,6 +648,7 @@ def main():
     ap.add_argument("--c5-layers", type=int, default=32)
     ap.add_argument("--c5-prompt", type=int, default=131072)
     ap.add_argument("--c5-new-tokens", type=int, default=256)
+    ap.add_argument("--c5-fuse", type=int, default=1, help="one projection for q|k|v and one for gate|up per layer")
     ap.add_argument("--c5-graph", type=int, default=1, help="decode the second half of the new tokens from a CUDA graph")
     ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
                     help="N > 1: partition the global batch (strong, default) or run the whole batch on every rank")

@@ -173,6 +173,16 @@ class CascadeAttention(nn.Module):
         return n_heads, n_kv, head_dim
 
     def qkv(self, x, size, kv_size):
+        w = getattr(self, "_qkv_weight", None)
+        if w is not None and w.device == x.device and w.dtype == x.dtype:
+            # one projection for q | k | v (thin_model.fuse_projections); the three results are strided views of
+            # its output, which the attention call reads in place
+            qkv = nn.functional.linear(x, w, getattr(self, "_qkv_bias", None))
+            nq, nkv = size[2] * size[3], kv_size[2] * kv_size[3]
+            q = qkv[..., :nq].view(*size).transpose(1, 2)
+            k = qkv[..., nq:nq + nkv].view(*kv_size).transpose(1, 2)
+            v = qkv[..., nq + nkv:].view(*kv_size).transpose(1, 2)
+            return q, k, v
         q, k, v = self.q_proj(x), self.k_proj(x), self.v_proj(x)
         q = q.view(*size).transpose(1, 2)
         k = k.view(*kv_size).transpose(1, 2)

@@ -60,15 +60,19 @@ def add_rmsnorm(x: torch.Tensor, residual: Optional[torch.Tensor], weight: torch
 def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     """``silu(gate) * up`` (modeling_llama.py:282-313), one kernel on 16-bit CUDA tensors (``ckv_silu_mul``)."""
     if _fusable(gate) and _fusable(up) and gate.shape == up.shape and gate.dtype == up.dtype:
-        lib = _lib.load()
-        out = torch.empty_like(gate)
         cols = gate.size(-1)
-        with torch.cuda.device(gate.device):
-            rc = lib.ckv_silu_mul(gate.data_ptr(), up.data_ptr(), out.data_ptr(), gate.numel() // cols, cols, cols, cols,
-                                  _lib.DTYPE_CODE[gate.dtype], _lib.current_stream_ptr(gate.device))
-        _lib.check(rc, "ckv_silu_mul")
-        return out
+        return _silu_mul_rows(gate, up, gate.numel() // cols, cols, cols, cols, gate.shape)
     return nn.functional.silu(gate) * up
+
+
+def _silu_mul_rows(gate, up, rows, cols, ld_gate, ld_up, shape):
+    lib = _lib.load()
+    out = torch.empty(shape, device=gate.device, dtype=gate.dtype)
+    with torch.cuda.device(gate.device):
+        rc = lib.ckv_silu_mul(gate.data_ptr(), up.data_ptr(), out.data_ptr(), rows, cols, ld_gate, ld_up,
+                              _lib.DTYPE_CODE[gate.dtype], _lib.current_stream_ptr(gate.device))
+    _lib.check(rc, "ckv_silu_mul")
+    return out
 
 
 class RMSNorm(nn.Module):
@@ -96,6 +100,16 @@ class SwiGLU(nn.Module):
         self.down_proj = nn.Linear(intermediate_size, hidden_size, bias=False)
 
     def forward(self, x):
+        w = getattr(self, "_gate_up_weight", None)
+        if w is not None and w.device == x.device and w.dtype == x.dtype:
+            # one projection for gate | up (fuse_projections); the gate kernel reads the two halves in place
+            n = w.size(0) // 2
+            gu = nn.functional.linear(x, w).view(-1, 2 * n)
+            if _fusable(gu) and n % 8 == 0:
+                h = _silu_mul_rows(gu[:, :n], gu[:, n:], gu.size(0), n, 2 * n, 2 * n, (*x.shape[:-1], n))
+            else:
+                h = (nn.functional.silu(gu[:, :n]) * gu[:, n:]).view(*x.shape[:-1], n)
+            return self.down_proj(h)
         return self.down_proj(silu_mul(self.gate_proj(x), self.up_proj(x)))
 
 
@@ -166,6 +180,39 @@ class CascadeForCausalLM(nn.Module):
         ``config._cascade_stride`` through the cascading cache, then one token at a time."""
         return self._sample(input_ids, past_key_values, max_new_tokens=max_new_tokens, do_sample=do_sample,
                             num_logits_to_keep=1, **kwargs)
+
+    @torch.no_grad()
+    def fuse_projections(self):
+        """q | k | v and gate | up of every layer as one weight each, so that a layer runs four projections instead
+        of seven.  The separate parameters stay (same names, same values in ``state_dict``): they become views of
+        the fused storage.  Call it once the model sits on its device in its dtype; a later ``.to()`` drops the
+        sharing and the layers fall back to the separate projections."""
+        for lyr in self.model.layers:
+            a, m = lyr.self_attn, lyr.mlp
+            parts = [a.q_proj, a.k_proj, a.v_proj]
+            with_bias = [p.bias is not None for p in parts]
+            if any(with_bias) and not all(with_bias):
+                raise ValueError("fuse_projections: q / k / v projections must all have a bias or none")
+            w = torch.cat([p.weight for p in parts], dim=0)
+            off = 0
+            for p in parts:
+                n = p.weight.size(0)
+                p.weight.data = w[off:off + n]
+                off += n
+            a._qkv_weight = w
+            if all(with_bias):
+                bias = torch.cat([p.bias for p in parts], dim=0)
+                off = 0
+                for p in parts:
+                    n = p.bias.size(0)
+                    p.bias.data = bias[off:off + n]
+                    off += n
+                a._qkv_bias = bias
+            wg = torch.cat([m.gate_proj.weight, m.up_proj.weight], dim=0)
+            n = m.gate_proj.weight.size(0)
+            m.gate_proj.weight.data, m.up_proj.weight.data = wg[:n], wg[n:]
+            m._gate_up_weight = wg
+        return self
 
     @torch.no_grad()
     def init_weights(self, seed: int, std: float = 0.02):

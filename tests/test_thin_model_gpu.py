@@ -172,3 +172,39 @@ def test_fused_layer_operators_against_torch(dtype, shape):
     want = torch.nn.functional.silu(x) * r
     assert torch.allclose(got.float(), want.float(), rtol=2 ** -7 if dtype == torch.bfloat16 else 2 ** -10, atol=1e-6)
     assert (got == want).float().mean().item() >= 0.999
+
+
+@pytest.mark.parametrize("family", ["llama", "qwen2"])
+def test_fused_projections_give_the_same_model(family):
+    """``fuse_projections``: q|k|v and gate|up as one weight each.  The parameters keep their names and values, the
+    logits of a chunked prefill + decode agree with the separate projections (the library GEMM may pick another
+    kernel for the wider weight: 16-bit tolerance), and the caches hold the same tokens."""
+    from cascading_kv_cache_b200.thin_model import get_cache
+    model, cfg = _tiny(family, torch.bfloat16, cascades=4, window=128, sinks=4, stride=48, layers=2)
+    before = {k: v.clone() for k, v in model.state_dict().items()}
+    g = torch.Generator().manual_seed(5)
+    ids = torch.randint(0, cfg.vocab_size, (1, 150), generator=g).to(DEV)
+
+    def run():
+        cache = get_cache(model)
+        cache.beta = 0.999
+        outs = []
+        with torch.no_grad():
+            for i in range(0, 150, 48):
+                outs.append(model(ids[:, i:i + 48], past_key_values=cache).logits.float())
+            for t in range(3):
+                outs.append(model(ids[:, t:t + 1], past_key_values=cache).logits.float())
+        assert cache.kernel_status() == 0
+        return outs, [cache.og_pos[l].clone() for l in range(cfg.num_hidden_layers)]
+
+    want, want_pos = run()
+    model.fuse_projections()
+    after = model.state_dict()
+    assert set(after) == set(before) and all(torch.equal(after[k], before[k]) for k in before)
+    lyr = model.model.layers[0]
+    assert lyr.self_attn.q_proj.weight.data_ptr() == lyr.self_attn._qkv_weight.data_ptr()       # views, not copies
+    got, got_pos = run()
+    for a, b in zip(got, want):
+        assert torch.allclose(a, b, atol=1e-1, rtol=0), (a - b).abs().max().item()
+    agree = sum((p == q).float().mean().item() for p, q in zip(got_pos, want_pos)) / len(want_pos)
+    assert agree >= 0.99, agree
