@@ -125,3 +125,23 @@ def test_attention_refuses_null_sink_buffers():
     assert lib.ckv_dense_attention_workspace_bytes(1, 2, 16) > 0
     status = ctypes.c_int32(0)
     assert lib.ckv_static_status(None) == -1
+
+
+def test_layer_operator_argument_errors_do_not_need_a_gpu():
+    """``ckv_add_rmsnorm`` / ``ckv_silu_mul`` refuse what they cannot serve before any CUDA call."""
+    from cascading_kv_cache_b200 import _lib
+    lib = _lib.load()
+    p = ctypes.c_void_p(4096)          # an aligned, never dereferenced address: every case below is refused first
+    assert lib.ckv_add_rmsnorm(None, None, p, p, None, 4, 64, 1e-5, _lib.CKV_BF16, None) == -1
+    assert b"required" in lib.ckv_last_error()
+    assert lib.ckv_add_rmsnorm(p, None, p, p, None, 4, 60, 1e-5, _lib.CKV_BF16, None) == -1
+    assert b"multiple of 8" in lib.ckv_last_error()
+    assert lib.ckv_add_rmsnorm(p, None, p, p, None, 4, 64, 1e-5, _lib.CKV_F32, None) != 0
+    assert b"16-bit" in lib.ckv_last_error()
+    assert lib.ckv_add_rmsnorm(ctypes.c_void_p(4100), None, p, p, None, 4, 64, 1e-5, _lib.CKV_BF16, None) == -1
+    assert b"aligned" in lib.ckv_last_error()
+    assert lib.ckv_add_rmsnorm(p, None, p, p, None, 0, 64, 1e-5, _lib.CKV_BF16, None) == 0      # no rows: nothing to do
+    assert lib.ckv_silu_mul(p, None, p, 4, 64, 64, 64, _lib.CKV_BF16, None) == -1
+    assert lib.ckv_silu_mul(p, p, p, 4, 64, 32, 64, _lib.CKV_BF16, None) == -1                 # row stride shorter than a row
+    assert lib.ckv_silu_mul(p, p, p, 4, 64, 64, 64, _lib.CKV_F32, None) != 0
+    assert lib.ckv_silu_mul(p, p, p, 0, 64, 64, 64, _lib.CKV_BF16, None) == 0
