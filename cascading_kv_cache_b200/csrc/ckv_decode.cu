@@ -805,15 +805,16 @@ __global__ void __launch_bounds__(kFinishThreads, 3) decode_finish_kernel(Decode
     const bool work_block = (int)blockIdx.x < upd_base;
 
     // the counters after this token: needed by whoever inserts the token (the old ones) and by whoever turns out
-    // to publish (the new ones); the work blocks fetch them after their EMA pass, off their critical path
-    auto load_counters = [&]() {
-        if (tid < p.C) {
-            s_stored[tid] = s_new_stored[tid] = p.stored_tokens[tid];
-            s_start[tid] = s_new_start[tid] = p.start_indices[tid];
-            s_every[tid] = p.every_n[tid];
+    // to publish (the new ones).  One warp fetches and advances them: in a work block a warp that has no head to
+    // merge, while the others merge, so the fetch adds nothing to the block's critical path.
+    auto counters_by_warp = [&]() {
+        for (int i = lane_id; i < p.C; i += 32) {
+            s_stored[i] = s_new_stored[i] = p.stored_tokens[i];
+            s_start[i] = s_new_start[i] = p.start_indices[i];
+            s_every[i] = p.every_n[i];
         }
-        __syncthreads();
-        if (tid == 0) {
+        __syncwarp();
+        if (lane_id == 0) {
             long long sinks = sc.sinks;
             advance_counters(s_new_stored, s_new_start, sinks, sc.seen, s_every, 1, p.NS, p.W, p.C, p.S, p.eager_fill);
             long long total = 0;
@@ -827,7 +828,6 @@ __global__ void __launch_bounds__(kFinishThreads, 3) decode_finish_kernel(Decode
             const volatile long long *tag = p.image_tag + 4 * ((sc.seen + 1) & 1);
             s_image_there = tag[0] == t.seen && tag[1] == t.counters && tag[2] == t.table && tag[3] == t.geometry;
         }
-        __syncthreads();
     };
     auto arrive_and_publish = [&]() {
         // every block that changed state counts itself once its writes are fenced; the last one of the grid
@@ -862,7 +862,10 @@ __global__ void __launch_bounds__(kFinishThreads, 3) decode_finish_kernel(Decode
         }
     };
 
-    if (!kStatsOnly && p.update && !work_block) load_counters();
+    if (!kStatsOnly && p.update && !work_block) {
+        if (warp == 0) counters_by_warp();
+        __syncthreads();
+    }
     if (!kStatsOnly && p.update && (int)blockIdx.x >= img_base) {
         // ---- image blocks: positions / masks from the advanced counters, every image block of the grid taking
         //      an equal share of the slots (nothing in this kernel reads them)
@@ -958,6 +961,7 @@ __global__ void __launch_bounds__(kFinishThreads, 3) decode_finish_kernel(Decode
 
     // 2. one warp per head: the partials' (max, sum) are fetched first, the new token's own logit (both
     //    operands rotated at max_pos and scaled) is worked out while they travel, then everything is merged
+    if (!kStatsOnly && p.update && warp == kFinishThreads / 32 - 1) counters_by_warp();
     constexpr int kPartsPerLane = (kMaxParts + 31) / 32;
     for (int gh = warp; gh < p.G; gh += kFinishThreads / 32) {
         float pm[kPartsPerLane], pl[kPartsPerLane];
@@ -1037,7 +1041,9 @@ __global__ void __launch_bounds__(kFinishThreads, 3) decode_finish_kernel(Decode
     {
         const int n_out = p.G * 128, per_out = (n_out + p.finish_chunks - 1) / p.finish_chunks;
         const int o_end = min(n_out, (int)(blockIdx.x + 1) * per_out);
-        for (int idx = blockIdx.x * per_out + tid; idx < o_end; idx += kFinishThreads) {
+        // the highest threads take the output rows: with a short EMA share they are the ones that have fewer
+        // vectors of the EMA pass below
+        for (int idx = blockIdx.x * per_out + (kFinishThreads - 1 - tid); idx < o_end; idx += kFinishThreads) {
             const int gh = idx >> 7, d = idx & 127;
             float acc = __expf(s_snew[gh] - s_m[gh]) * Elem<T>::to_f(vrow[d]);
 #pragma unroll 4
@@ -1099,7 +1105,6 @@ __global__ void __launch_bounds__(kFinishThreads, 3) decode_finish_kernel(Decode
         }
     }
 
-    load_counters();
     if (p.ema) {
         // the last work block of the lane inserts the token: the scores of every slot must be final
         __threadfence();
